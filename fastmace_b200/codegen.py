@@ -1,0 +1,143 @@
+"""Generates the straight-line CUDA bodies of the channelwise tensor product from the coupling tables.
+
+``python -m fastmace_b200.codegen`` writes ``csrc/generated/tp_generated.cuh`` with, for every node l_max
+(0, 1, 2) entering the product:
+
+* ``TpShape<LIN>``: number of paths, input components, components of the scattered message;
+* ``tp_forward<LIN>(x, Y, w, acc)``: ``acc[slot] += w[path] * sum_terms coef * x[m_in] * Y[m_edge]``;
+* ``tp_backward<LIN, FLIP, NEED_DX>(x, Y, w, wp, g, dY, dr, dx)``: the adjoint of the same expression for one edge and
+  one channel given the gradient ``g`` of the receiver's scattered message. ``FLIP`` evaluates the edge in the opposite
+  direction (``Y_l -> (-1)^l Y_l``, folded into the coefficients), which is how a receiver-owned walk also produces
+  the sender-side gradient of its mirror edge without atomics.
+
+The message layout is K-contiguous for the per-l linear that follows: inside the block of output irrep l the component
+index is ``base_l + m * n_seg(l) + seg`` (m the component, seg the path's rank among the paths into l).
+
+All indices are compile-time constants, so ``x``, ``Y``, ``w``, ``acc`` ... live in registers.
+"""
+
+from __future__ import annotations
+
+import os
+
+from . import so3
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+OUT = os.path.join(HERE, "csrc", "generated", "tp_generated.cuh")
+
+
+def message_slots(paths):
+    """slot[(path, m_out)] -> component index of the K-contiguous message layout; also per-l (base, n_seg)."""
+    slots, blocks, base = {}, {}, 0
+    for l_out in range(so3.LMAX_SH + 1):
+        into = so3.paths_into(paths, l_out)
+        blocks[l_out] = (base, len(into))
+        for seg, p in enumerate(into):
+            for m in range(2 * l_out + 1):
+                slots[(p, m)] = base + m * len(into) + seg
+        base += len(into) * (2 * l_out + 1)
+    return slots, blocks
+
+
+def _lit(value: float) -> str:
+    text = f"{float(value):.9g}"
+    if "." not in text and "e" not in text:
+        text += ".0"
+    return text + "f"
+
+
+def _emit(lin: int) -> str:
+    paths = so3.tp_paths(lin)
+    slots, blocks = message_slots(paths)
+    in_dim = (lin + 1) ** 2
+    mid = so3.mid_dim(paths)
+    n_terms = sum(len(p["terms"]) for p in paths)
+    out = [f"// ---- node l_max = {lin}: {len(paths)} paths, {mid} message components, {n_terms} coupling terms",
+           f"template <> struct TpShape<{lin}> {{",
+           f"    static constexpr int kPaths = {len(paths)};",
+           f"    static constexpr int kInDim = {in_dim};",
+           f"    static constexpr int kMidDim = {mid};",
+           "};",
+           ""]
+    # forward
+    out += [f"template <> __device__ __forceinline__ void tp_forward<{lin}>(const float (&x)[{in_dim}], "
+            f"const float (&Y)[16], const float (&w)[{len(paths)}], float (&acc)[{mid}]) {{"]
+    for p, path in enumerate(paths):
+        out.append(f"    // path {p}: {path['l_in']} x {path['l_edge']} -> {path['l_out']}")
+        by_out: dict[int, list] = {}
+        for mi, me, mo, c in path["terms"]:
+            by_out.setdefault(mo, []).append((mi, me, c))
+        for mo, terms in sorted(by_out.items()):
+            expr = " + ".join(f"{_lit(c)} * x[{path['in_off'] + mi}] * Y[{path['edge_off'] + me}]"
+                              for mi, me, c in terms)
+            out.append(f"    acc[{slots[(p, mo)]}] = fmaf(w[{p}], {expr}, acc[{slots[(p, mo)]}]);")
+    out += ["}", ""]
+    # backward
+    out += [f"template <bool FLIP, bool NEED_DX> __device__ __forceinline__ void tp_backward_{lin}("
+            f"const float (&x)[{in_dim}], const float (&Y)[16], const float (&w)[{len(paths)}], "
+            f"const float (&wp)[{len(paths)}], const float (&g)[{mid}], float (&dY)[16], float& dr, "
+            f"float (&dx)[{in_dim}]) {{"]
+    for p, path in enumerate(paths):
+        sign = -1.0 if path["l_edge"] % 2 else 1.0
+        out.append(f"    {{  // path {p}: {path['l_in']} x {path['l_edge']} -> {path['l_out']}")
+        out.append(f"        constexpr float sg = FLIP ? {_lit(sign)} : 1.0f;")
+        by_edge: dict[int, list] = {}
+        by_in: dict[int, list] = {}
+        for mi, me, mo, c in path["terms"]:
+            by_edge.setdefault(me, []).append((mi, mo, c))
+            by_in.setdefault(mi, []).append((me, mo, c))
+        out.append("        float dw = 0.0f;")
+        for me, terms in sorted(by_edge.items()):
+            expr = " + ".join(f"{_lit(c)} * x[{path['in_off'] + mi}] * g[{slots[(p, mo)]}]" for mi, mo, c in terms)
+            ye = path["edge_off"] + me
+            out.append(f"        {{ const float s = sg * ({expr}); dw = fmaf(s, Y[{ye}], dw); "
+                       f"dY[{ye}] = fmaf(w[{p}], s, dY[{ye}]); }}")
+        out.append(f"        dr = fmaf(wp[{p}], dw, dr);")
+        out.append("        if (NEED_DX) {")
+        for mi, terms in sorted(by_in.items()):
+            expr = " + ".join(f"{_lit(c)} * Y[{path['edge_off'] + me}] * g[{slots[(p, mo)]}]" for me, mo, c in terms)
+            xi = path["in_off"] + mi
+            out.append(f"            dx[{xi}] = fmaf(w[{p}] * sg, {expr}, dx[{xi}]);")
+        out.append("        }")
+        out.append("    }")
+    out += ["}", ""]
+    # per-l blocks of the message layout for the host (base component, segments)
+    out.append(f"template <> struct TpBlocks<{lin}> {{")
+    out.append("    static constexpr int kBase[4] = {" + ", ".join(str(blocks[l][0]) for l in range(4)) + "};")
+    out.append("    static constexpr int kSegs[4] = {" + ", ".join(str(blocks[l][1]) for l in range(4)) + "};")
+    out.append("};")
+    out.append("")
+    return "\n".join(out)
+
+
+def render() -> str:
+    head = ["// GENERATED by fastmace_b200/codegen.py from fastmace_b200/so3.py -- do not edit.",
+            "// Channelwise (uvu) tensor product of node irreps 0..LIN with spherical harmonics l <= 3 into 0e+1o+2e+3o;",
+            "// coefficients are sqrt(2 l_out + 1) * wigner_3j(l_in, l_edge, l_out).",
+            "#pragma once",
+            "",
+            "namespace fmb {",
+            "",
+            "template <int LIN> struct TpShape;",
+            "template <int LIN> struct TpBlocks;",
+            "template <int LIN> __device__ __forceinline__ void tp_forward(const float (&x)[(LIN + 1) * (LIN + 1)], "
+            "const float (&Y)[16], const float (&w)[LIN == 0 ? 4 : LIN == 1 ? 10 : 17], "
+            "float (&acc)[LIN == 0 ? 16 : LIN == 1 ? 40 : 71]);",
+            ""]
+    body = [_emit(lin) for lin in (0, 1, 2)]
+    tail = ["}  // namespace fmb", ""]
+    return "\n".join(head + body + tail)
+
+
+def main() -> str:
+    os.makedirs(os.path.dirname(OUT), exist_ok=True)
+    text = render()
+    old = open(OUT).read() if os.path.exists(OUT) else None
+    if old != text:
+        with open(OUT, "w") as handle:
+            handle.write(text)
+    return OUT
+
+
+if __name__ == "__main__":
+    print(main())

@@ -1,0 +1,282 @@
+// The energy / forces / stress evaluation: forward through both interaction layers, analytic backward to the edge
+// vectors, float64 reductions. Replaces MACEForceField.__call__ (fastmace/model/forces.py:1127-1136,1220-1240) and the
+// autograd force/virial path it runs (fastmace/rewrites/engine.py:122-192). Everything is stream-ordered and reads
+// the edge count from the device, so the whole call can be captured in a CUDA graph.
+//
+// Tensor-product weights are materialised per chunk of `chunk_edges` edges (values in the first half of tp_w,
+// d/dr in the second half); the backward pass recomputes them chunk by chunk instead of keeping them.
+
+#include "gemm.cuh"
+#include "stages.cuh"
+
+#include <cmath>
+
+namespace fmb {
+
+namespace {
+
+inline int dim_of(int lmax) { return (lmax + 1) * (lmax + 1); }
+
+// K-contiguous message layout: per output irrep l the block starts at component base[l] and holds (2l+1) rows of
+// segs[l] * C values.
+struct MidLayout {
+    int base[4];
+    int segs[4];
+    int mid_dim;
+};
+
+MidLayout mid_layout(int l_in_max) {
+    // paths of a node irrep set 0..l_in_max with harmonics 0..3 into 0..3, natural parity: count per output l
+    MidLayout m{};
+    int comp = 0;
+    for (int lo = 0; lo <= 3; ++lo) {
+        int segs = 0;
+        for (int li = 0; li <= l_in_max; ++li)
+            for (int le = 0; le <= 3; ++le)
+                if (std::abs(li - le) <= lo && lo <= li + le && ((li + le + lo) % 2 == 0)) ++segs;
+        m.base[lo] = comp;
+        m.segs[lo] = segs;
+        comp += segs * (2 * lo + 1);
+    }
+    m.mid_dim = comp;
+    return m;
+}
+
+struct Ctx {
+    const fmb_model_t* m;
+    const fmb_nl_t* nl;
+    const fmb_work_t* w;
+    cudaStream_t stream;
+    int n;
+    int hidden_dim;      // components of h after layer 0
+    long long count_cap; // entries of the edge buffers
+    int n_chunks;
+    long long chunk;
+};
+
+float* h_of(const Ctx& c, int layer) {
+    return layer == 0 ? c.w->h : c.w->h + (long long)c.n * c.hidden_dim * kC;
+}
+float* msg_of(const Ctx& c, int layer) { return c.w->msg + (long long)layer * c.n * kNSH * kC; }
+const float* hidden_of(const Ctx& c, int layer, int tangent) {
+    return c.w->edge_hidden + ((long long)(2 * layer + tangent) * c.count_cap) * kRadial;
+}
+
+int radial_weights(const Ctx& c, int layer, long long e0, bool with_tangent) {
+    const fmb_layer_t& L = c.m->layer[layer];
+    const long long rows = std::min<long long>(c.chunk, c.count_cap - e0);
+    for (int tangent = 0; tangent < (with_tangent ? 2 : 1); ++tangent) {
+        GemmArgs g;
+        g.a = hidden_of(c, layer, tangent) + e0 * kRadial;
+        g.a_bs = kRadial;
+        g.b = L.rad_w[3];
+        g.c = c.w->tp_w + (long long)tangent * c.chunk * L.n_paths * kC;
+        g.c_bs = (long long)L.n_paths * kC;
+        g.m = (int)rows;
+        g.n = L.n_paths * kC;
+        g.k = kRadial;
+        g.m_limit = (const long long*)c.nl->count;
+        g.m_limit_offset = e0;
+        const int rc = gemm(g, c.stream);
+        if (rc) return rc;
+    }
+    return FMB_OK;
+}
+
+// per-irrep linear: rows (atom, m) of block l; in/out strides in floats per atom
+int block_linear(const Ctx& c, const float* in, long long in_atom, long long in_off, int k, const float* weight,
+                 float* out, long long out_atom, long long out_off, int n_out, int l, int accumulate,
+                 const int32_t* batch_species = nullptr, int select = -1) {
+    GemmArgs g;
+    const int nm = 2 * l + 1;
+    g.a = in + in_off;
+    g.a_nm = nm; g.a_bs = in_atom; g.a_rs = k;
+    g.b = weight;
+    g.c = out + out_off;
+    g.c_nm = nm; g.c_bs = out_atom; g.c_rs = n_out;
+    g.m = c.n * nm; g.n = n_out; g.k = k;
+    g.accumulate = accumulate;
+    g.batch_species = batch_species;
+    g.select = select;
+    return gemm(g, c.stream);
+}
+
+long long lin_weight_offset(const MidLayout& ml, int l) {
+    long long off = 0;
+    for (int q = 0; q < l; ++q) off += (long long)ml.segs[q] * kC * kC;
+    return off;
+}
+
+#define FMB_TRY(expr)            \
+    do {                         \
+        const int rc__ = (expr); \
+        if (rc__) return rc__;   \
+    } while (0)
+
+int forward_layer(const Ctx& c, int layer) {
+    const fmb_layer_t& L = c.m->layer[layer];
+    const MidLayout ml = mid_layout(L.l_in_max);
+    FMB_REQUIRE(ml.mid_dim == L.mid_dim, "forward: message layout mismatch");
+    const int in_dim = dim_of(L.l_in_max), out_dim = dim_of(L.l_out_max);
+    float* h_out = h_of(c, layer);
+    const float* x = nullptr;
+    if (layer == 0) {
+        FMB_TRY(fill_from_species(c.n, out_dim * kC, c.w->species, L.sc_species, h_out, c.stream));
+        x = L.x_species;
+    } else {
+        const float* h_in = h_of(c, layer - 1);
+        const int h_in_dim = c.hidden_dim;
+        // species-dependent skip: one masked GEMM per present species and irrep, each row written exactly once
+        for (int l = 0; l <= L.skip_lmax; ++l)
+            for (int z = 0; z < c.m->n_species; ++z)
+                FMB_TRY(block_linear(c, h_in, (long long)h_in_dim * kC, (long long)l * l * kC, kC,
+                                     L.w_skip + ((long long)l * c.m->n_species + z) * kC * kC, h_out,
+                                     (long long)out_dim * kC, (long long)l * l * kC, kC, l, 0, c.w->species, z));
+        for (int l = 0; l <= L.l_in_max; ++l)
+            FMB_TRY(block_linear(c, h_in, (long long)h_in_dim * kC, (long long)l * l * kC, kC,
+                                 L.w_up + (long long)l * kC * kC, c.w->x, (long long)in_dim * kC,
+                                 (long long)l * l * kC, kC, l, 0));
+        x = c.w->x;
+    }
+    for (int k = 0; k < c.n_chunks; ++k) {
+        const long long e0 = (long long)k * c.chunk;
+        FMB_TRY(radial_weights(c, layer, e0, false));
+        TpArgs t{};
+        t.lin = L.l_in_max; t.species_x = layer == 0; t.n_atoms = c.n;
+        t.chunk_e0 = e0; t.chunk_edges = c.chunk;
+        t.count = (const long long*)c.nl->count; t.row_ptr = c.nl->edge_row_ptr; t.senders = c.nl->edge_index;
+        t.species = c.w->species; t.x = x; t.edge_sh = c.w->edge_sh; t.tp_w = c.w->tp_w; t.mid = c.w->mid;
+        FMB_TRY(tp_forward_launch(t, c.stream));
+    }
+    float* msg = msg_of(c, layer);
+    for (int l = 0; l <= 3; ++l)
+        FMB_TRY(block_linear(c, c.w->mid, (long long)ml.mid_dim * kC, (long long)ml.base[l] * kC, ml.segs[l] * kC,
+                             L.w_lin + lin_weight_offset(ml, l), msg, (long long)kNSH * kC, (long long)l * l * kC, kC, l, 0));
+    FMB_TRY(symcon_forward(c.n, L.n_sc_terms, out_dim, L.sc_terms, L.sc_coef, c.w->species, msg, c.w->basis, c.stream));
+    for (int l = 0; l <= L.l_out_max; ++l)
+        FMB_TRY(block_linear(c, c.w->basis, (long long)out_dim * kC, (long long)l * l * kC, kC,
+                             L.w_prod + (long long)l * kC * kC, h_out, (long long)out_dim * kC, (long long)l * l * kC,
+                             kC, l, 1));
+    return FMB_OK;
+}
+
+// d_h_out: gradient of this layer's output features [n][out_dim][C]. Produces d_x (layer >= 1) and the force / virial
+// contributions; for layer >= 1 also adds the skip and linear_up terms into d_h_in.
+int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in, int first_layer_of_pass) {
+    const fmb_layer_t& L = c.m->layer[layer];
+    const MidLayout ml = mid_layout(L.l_in_max);
+    const int in_dim = dim_of(L.l_in_max), out_dim = dim_of(L.l_out_max);
+    for (int l = 0; l <= L.l_out_max; ++l)
+        FMB_TRY(block_linear(c, d_h_out, (long long)out_dim * kC, (long long)l * l * kC, kC,
+                             L.w_prod_t + (long long)l * kC * kC, c.w->d_basis, (long long)out_dim * kC,
+                             (long long)l * l * kC, kC, l, 0));
+    if (layer > 0) {
+        for (int l = 0; l <= L.skip_lmax; ++l)
+            for (int z = 0; z < c.m->n_species; ++z)
+                FMB_TRY(block_linear(c, d_h_out, (long long)out_dim * kC, (long long)l * l * kC, kC,
+                                     L.w_skip_t + ((long long)l * c.m->n_species + z) * kC * kC, d_h_in,
+                                     (long long)c.hidden_dim * kC, (long long)l * l * kC, kC, l, 1, c.w->species, z));
+    }
+    FMB_TRY(symcon_backward(c.n, L.n_sc_terms, out_dim, L.sc_terms, L.sc_coef, c.w->species, msg_of(c, layer),
+                            c.w->d_basis, c.w->d_msg, c.stream));
+    for (int l = 0; l <= 3; ++l)
+        FMB_TRY(block_linear(c, c.w->d_msg, (long long)kNSH * kC, (long long)l * l * kC, kC,
+                             L.w_lin_t + lin_weight_offset(ml, l), c.w->d_mid, (long long)ml.mid_dim * kC,
+                             (long long)ml.base[l] * kC, ml.segs[l] * kC, l, 0));
+    for (int k = 0; k < c.n_chunks; ++k) {
+        const long long e0 = (long long)k * c.chunk;
+        FMB_TRY(radial_weights(c, layer, e0, true));
+        TpArgs t{};
+        t.lin = L.l_in_max; t.species_x = layer == 0; t.n_atoms = c.n;
+        t.chunk_e0 = e0; t.chunk_edges = c.chunk; t.tangent_offset = c.chunk * L.n_paths * kC;
+        t.count = (const long long*)c.nl->count; t.row_ptr = c.nl->edge_row_ptr; t.senders = c.nl->edge_index;
+        t.species = c.w->species; t.x = layer == 0 ? L.x_species : c.w->x;
+        t.edge_sh = c.w->edge_sh; t.edge_vec = c.w->edge_vec; t.tp_w = c.w->tp_w;
+        t.d_mid = c.w->d_mid; t.d_x = c.w->d_x; t.force_acc = c.w->force_acc; t.atom_virial = c.w->atom_virial;
+        t.first_layer_of_pass = first_layer_of_pass;
+        FMB_TRY(tp_backward_launch(t, c.stream));
+    }
+    if (layer > 0) {
+        for (int l = 0; l <= L.l_in_max; ++l)
+            FMB_TRY(block_linear(c, c.w->d_x, (long long)in_dim * kC, (long long)l * l * kC, kC,
+                                 L.w_up_t + (long long)l * kC * kC, d_h_in, (long long)c.hidden_dim * kC,
+                                 (long long)l * l * kC, kC, l, 1));
+    }
+    return FMB_OK;
+}
+
+int make_ctx(Ctx& c, const fmb_model_t* m, const fmb_nl_t* nl, const fmb_work_t* w, cudaStream_t stream) {
+    FMB_REQUIRE(m && nl && w, "forces: null argument");
+    FMB_REQUIRE(m->channels == kC && m->n_layers == 2 && m->radial_width == kRadial && m->n_bessel == kBessel &&
+                    m->cutoff_p == 5 && m->mlp_hidden == 16,
+                "forces: unsupported model shape (128 channels, 2 layers, 8 Bessel, p = 5, 64-wide radial MLP)");
+    FMB_REQUIRE(m->n_species >= 1 && m->n_species <= FMB_MAX_SPECIES, "forces: too many species");
+    FMB_REQUIRE(w->n_atoms == nl->n_atoms && w->edge_capacity == nl->capacity, "forces: workspace / list mismatch");
+    FMB_REQUIRE(w->chunk_edges > 0, "forces: chunk_edges must be positive");
+    c.m = m; c.nl = nl; c.w = w; c.stream = stream;
+    c.n = w->n_atoms;
+    c.hidden_dim = dim_of(m->hidden_lmax);
+    c.count_cap = nl->capacity;
+    c.chunk = std::min<long long>(w->chunk_edges, nl->capacity);
+    c.n_chunks = ceil_div(nl->capacity, c.chunk);
+    return FMB_OK;
+}
+
+double cell_volume(const fmb_nl_t* nl) {
+    const double* m = nl->cell;
+    return std::fabs(m[0] * (m[4] * m[8] - m[5] * m[7]) - m[1] * (m[3] * m[8] - m[5] * m[6]) +
+                     m[2] * (m[3] * m[7] - m[4] * m[6]));
+}
+
+}  // namespace
+
+}  // namespace fmb
+
+using namespace fmb;
+
+extern "C" FMB_API int fmb_edge_features(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work,
+                                 const double* positions, fmb_stream_t stream) {
+    FMB_REQUIRE(model && nl && work && positions, "fmb_edge_features: null argument");
+    return edge_features(model, nl, work, positions, (cudaStream_t)stream);
+}
+
+extern "C" FMB_API int fmb_forward(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, fmb_stream_t stream) {
+    Ctx c;
+    FMB_TRY(make_ctx(c, model, nl, work, (cudaStream_t)stream));
+    FMB_TRY(forward_layer(c, 0));
+    FMB_TRY(forward_layer(c, 1));
+    // readout; the gradient of the last layer's scalars is parked in `basis` (free after the forward pass)
+    FMB_TRY(readout(model, c.n, h_of(c, 0), h_of(c, 1), work->node_energy, work->d_h, work->basis, c.stream));
+    return FMB_OK;
+}
+
+extern "C" FMB_API int fmb_backward(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, fmb_stream_t stream) {
+    Ctx c;
+    FMB_TRY(make_ctx(c, model, nl, work, (cudaStream_t)stream));
+    FMB_TRY(backward_layer(c, 1, work->basis, work->d_h, 1));
+    FMB_TRY(backward_layer(c, 0, work->d_h, nullptr, 0));
+    FMB_TRY(reduce_outputs(model, work, cell_volume(nl), c.stream));
+    return FMB_OK;
+}
+
+extern "C" FMB_API int fmb_forces(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, const double* positions,
+                          fmb_stream_t stream) {
+    FMB_TRY(fmb_edge_features(model, nl, work, positions, stream));
+    FMB_TRY(fmb_forward(model, nl, work, stream));
+    FMB_TRY(fmb_backward(model, nl, work, stream));
+    return FMB_OK;
+}
+
+extern "C" FMB_API int fmb_gemm(const float* a, const float* b, float* c, int m, int n, int k, int accumulate, int impl,
+                        fmb_stream_t stream) {
+    GemmArgs g;
+    g.a = a; g.b = b; g.c = c; g.m = m; g.n = n; g.k = k;
+    g.a_bs = k; g.c_bs = n; g.accumulate = accumulate;
+    return impl == 1 ? gemm_tc(g, (cudaStream_t)stream) : gemm_simt(g, (cudaStream_t)stream);
+}
+
+extern "C" FMB_API int fmb_commit_forces(const fmb_work_t* work, double* forces64, double* energy64, double* stress64,
+                                 fmb_stream_t stream) {
+    FMB_REQUIRE(work && forces64 && energy64, "fmb_commit_forces: null argument");
+    return commit_forces(work, forces64, energy64, work->compute_stress ? stress64 : nullptr, (cudaStream_t)stream);
+}

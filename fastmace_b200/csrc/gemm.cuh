@@ -1,0 +1,37 @@
+// fp32 GEMM with batch/row-strided operands, the building block of the per-irrep linears, the species-dependent
+// skip, the readout-side products and the last layer of the radial MLP.
+#pragma once
+
+#include "fmb_common.cuh"
+
+namespace fmb {
+
+// C[r, :] (+)= A[r, :] * B for r in [0, m). Row r of A starts at a + (r / a_nm) * a_bs + (r % a_nm) * a_rs, and the
+// same for C; B is [k][n] row-major with leading dimension ldb.
+struct GemmArgs {
+    const float* a = nullptr;
+    const float* b = nullptr;
+    float* c = nullptr;
+    int m = 0, n = 0, k = 0;
+    int a_nm = 1;
+    long long a_bs = 0, a_rs = 0;
+    int c_nm = 1;
+    long long c_bs = 0, c_rs = 0;
+    int ldb = 0;
+    int accumulate = 0;
+    // optional: rows at or beyond *m_limit - m_limit_offset (a device scalar, e.g. the edge count) are skipped
+    const long long* m_limit = nullptr;
+    long long m_limit_offset = 0;
+    int m_limit_scale = 1;            // rows per counted unit (2 when values and tangents are stacked)
+    // optional: only batches whose species equals `select` are written (species-dependent linear)
+    const int32_t* batch_species = nullptr;
+    int select = -1;
+};
+
+int gemm_simt(const GemmArgs& args, cudaStream_t stream);
+// tcgen05 / TMEM 3xTF32 kernel; returns FMB_ERR_UNSUPPORTED for shapes it does not take.
+int gemm_tc(const GemmArgs& args, cudaStream_t stream);
+// picks gemm_tc when it applies and FMB_GEMM selects it, else gemm_simt
+int gemm(const GemmArgs& args, cudaStream_t stream);
+
+}  // namespace fmb

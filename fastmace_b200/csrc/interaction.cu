@@ -1,0 +1,338 @@
+// Channelwise equivariant tensor product fused with the receiver-sorted segmented sum, and its analytic adjoint.
+//
+// Forward (replaces conv_tp + scatter_sum, fastmace/rewrites/generic/modules.py:485-486, and the receiver-streaming
+// kernel fastmace/kernels/oeq_streaming/factorized_projected.cuh:128-186): one CTA of 128 threads (one per channel)
+// owns a receiver, walks its CSR edges, keeps the whole message row in registers and writes it once. No atomics.
+//
+// Backward (replaces autograd through conv_tp and the edge-owned kernel factorized_projected.cuh:258-353, which
+// scatters the sender gradient with atomicAdd): the neighbour list is full, so every edge j -> a has a mirror
+// a -> j with the opposite vector, the same length (hence the same radial weights) and harmonics (-1)^l Y_lm.
+// The CTA that owns atom a therefore evaluates, for each edge j -> a of its row,
+//   * the edge as stored   (receiver a: own message gradient g_a, gathered sender features x_j), and
+//   * its mirror a -> j    (receiver j: gathered g_j, own features x_a),
+// which yields dE/dY and dE/dr of both edges summed (the force on a is minus the sum over its row of the combined
+// edge-vector gradient) and the complete gradient of x_a -- all owned by this CTA, so nothing is scattered.
+// The virial is half the sum over rows of v (x) q because every edge is visited in both roles.
+
+#include "stages.cuh"
+#include "generated/tp_generated.cuh"
+
+#include <map>
+
+namespace fmb {
+
+namespace {
+
+template <int LIN, bool FLIP, bool NEED_DX> struct TpBackward;
+#define FMB_TP_BACKWARD(LIN_)                                                                                          \
+    template <bool FLIP, bool NEED_DX> struct TpBackward<LIN_, FLIP, NEED_DX> {                                        \
+        template <typename... A> static __device__ __forceinline__ void run(A&&... a) {                               \
+            tp_backward_##LIN_<FLIP, NEED_DX>(a...);                                                                   \
+        }                                                                                                              \
+    };
+FMB_TP_BACKWARD(0)
+FMB_TP_BACKWARD(1)
+FMB_TP_BACKWARD(2)
+
+// First row a chunk starting at edge e0 has to visit: the smallest r whose edges reach beyond e0 or start at or after
+// it (rows finished by earlier chunks are skipped; empty rows are initialised by the chunk their offset falls in).
+__device__ __forceinline__ int chunk_first_row(const int32_t* __restrict__ row_ptr, int n, long long e0) {
+    int lo = 0, hi = n;
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (row_ptr[mid + 1] > e0 || row_ptr[mid] >= e0) hi = mid; else lo = mid + 1;
+    }
+    return lo;
+}
+
+__device__ __forceinline__ void load_sh(const float* __restrict__ edge_sh, long long e, float (&Y)[16]) {
+    const float4* p = reinterpret_cast<const float4*>(edge_sh + 16 * e);
+    const float4 a = __ldg(p), b = __ldg(p + 1), c = __ldg(p + 2), d = __ldg(p + 3);
+    Y[0] = a.x; Y[1] = a.y; Y[2] = a.z; Y[3] = a.w; Y[4] = b.x; Y[5] = b.y; Y[6] = b.z; Y[7] = b.w;
+    Y[8] = c.x; Y[9] = c.y; Y[10] = c.z; Y[11] = c.w; Y[12] = d.x; Y[13] = d.y; Y[14] = d.z; Y[15] = d.w;
+}
+
+// ---------------------------------------------------------------------------------------------- forward
+template <int LIN, bool SPECIES_X>
+__global__ void __launch_bounds__(kC)
+k_tp_forward(int n_atoms, long long chunk_e0, long long chunk_edges, const long long* __restrict__ count_ptr,
+             const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ senders,
+             const int32_t* __restrict__ species, const float* __restrict__ x, const float* __restrict__ edge_sh,
+             const float* __restrict__ tp_w, float* __restrict__ mid) {
+    constexpr int P = TpShape<LIN>::kPaths, IN = TpShape<LIN>::kInDim, MID = TpShape<LIN>::kMidDim;
+    const long long count = *count_ptr;
+    const long long e0 = chunk_e0, e1 = min(count, chunk_e0 + chunk_edges);
+    if (e0 >= e1 && !(e0 == 0 && count == 0)) return;
+    const int c = threadIdx.x;
+    const int first = (e0 == 0) ? 0 : chunk_first_row(row_ptr, n_atoms, e0);
+    for (int i = first + blockIdx.x; i < n_atoms; i += gridDim.x) {
+        const long long rb = row_ptr[i], re = row_ptr[i + 1];
+        if (rb >= e1 && e1 < count) break;   // rows of later chunks (the last chunk also zeroes trailing empty rows)
+        float acc[MID];
+        float* out = mid + ((long long)i * MID) * kC + c;
+        if (rb < e0) {
+#pragma unroll
+            for (int k = 0; k < MID; ++k) acc[k] = out[(long long)k * kC];   // continue a row split by the chunking
+        } else {
+#pragma unroll
+            for (int k = 0; k < MID; ++k) acc[k] = 0.0f;
+        }
+        const long long b = max(rb, e0), en = min(re, e1);
+        for (long long e = b; e < en; ++e) {
+            const int s = senders[e];
+            float xs[IN], Y[16], w[P];
+            if (SPECIES_X) {
+                xs[0] = __ldg(x + (long long)species[s] * kC + c);
+            } else {
+#pragma unroll
+                for (int k = 0; k < IN; ++k) xs[k] = __ldg(x + ((long long)s * IN + k) * kC + c);
+            }
+            load_sh(edge_sh, e, Y);
+            const float* wr = tp_w + (e - chunk_e0) * (long long)(P * kC) + c;
+#pragma unroll
+            for (int p = 0; p < P; ++p) w[p] = __ldg(wr + p * kC);
+            tp_forward<LIN>(xs, Y, w, acc);
+        }
+#pragma unroll
+        for (int k = 0; k < MID; ++k) out[(long long)k * kC] = acc[k];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------- backward
+constexpr int kEdgeBatch = 8;
+constexpr int kRed = 17;     // 16 harmonic gradients + the radial one
+
+// After the call, lane l of each warp holds in `v[0]` the warp sum of value (l >> 1) of the 16 inputs.
+__device__ __forceinline__ void warp_reduce16(float (&v)[16]) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int half = 8, bit = 16; half >= 1; half >>= 1, bit >>= 1) {
+        const bool upper = (lane & bit) != 0;
+#pragma unroll
+        for (int i = 0; i < half; ++i) {
+            const float keep = upper ? v[i + half] : v[i];
+            const float send = upper ? v[i] : v[i + half];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
+        }
+    }
+    v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1);
+}
+
+// gradient of the 16 harmonics (component normalised, on the unit vector u) and of the length with respect to the
+// edge vector: fastmace/kernels/triton/edge_sh.py:82-126 plus dr * u.
+__device__ __forceinline__ void edge_vector_gradient(const float* g, float dr, float x, float y, float z, float len,
+                                                     float (&q)[3]) {
+    const float S3 = 1.7320508075688772f, S5 = 2.23606797749979f, S56 = 0.9128709291752769f, S38 = 0.6123724356957945f;
+    const float C1 = 1.7320508075688772f, C2 = 2.23606797749979f, C3 = 2.6457513110645907f;
+    const float g1x = g[1] * C1, g1y = g[2] * C1, g1z = g[3] * C1;
+    const float g20 = g[4] * C2, g21 = g[5] * C2, g22 = g[6] * C2, g23 = g[7] * C2, g24 = g[8] * C2;
+    const float g30 = g[9] * C3, g31 = g[10] * C3, g32 = g[11] * C3, g33 = g[12] * C3, g34 = g[13] * C3,
+                g35 = g[14] * C3, g36 = g[15] * C3;
+    const float s20 = S3 * x * z;
+    const float s24 = S3 / 2.0f * (z * z - x * x);
+    const float y2 = y * y;
+    const float x2z2 = x * x + z * z;
+    const float a = 4.0f * y2 - x2z2;
+    const float b = 2.0f * y2 - 3.0f * x2z2;
+    const float gs20 = g20 + S56 * (g30 * z - g36 * x) + S5 * g31 * y;
+    const float gs24 = g24 + S56 * (g30 * x + g36 * z) + S5 * g35 * y;
+    const float ga = S38 * (g32 * x + g34 * z);
+    const float gb = 0.5f * y * g33;
+    const float gy2 = g22 + 4.0f * ga + 2.0f * gb;
+    const float gx2z2 = -0.5f * g22 - ga - 3.0f * gb;
+    const float gx = g1x + S3 * z * gs20 + S3 * y * g21 - S3 * x * gs24 + 2.0f * x * gx2z2 +
+                     S56 * (g30 * s24 - g36 * s20) + S38 * a * g32;
+    const float gy = g1y + S3 * x * g21 + S3 * z * g23 + 2.0f * y * gy2 + S5 * (g31 * s20 + g35 * s24) + 0.5f * b * g33;
+    const float gz = g1z + S3 * x * gs20 + S3 * y * g23 + S3 * z * gs24 + 2.0f * z * gx2z2 +
+                     S56 * (g30 * s20 + g36 * s24) + S38 * a * g34;
+    const float d = fmaxf(len, 1e-12f);
+    const float dot = len > 1e-12f ? x * gx + y * gy + z * gz : 0.0f;
+    q[0] = (gx - x * dot) / d + dr * x;
+    q[1] = (gy - y * dot) / d + dr * y;
+    q[2] = (gz - z * dot) / d + dr * z;
+}
+
+template <int LIN, bool SPECIES_X, bool NEED_DX>
+__global__ void __launch_bounds__(kC)
+k_tp_backward(int n_atoms, long long chunk_e0, long long chunk_edges, long long tangent_offset,
+              const long long* __restrict__ count_ptr, const int32_t* __restrict__ row_ptr,
+              const int32_t* __restrict__ senders, const int32_t* __restrict__ species, const float* __restrict__ x,
+              const float* __restrict__ edge_sh, const float* __restrict__ edge_vec, const float* __restrict__ tp_w,
+              const float* __restrict__ d_mid, float* __restrict__ d_x, float* __restrict__ force_acc,
+              float* __restrict__ atom_virial, int first_layer_of_pass) {
+    constexpr int P = TpShape<LIN>::kPaths, IN = TpShape<LIN>::kInDim, MID = TpShape<LIN>::kMidDim;
+    __shared__ float red[kEdgeBatch][4][kRed + 1];
+    const long long count = *count_ptr;
+    const long long e0 = chunk_e0, e1 = min(count, chunk_e0 + chunk_edges);
+    const int c = threadIdx.x, warp = c >> 5, lane = c & 31;
+    if (e0 >= e1 && !(e0 == 0 && count == 0)) return;
+    const int first = (e0 == 0) ? 0 : chunk_first_row(row_ptr, n_atoms, e0);
+    for (int a = first + blockIdx.x; a < n_atoms; a += gridDim.x) {
+        const long long rb = row_ptr[a], re = row_ptr[a + 1];
+        if (rb >= e1 && e1 < count) break;
+        const bool continued = rb < e0;     // this row started in an earlier chunk: accumulate onto its partial sums
+        float g_a[MID], x_a[IN], dx[IN];
+#pragma unroll
+        for (int k = 0; k < MID; ++k) g_a[k] = __ldg(d_mid + ((long long)a * MID + k) * kC + c);
+        if (SPECIES_X) {
+            x_a[0] = __ldg(x + (long long)species[a] * kC + c);
+        } else {
+#pragma unroll
+            for (int k = 0; k < IN; ++k) x_a[k] = __ldg(x + ((long long)a * IN + k) * kC + c);
+        }
+#pragma unroll
+        for (int k = 0; k < IN; ++k) dx[k] = 0.0f;
+        float fsum[3] = {0.f, 0.f, 0.f}, vir[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        const long long b = max(rb, e0), en = min(re, e1);
+        for (long long batch = b; batch < en; batch += kEdgeBatch) {
+            const int nb = (int)min((long long)kEdgeBatch, en - batch);
+            for (int k = 0; k < nb; ++k) {
+                const long long e = batch + k;
+                const int j = senders[e];
+                float Y[16], w[P], wp[P], x_j[IN], dY[16];
+                load_sh(edge_sh, e, Y);
+                const float* wr = tp_w + (e - chunk_e0) * (long long)(P * kC) + c;
+#pragma unroll
+                for (int p = 0; p < P; ++p) {
+                    w[p] = __ldg(wr + p * kC);
+                    wp[p] = __ldg(wr + tangent_offset + p * kC);
+                }
+                if (SPECIES_X) {
+                    x_j[0] = __ldg(x + (long long)species[j] * kC + c);
+                } else {
+#pragma unroll
+                    for (int q = 0; q < IN; ++q) x_j[q] = __ldg(x + ((long long)j * IN + q) * kC + c);
+                }
+#pragma unroll
+                for (int q = 0; q < 16; ++q) dY[q] = 0.0f;
+                float dr = 0.0f;
+                float unused[IN];
+                // the edge as stored: receiver a, sender j
+                TpBackward<LIN, false, false>::run(x_j, Y, w, wp, g_a, dY, dr, unused);
+                // its mirror: receiver j, sender a
+                {
+                    float g_j[MID];
+#pragma unroll
+                    for (int q = 0; q < MID; ++q) g_j[q] = __ldg(d_mid + ((long long)j * MID + q) * kC + c);
+                    TpBackward<LIN, true, NEED_DX>::run(x_a, Y, w, wp, g_j, dY, dr, dx);
+                }
+                warp_reduce16(dY);
+                dr = warp_sum(dr);
+                if ((lane & 1) == 0) red[k][warp][lane >> 1] = dY[0];
+                if (lane == 0) red[k][warp][16] = dr;
+            }
+            __syncthreads();
+            if (c < nb) {
+                const long long e = batch + c;
+                float g[16];
+#pragma unroll
+                for (int q = 0; q < 16; ++q) g[q] = red[c][0][q] + red[c][1][q] + red[c][2][q] + red[c][3][q];
+                const float drt = red[c][0][16] + red[c][1][16] + red[c][2][16] + red[c][3][16];
+                const float4 uv = __ldg(reinterpret_cast<const float4*>(edge_vec) + e);
+                float q3[3];
+                edge_vector_gradient(g, drt, uv.x, uv.y, uv.z, uv.w, q3);
+                fsum[0] += q3[0]; fsum[1] += q3[1]; fsum[2] += q3[2];
+                const float vx = uv.x * uv.w, vy = uv.y * uv.w, vz = uv.z * uv.w;
+                vir[0] += vx * q3[0]; vir[1] += vy * q3[1]; vir[2] += vz * q3[2];
+                vir[3] += 0.5f * (vy * q3[2] + vz * q3[1]);
+                vir[4] += 0.5f * (vx * q3[2] + vz * q3[0]);
+                vir[5] += 0.5f * (vx * q3[1] + vy * q3[0]);
+            }
+            __syncthreads();
+        }
+        // threads 0..7 hold partial force / virial sums: fold them inside warp 0
+        if (warp == 0) {
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) {
+#pragma unroll
+                for (int q = 0; q < 3; ++q) fsum[q] += __shfl_xor_sync(0xffffffffu, fsum[q], o);
+#pragma unroll
+                for (int q = 0; q < 6; ++q) vir[q] += __shfl_xor_sync(0xffffffffu, vir[q], o);
+            }
+            if (lane == 0) {
+                const bool fresh = first_layer_of_pass && !continued;
+#pragma unroll
+                for (int q = 0; q < 3; ++q)
+                    force_acc[3 * a + q] = (fresh ? 0.0f : force_acc[3 * a + q]) + fsum[q];
+#pragma unroll
+                for (int q = 0; q < 6; ++q)
+                    atom_virial[6 * a + q] = (fresh ? 0.0f : atom_virial[6 * a + q]) + 0.5f * vir[q];
+            }
+        }
+        if (NEED_DX) {
+#pragma unroll
+            for (int k = 0; k < IN; ++k) {
+                float* dst = d_x + ((long long)a * IN + k) * kC + c;
+                *dst = continued ? *dst + dx[k] : dx[k];
+            }
+        }
+    }
+}
+
+int persistent_grid(const void* kernel, int n_atoms) {
+    static std::map<const void*, int> cache;
+    auto it = cache.find(kernel);
+    if (it == cache.end()) {
+        int per_sm = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kC, 0) != cudaSuccess || per_sm < 1) per_sm = 1;
+        int sms = 148, dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        it = cache.emplace(kernel, per_sm * sms * 4).first;
+    }
+    return n_atoms < it->second ? n_atoms : it->second;
+}
+
+}  // namespace
+
+int tp_forward_launch(const TpArgs& t, cudaStream_t stream) {
+#define FMB_FWD(LIN_, SP_)                                                                                             \
+    {                                                                                                                  \
+        auto kernel = k_tp_forward<LIN_, SP_>;                                                                         \
+        const int grid = persistent_grid((const void*)kernel, t.n_atoms);                                                           \
+        kernel<<<grid, kC, 0, stream>>>(t.n_atoms, t.chunk_e0, t.chunk_edges, t.count, t.row_ptr, t.senders,           \
+                                        t.species, t.x, t.edge_sh, t.tp_w, t.mid);                                     \
+    }
+    if (t.species_x) {
+        FMB_REQUIRE(t.lin == 0, "tp_forward: species table only for scalar senders");
+        FMB_FWD(0, true)
+    } else if (t.lin == 0) {
+        FMB_FWD(0, false)
+    } else if (t.lin == 1) {
+        FMB_FWD(1, false)
+    } else if (t.lin == 2) {
+        FMB_FWD(2, false)
+    } else {
+        FMB_REQUIRE(false, "tp_forward: unsupported node l_max");
+    }
+#undef FMB_FWD
+    FMB_LAUNCH_CHECK();
+    return FMB_OK;
+}
+
+int tp_backward_launch(const TpArgs& t, cudaStream_t stream) {
+#define FMB_BWD(LIN_, SP_, DX_)                                                                                        \
+    {                                                                                                                  \
+        auto kernel = k_tp_backward<LIN_, SP_, DX_>;                                                                   \
+        const int grid = persistent_grid((const void*)kernel, t.n_atoms);                                                           \
+        kernel<<<grid, kC, 0, stream>>>(t.n_atoms, t.chunk_e0, t.chunk_edges, t.tangent_offset, t.count, t.row_ptr,    \
+                                        t.senders, t.species, t.x, t.edge_sh, t.edge_vec, t.tp_w, t.d_mid, t.d_x,      \
+                                        t.force_acc, t.atom_virial, t.first_layer_of_pass);                            \
+    }
+    if (t.species_x) {
+        FMB_REQUIRE(t.lin == 0, "tp_backward: species table only for scalar senders");
+        FMB_BWD(0, true, false)
+    } else if (t.lin == 0) {
+        FMB_BWD(0, false, true)
+    } else if (t.lin == 1) {
+        FMB_BWD(1, false, true)
+    } else if (t.lin == 2) {
+        FMB_BWD(2, false, true)
+    } else {
+        FMB_REQUIRE(false, "tp_backward: unsupported node l_max");
+    }
+#undef FMB_BWD
+    FMB_LAUNCH_CHECK();
+    return FMB_OK;
+}
+
+}  // namespace fmb

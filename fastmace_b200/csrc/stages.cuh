@@ -1,0 +1,44 @@
+// Internal launch functions shared between the translation units of libfmb200.
+#pragma once
+
+#include "fmb_common.cuh"
+
+namespace fmb {
+
+int edge_features(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, const double* positions,
+                  cudaStream_t stream);
+
+struct TpArgs {
+    int lin;
+    bool species_x;
+    int n_atoms;
+    long long chunk_e0, chunk_edges, tangent_offset;
+    const long long* count;
+    const int32_t* row_ptr;
+    const int32_t* senders;
+    const int32_t* species;
+    const float* x;
+    const float* edge_sh;
+    const float* edge_vec;
+    const float* tp_w;
+    float* mid;            // forward output
+    const float* d_mid;    // backward input
+    float* d_x;
+    float* force_acc;
+    float* atom_virial;
+    int first_layer_of_pass;
+};
+int tp_forward_launch(const TpArgs& t, cudaStream_t stream);
+int tp_backward_launch(const TpArgs& t, cudaStream_t stream);
+
+int symcon_forward(int n_atoms, int n_terms, int out_dim, const int32_t* terms, const float* coef,
+                   const int32_t* species, const float* msg, float* basis, cudaStream_t stream);
+int symcon_backward(int n_atoms, int n_terms, int out_dim, const int32_t* terms, const float* coef,
+                    const int32_t* species, const float* msg, const float* d_basis, float* d_msg, cudaStream_t stream);
+int fill_from_species(int n_atoms, int row, const int32_t* species, const float* table, float* out, cudaStream_t stream);
+int readout(const fmb_model_t* m, int n_atoms, const float* h_first, const float* h_last, float* node_energy,
+            float* d_h_first, float* d_h_last, cudaStream_t stream);
+int reduce_outputs(const fmb_model_t* m, const fmb_work_t* w, double volume, cudaStream_t stream);
+int commit_forces(const fmb_work_t* w, double* f64, double* e64, double* s64, cudaStream_t stream);
+
+}  // namespace fmb

@@ -1,0 +1,199 @@
+"""``B200ForceField``: FastMACE's ``ForceField`` protocol (``fastmace/model/forces.py:63-161``) over the C ABI.
+
+Same members, argument meaning and ownership rules as the reference's ``MACEForceField`` (``forces.py:382``) and its
+minimal worked example ``TorchLJ`` (``tests/cpu/test_engine.py:40-114``): the force field owns the model, the
+neighbour list and every persistent device buffer at a fixed address; ``__call__`` is graph-capturable and returns
+views it owns; ``rebuild`` is host-driven and returns True when the edge buffers moved.
+
+Differences that follow from the device design: the kernels read the edge count and CSR row pointers on the device,
+so ``use_edges`` only records the padded size the caller asked for (``padding_exact`` stays True: edges past the count
+are simply never read), and forces come from analytic backward kernels, not autograd.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import NamedTuple
+
+import numpy as np
+import torch
+
+from . import _lib
+from .model import MaceSpec
+from .neighbours import CellListNeighbours, NeighbourConfig
+from .packing import PackedModel
+
+DEFAULT_CHUNK_EDGES = 1 << 19
+
+
+class ForceOutput(NamedTuple):
+    """``energy`` (1,) float64 eV, ``forces`` (N, 3) float32 eV/Å, ``stress`` (3, 3) float32 eV/Å³ or None
+    (ASE sign, no kinetic part): ``fastmace/model/forces.py:35-47``."""
+    energy: torch.Tensor
+    forces: torch.Tensor
+    stress: torch.Tensor | None
+
+
+class B200ForceField:
+    def __init__(self, spec: MaceSpec, weights, numbers, cell, *, compute_stress: bool = False, device="cuda",
+                 neighbours: NeighbourConfig | None = None, chunk_edges: int = DEFAULT_CHUNK_EDGES,
+                 positions=None):
+        if not torch.cuda.is_available():
+            raise _lib.Fmb200Error("B200ForceField needs a CUDA device: there is no CPU path")
+        self.lib = _lib.load()
+        self.spec = spec
+        self._device = torch.device(device)
+        if self._device.index is None:
+            self._device = torch.device("cuda", torch.cuda.current_device())
+        self._compute_stress = bool(compute_stress)
+        self.numbers = np.asarray(numbers, dtype=np.int64)
+        self.natoms = len(self.numbers)
+        self.cell = np.asarray(cell, dtype=np.float64).reshape(3, 3)
+        self.packed = PackedModel(spec, weights, sorted(set(int(z) for z in self.numbers)), self._device)
+        self.species = self.packed.species_index(self.numbers)
+        self.neighbours = CellListNeighbours(self.cell, spec.r_cut, self._device, torch.float32, neighbours)
+        self.chunk_edges = int(chunk_edges)
+        self.num_edges = 0
+        self.calls = 0
+        self.data = {}
+        self.work = None
+        self._outputs()
+        if positions is not None:
+            x = torch.as_tensor(positions, dtype=torch.float64, device=self._device)
+            self.rebuild(x)
+            self.compact(x)
+            self.use_edges(int(self.edge_count))
+
+    # ------------------------------------------------------------------ protocol properties
+    @property
+    def device(self) -> torch.device:
+        return self._device
+
+    dtype = torch.float32
+    padding_exact = True
+    compile_mode = "none"
+
+    @property
+    def compute_stress(self) -> bool:
+        return self._compute_stress
+
+    @property
+    def edge_count(self) -> torch.Tensor:
+        return self.neighbours.count
+
+    @property
+    def edge_capacity(self) -> int:
+        return self.neighbours.capacity
+
+    # ------------------------------------------------------------------ buffers
+    def _outputs(self):
+        dev = self._device
+        self.energy = torch.zeros(1, dtype=torch.float64, device=dev)
+        self.forces = torch.zeros(self.natoms, 3, dtype=torch.float32, device=dev)
+        self.stress = torch.zeros(3, 3, dtype=torch.float32, device=dev)
+        self.status = torch.zeros((), dtype=torch.int32, device=dev)
+
+    def _allocate_work(self):
+        spec, n, cap, dev = self.spec, self.natoms, self.neighbours.capacity, self._device
+        c = spec.channels
+        chunk = min(self.chunk_edges, cap)
+        max_paths = max(len(spec.paths(t)) for t in range(spec.num_interactions))
+        max_mid = max(self.packed.struct.layer[t].mid_dim for t in range(spec.num_interactions))
+        hid = (spec.hidden_lmax + 1) ** 2
+        f32 = dict(dtype=torch.float32, device=dev)
+        buf = {
+            "edge_vec": torch.zeros(cap, 4, **f32),
+            "edge_sh": torch.zeros(cap, 16, **f32),
+            "edge_hidden": torch.zeros(spec.num_interactions, 2, cap, 64, **f32),
+            "tp_w": torch.zeros(2 * chunk, max_paths * c, **f32),
+            "x": torch.zeros(n, hid, c, **f32),
+            "mid": torch.zeros(n, max_mid, c, **f32),
+            "msg": torch.zeros(spec.num_interactions, n, 16, c, **f32),
+            "basis": torch.zeros(n, hid, c, **f32),
+            "h": torch.zeros(n * (hid + 1), c, **f32),
+            "d_h": torch.zeros(n, hid, c, **f32),
+            "d_basis": torch.zeros(n, hid, c, **f32),
+            "d_msg": torch.zeros(n, 16, c, **f32),
+            "d_mid": torch.zeros(n, max_mid, c, **f32),
+            "d_x": torch.zeros(n, hid, c, **f32),
+            "node_energy": torch.zeros(n, **f32),
+            "atom_virial": torch.zeros(n, 6, **f32),
+            "force_acc": torch.zeros(n, 3, **f32),
+            "partial": torch.zeros(1024 * 8, dtype=torch.float64, device=dev),
+        }
+        self.buf = buf
+        w = _lib.WorkStruct()
+        w.n_atoms, w.edge_capacity, w.chunk_edges, w.compute_stress = n, cap, chunk, int(self._compute_stress)
+        w.species = self.species.data_ptr()
+        for name, tensor in buf.items():
+            setattr(w, name, tensor.data_ptr())
+        w.energy, w.forces, w.stress = self.energy.data_ptr(), self.forces.data_ptr(), self.stress.data_ptr()
+        w.status = self.status.data_ptr()
+        self.work = w
+
+    # ------------------------------------------------------------------ protocol methods
+    def rebuild(self, positions: torch.Tensor) -> bool:
+        """Rebuild the candidate pairs (host-driven, synchronises). True if the edge capacity grew."""
+        grew = self.neighbours.build(positions)
+        if grew or self.work is None:
+            self._allocate_work()
+        return grew
+
+    def compact(self, positions: torch.Tensor) -> None:
+        self.neighbours.compact(positions)
+
+    def needs_rebuild(self, positions: torch.Tensor, fraction: float = 1.0) -> torch.Tensor:
+        return self.neighbours.needs_rebuild(positions, fraction) != 0
+
+    def use_edges(self, num_edges: int) -> None:
+        self.num_edges = int(num_edges)
+        self.data["edge_index"] = self.neighbours.edge_index[:, :self.num_edges]
+
+    def set_cell(self, cell: torch.Tensor) -> None:
+        raise NotImplementedError("variable-cell runs are outside this force field's scope (fixed cell only)")
+
+    def __call__(self, positions: torch.Tensor) -> ForceOutput:
+        """Energy, forces (and stress) at float64 ``positions`` (N, 3) on the compacted edges. Graph-capturable."""
+        if self.work is None:
+            raise _lib.Fmb200Error("call rebuild() and compact() before the first force call")
+        if positions.dtype != torch.float64 or not positions.is_cuda:
+            raise ValueError("positions must be a float64 CUDA tensor")
+        self.calls += 1
+        _lib.check(self.lib.fmb_forces(self.packed.pointer(), self.neighbours.pointer(), ctypes.byref(self.work),
+                                       positions.data_ptr(), _lib.current_stream()), "fmb_forces")
+        return ForceOutput(self.energy, self.forces, self.stress if self._compute_stress else None)
+
+    def evaluate(self, atoms, stress: bool = False):
+        """One-off evaluation (``ForceField.evaluate``): rebuilds the list, synchronises, returns host values:
+        (energy float eV, forces (N, 3) float64 ndarray, stress (3, 3) ndarray or None)."""
+        if stress and not self._compute_stress:
+            raise ValueError("built without compute_stress")
+        x = torch.as_tensor(np.asarray(atoms.get_positions(), dtype=np.float64), device=self._device)
+        self.rebuild(x)
+        self.compact(x)
+        self.use_edges(int(self.edge_count))
+        out = self(x)
+        torch.cuda.synchronize(self._device)
+        self.check_status()
+        return (float(out.energy.item()), out.forces.double().cpu().numpy(),
+                out.stress.double().cpu().numpy() if stress else None)
+
+    def check_status(self) -> None:
+        self.neighbours.check_status()
+        if int(self.status.item()) & _lib.STATUS_NONFINITE:
+            raise _lib.Fmb200Error("the force call produced a non-finite energy")
+
+    def per_atom_energies(self):
+        return self.buf["node_energy"].double().cpu().numpy()
+
+    def buffers(self):
+        out = {f"neighbours.{name}": value for name, value in self.neighbours.buffers().items()}
+        return out
+
+    def info(self):
+        return {"streaming_interactions": self.spec.num_interactions, "sort_receivers": True,
+                "neighbour_rebuilds": self.neighbours.rebuilds, "edge_capacity": self.neighbours.capacity,
+                "engine": "fmb200", "force_calls": self.calls}
+
+
+__all__ = ["B200ForceField", "ForceOutput", "DEFAULT_CHUNK_EDGES"]

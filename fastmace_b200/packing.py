@@ -1,0 +1,157 @@
+"""Packs a MACE model for the device: folds every normalisation constant into the weights, restricts the
+species-dependent tensors to the species that are present, lays the per-irrep linears out as plain [K][N] matrices and
+turns the symmetric contraction into per-(species, channel) polynomial coefficients.
+
+These are the exact algebraic rewrites the reference applies once at set-up ("species tables", 1/sqrt(fan_in) folded
+into W, species skip restricted to present species: ``fastmace/config.py:208-219``,
+``fastmace/rewrites/generic/modules.py:584-593,726-737``); nothing here runs per step.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+
+import numpy as np
+import torch
+
+from . import so3
+from ._lib import MAX_SPECIES, LayerStruct, ModelStruct
+from .codegen import message_slots
+from .model import SILU_NORM, MaceSpec, e0_table
+
+
+def _f64(t: torch.Tensor) -> torch.Tensor:
+    return t.detach().to(torch.float64).cpu()
+
+
+def contraction_terms(spec: MaceSpec, weights, layer: int, species_z):
+    """(terms int32 [T, 4], coef float64 [n_species, T, C]) of one layer's symmetric contraction, sorted by output."""
+    c = spec.channels
+    merged: dict[tuple, np.ndarray] = {}
+    for big_l in range(spec.l_out_max(layer) + 1):
+        for nu in range(1, spec.correlation + 1):
+            mono, m_out, weight, coef, _ = so3.contraction_polynomial(nu, big_l, spec.sh_lmax)
+            w = _f64(weights[f"l{layer}.sc.{big_l}.{nu}"]).numpy()[[z - 1 for z in species_z]]  # [nz, k, C]
+            for t in range(len(coef)):
+                key = (big_l * big_l + int(m_out[t]), nu, tuple(int(i) for i in mono[t]))
+                value = coef[t] * w[:, weight[t], :]
+                if key in merged:
+                    merged[key] = merged[key] + value
+                else:
+                    merged[key] = value
+    keys = sorted(merged)
+    terms = np.full((len(keys), 4), -1, dtype=np.int32)
+    coefs = np.zeros((len(species_z), len(keys), c), dtype=np.float64)
+    for t, key in enumerate(keys):
+        m_out, _, mono = key
+        terms[t, :len(mono)] = mono
+        terms[t, 3] = m_out
+        coefs[:, t, :] = merged[key]
+    return terms, coefs
+
+
+class PackedModel:
+    """Device tensors of a model restricted to ``species_z`` (sorted atomic numbers present) and the ``ModelStruct``
+    the C ABI reads. Keeps the tensors alive for as long as the struct is used."""
+
+    def __init__(self, spec: MaceSpec, weights, species_z, device):
+        species_z = [int(z) for z in species_z]
+        if species_z != sorted(set(species_z)):
+            raise ValueError("species_z must be sorted and unique")
+        if len(species_z) > MAX_SPECIES:
+            raise ValueError(f"at most {MAX_SPECIES} species per structure, got {len(species_z)}")
+        if spec.num_interactions != 2 or spec.channels != 128 or spec.correlation != 3:
+            raise ValueError("the device path takes 2 interactions, 128 channels, correlation 3")
+        self.spec = spec
+        self.species_z = species_z
+        self.device = torch.device(device)
+        self.tensors: dict[str, torch.Tensor] = {}
+        c, n_el = spec.channels, spec.num_elements
+        idx = [z - 1 for z in species_z]
+        w = {k: _f64(v) for k, v in weights.items()}
+        struct = ModelStruct()
+        struct.n_species = len(species_z)
+        struct.channels = c
+        struct.hidden_lmax = spec.hidden_lmax
+        struct.n_layers = spec.num_interactions
+        struct.n_bessel = spec.num_bessel
+        struct.cutoff_p = spec.cutoff_p
+        struct.radial_width = spec.radial_hidden[-1]
+        struct.mlp_hidden = spec.mlp_hidden
+        struct.r_cut = spec.r_cut
+        struct.scale = spec.scale
+        struct.shift = spec.shift
+        struct.silu_norm = SILU_NORM
+        e0 = e0_table(spec)
+        for k, z in enumerate(species_z):
+            struct.e0[k] = float(e0[z - 1])
+        h0 = w["emb"][idx] / math.sqrt(n_el)                                   # [nz, C]
+        for t in range(spec.num_interactions):
+            layer = struct.layer[t]
+            paths = spec.paths(t)
+            slots, blocks = message_slots(paths)
+            layer.l_in_max = spec.l_in_max(t)
+            layer.l_out_max = spec.l_out_max(t)
+            layer.n_paths = len(paths)
+            layer.mid_dim = so3.mid_dim(paths)
+            layer.skip_lmax = spec.skip_lmax(t)
+            layer.is_last = int(t == spec.num_interactions - 1)
+            widths = (spec.num_bessel, *spec.radial_hidden, len(paths) * c)
+            for i in range(4):
+                layer.rad_w[i] = self._put(f"l{t}.rad.{i}", w[f"l{t}.rad.{i}"] / math.sqrt(widths[i]))
+            if t == 0:
+                x_species = h0 @ (w["l0.up.0"] / math.sqrt(c))
+                sc = torch.zeros(len(idx), spec.out_dim(0), c, dtype=torch.float64)
+                skip = w["l0.skip.0"]                                           # [C, 89, C]
+                for k, e in enumerate(idx):
+                    sc[k, 0] = h0[k] @ skip[:, e, :] / math.sqrt(c * n_el)
+                layer.x_species = self._put("l0.x_species", x_species)
+                layer.sc_species = self._put("l0.sc_species", sc)
+            else:
+                up = torch.stack([w[f"l{t}.up.{l}"] / math.sqrt(c) for l in range(spec.l_in_max(t) + 1)])
+                layer.w_up = self._put(f"l{t}.w_up", up)
+                layer.w_up_t = self._put(f"l{t}.w_up_t", up.transpose(1, 2))
+                skip = torch.stack([w[f"l{t}.skip.{l}"][:, idx, :].permute(1, 0, 2) / math.sqrt(c * n_el)
+                                    for l in range(spec.skip_lmax(t) + 1)])     # [L, nz, C, C]
+                layer.w_skip = self._put(f"l{t}.w_skip", skip)
+                layer.w_skip_t = self._put(f"l{t}.w_skip_t", skip.transpose(2, 3))
+            lin, lin_t = [], []
+            for l_out in range(spec.sh_lmax + 1):
+                into = so3.paths_into(paths, l_out)
+                norm = 1.0 / math.sqrt(len(into) * c) / spec.avg_num_neighbors
+                block = torch.cat([w[f"l{t}.lin.{p}"] for p in into], dim=0) * norm   # [n_seg * C, C]
+                lin.append(block.reshape(-1))
+                lin_t.append(block.t().contiguous().reshape(-1))
+            layer.w_lin = self._put(f"l{t}.w_lin", torch.cat(lin))
+            layer.w_lin_t = self._put(f"l{t}.w_lin_t", torch.cat(lin_t))
+            prod = torch.stack([w[f"l{t}.prod.{big_l}"] / math.sqrt(c) for big_l in range(spec.l_out_max(t) + 1)])
+            layer.w_prod = self._put(f"l{t}.w_prod", prod)
+            layer.w_prod_t = self._put(f"l{t}.w_prod_t", prod.transpose(1, 2))
+            terms, coefs = contraction_terms(spec, weights, t, species_z)
+            layer.n_sc_terms = len(terms)
+            layer.sc_terms = self._put(f"l{t}.sc_terms", torch.from_numpy(terms), dtype=torch.int32)
+            layer.sc_coef = self._put(f"l{t}.sc_coef", torch.from_numpy(coefs))
+            if t < spec.num_interactions - 1:
+                layer.w_readout = self._put(f"l{t}.readout", w[f"l{t}.readout"] / math.sqrt(c))
+            else:
+                ro = torch.cat([(w[f"l{t}.readout.0"] / math.sqrt(c)).reshape(-1),
+                                w[f"l{t}.readout.1"] / math.sqrt(spec.mlp_hidden)])
+                layer.w_readout = self._put(f"l{t}.readout", ro)
+        self.struct = struct
+
+    def _put(self, name: str, tensor: torch.Tensor, dtype=torch.float32) -> int:
+        t = tensor.to(dtype).contiguous().to(self.device)
+        self.tensors[name] = t
+        return t.data_ptr()
+
+    def species_index(self, numbers) -> torch.Tensor:
+        """[N] int32 index of each atom's species among the present ones."""
+        lookup = {z: k for k, z in enumerate(self.species_z)}
+        return torch.tensor([lookup[int(z)] for z in numbers], dtype=torch.int32, device=self.device)
+
+    def pointer(self):
+        return ctypes.byref(self.struct)
+
+
+__all__ = ["PackedModel", "contraction_terms"]

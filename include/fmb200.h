@@ -1,0 +1,232 @@
+/* fmb200 -- C ABI of the B200-native MACE force path (sm_100a).
+ *
+ * Every entry point is extern "C", takes plain pointers and sizes, launches on the CUDA stream it is given and
+ * returns an int status (FMB_OK or an FMB_ERR_* code); none throws, none allocates device memory unless its comment
+ * says so: all device buffers belong to the caller (the Python host allocates them as torch tensors and passes
+ * data_ptr()). Device-side failures that cannot be returned synchronously (edge capacity overflow, a neighbour row
+ * longer than the sort buffer) set bits in the caller's `status` word on the device; the host reads it when it
+ * chooses (the reference's "overflow flag checked before commit", fastmace/engine/graph.py:44-56,586-595).
+ *
+ * Each function cites the reference interface it replaces (file:line within the FastMACE tree).
+ */
+#ifndef FMB200_H
+#define FMB200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define FMB_API __attribute__((visibility("default")))
+#else
+#define FMB_API
+#endif
+
+#define FMB_OK 0
+#define FMB_ERR_ARG 1       /* bad argument (null pointer, unsupported size) */
+#define FMB_ERR_CUDA 2      /* a CUDA call failed; fmb_last_error() has the text */
+#define FMB_ERR_UNSUPPORTED 3
+
+/* bits of the device status word */
+#define FMB_STATUS_CAND_OVERFLOW 1u   /* more candidate pairs than `capacity` */
+#define FMB_STATUS_ROW_OVERFLOW 2u    /* one receiver has more candidates than FMB_MAX_ROW */
+#define FMB_STATUS_BIN_OVERFLOW 4u    /* internal: cell-list bins inconsistent */
+#define FMB_STATUS_NONFINITE 8u       /* a non-finite energy was produced */
+
+#define FMB_MAX_ROW 1024              /* candidates per receiver the in-kernel sort can hold */
+#define FMB_MAX_LAYERS 2
+#define FMB_MAX_SPECIES 8
+#define FMB_MAX_PATHS 17
+
+typedef void* fmb_stream_t;           /* a cudaStream_t */
+
+FMB_API int fmb_version(void);
+FMB_API const char* fmb_last_error(void);
+/* sizeof of the structs below, for the host binding to verify its mirror: which = 0 fmb_nl_t, 1 fmb_model_t,
+ * 2 fmb_work_t, 3 fmb_langevin_t */
+FMB_API int fmb_sizeof(int which);
+
+/* ------------------------------------------------------------------------------------------------ neighbour list
+ * Replaces SkinNeighbourList (fastmace/neighbors/skin.py:164-747) with sort_receivers on and no sender groups.
+ * Buffers mirror the reference's names (skin.py:606-621): candidate_index, candidate_unit_shifts, edge_index,
+ * unit_shifts, shifts, count, reference_positions, build_cell; plus CSR row pointers the streaming kernels read. */
+typedef struct {
+    int32_t n_atoms;
+    int32_t capacity;                 /* entries of every per-edge buffer */
+    double cutoff;
+    double skin;
+    double cell[9];                   /* build cell, rows are lattice vectors */
+    double inverse[9];                /* inverse of the cell */
+    int32_t nbins[3];                 /* cell-list bins per axis (fractional slabs at least cutoff+skin thick) */
+    int32_t reach_bins[3];            /* stencil half-width per axis */
+    float pad_unit_shift[3];          /* padding pair: atom 0 and a far image (skin.py:247-252) */
+    int32_t max_bin_atoms;            /* unused by the kernels (bins are walked through bin_start) */
+    /* device buffers */
+    double* wrapped;                  /* [n_atoms, 3] positions wrapped into the cell */
+    double* offsets;                  /* [n_atoms, 3] integer cell of each atom (as double) */
+    int32_t* atom_bin;                /* [n_atoms] */
+    int32_t* bin_count;               /* [total_bins + 1] */
+    int32_t* bin_start;               /* [total_bins + 1] exclusive scan of bin_count */
+    int32_t* bin_fill;                /* [total_bins] */
+    int32_t* bin_atoms;               /* [n_atoms] atoms ordered by bin */
+    int32_t* cand_row_count;          /* [n_atoms + 1] */
+    int32_t* cand_row_ptr;            /* [n_atoms + 1] */
+    int32_t* candidate_index;         /* [2, capacity] row 0 sender, row 1 receiver */
+    float* candidate_unit_shifts;     /* [capacity, 3] */
+    int32_t* edge_row_count;          /* [n_atoms + 1] */
+    int32_t* edge_row_ptr;            /* [n_atoms + 1] CSR over the compacted edges (by receiver) */
+    int32_t* edge_index;              /* [2, capacity] */
+    float* unit_shifts;               /* [capacity, 3] */
+    float* shifts;                    /* [capacity, 3] */
+    int64_t* count;                   /* [1] edges inside the cutoff after compact */
+    int64_t* num_candidates;          /* [1] candidates of the last build */
+    double* reference_positions;      /* [n_atoms, 3] */
+    double* build_cell;               /* [9] */
+    int32_t* scan_scratch;            /* [>= 2 * ceil(max(n_atoms, total_bins) / 4096) + 8] */
+    uint64_t* max_disp2_bits;         /* [1] bit pattern of max |x - x_ref|^2 (non-negative double) */
+    int32_t* rebuild_flag;            /* [1] set by fmb_nl_needs_rebuild */
+    uint32_t* status;                 /* [1] FMB_STATUS_* bits */
+} fmb_nl_t;
+
+/* skin.py:421-497 (build_gpu): candidates within cutoff + skin, float64 decision, ordered by (receiver, sender,
+ * image). If `only_if_flag` is nonzero every kernel returns at once unless *rebuild_flag != 0 (a rebuild inside a
+ * captured step). Writes candidate_*, cand_row_ptr, num_candidates, reference_positions, build_cell. */
+FMB_API int fmb_nl_build(const fmb_nl_t* nl, const double* positions, int only_if_flag, fmb_stream_t stream);
+/* skin.py:702-729 (compact): stable partition, inside-cutoff first; writes edge_index, unit_shifts, shifts, count and
+ * edge_row_ptr. */
+FMB_API int fmb_nl_compact(const fmb_nl_t* nl, const double* positions, fmb_stream_t stream);
+/* skin.py:685-693 (needs_rebuild, fixed cell): rebuild_flag = max_i |x_i - x_ref,i|^2 > (fraction * skin / 2)^2. */
+FMB_API int fmb_nl_needs_rebuild(const fmb_nl_t* nl, const double* positions, double fraction, fmb_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------ model */
+typedef struct {
+    int32_t l_in_max;                 /* node irreps entering the tensor product: 0..l_in_max */
+    int32_t l_out_max;                /* irreps leaving the product block */
+    int32_t n_paths;
+    int32_t mid_dim;                  /* components per channel of the scattered message */
+    int32_t n_sc_terms;               /* polynomial terms of the symmetric contraction */
+    int32_t skip_lmax;
+    int32_t is_last;
+    int32_t pad_;
+    const float* rad_w[4];            /* radial MLP, [in][out], 1/sqrt(fan_in) folded */
+    const float* x_species;           /* layer 0: linear_up(embedding) per species [n_species][C] */
+    const float* sc_species;          /* layer 0: skip connection per species [n_species][out_dim][C] */
+    const float* w_up;                /* [l_in_max+1][C][C], 1/sqrt(C) folded */
+    const float* w_up_t;              /* transposed */
+    const float* w_skip;              /* [skip_lmax+1][n_species][C][C] */
+    const float* w_skip_t;
+    const float* w_lin;               /* per l_out: [K = n_seg*C][C], norm and 1/avg_num_neighbors folded; l blocks
+                                         concatenated in l order */
+    const float* w_lin_t;             /* per l_out: [C][K] */
+    const float* w_prod;              /* [l_out_max+1][C][C] */
+    const float* w_prod_t;
+    const int32_t* sc_terms;          /* [n_sc_terms][4]: i, j, k (unused = -1), m_out */
+    const float* sc_coef;             /* [n_species][n_sc_terms][C] */
+    const float* w_readout;           /* non-last: [C] (scale folded); last: [C][16] then [16] */
+} fmb_layer_t;
+
+typedef struct {
+    int32_t n_species;
+    int32_t channels;                 /* 128 */
+    int32_t hidden_lmax;
+    int32_t n_layers;
+    int32_t n_bessel;                 /* 8 */
+    int32_t cutoff_p;                 /* 5 */
+    int32_t radial_width;             /* 64 */
+    int32_t mlp_hidden;               /* 16 */
+    float r_cut;
+    float scale;
+    float shift;
+    float silu_norm;
+    double e0[FMB_MAX_SPECIES];       /* isolated-atom energies of the present species */
+    fmb_layer_t layer[FMB_MAX_LAYERS];
+} fmb_model_t;
+
+/* Workspace of one force evaluation; every buffer is the caller's. Sizes in floats unless noted. */
+typedef struct {
+    int32_t n_atoms;
+    int32_t edge_capacity;            /* entries of the per-edge buffers */
+    int32_t chunk_edges;              /* edges whose tensor-product weights are resident at once */
+    int32_t compute_stress;
+    const int32_t* species;           /* [n_atoms] index into the present species */
+    float* edge_vec;                  /* [edge_capacity][4] unit vector and length */
+    float* edge_sh;                   /* [edge_capacity][16] */
+    float* edge_hidden;               /* [n_layers][2][edge_capacity][64]: last hidden layer and its d/dr */
+    float* tp_w;                      /* [2 * chunk_edges][max_paths * C]: weights, then their d/dr */
+    float* x;                         /* [n_atoms][in_dim(1)][C] linear_up output of layer 1 */
+    float* mid;                       /* [n_atoms][max mid_dim][C] scattered message (reused by both layers) */
+    float* msg;                       /* [n_layers][n_atoms][16][C] */
+    float* basis;                     /* [n_atoms][max out_dim][C] symmetric contraction output */
+    float* h;                         /* [n_layers][n_atoms][out_dim][C] node features after each layer */
+    float* d_h;                       /* [n_atoms][hidden_dim][C] gradient of h1 (and scratch for h2's) */
+    float* d_basis;                   /* [n_atoms][max out_dim][C] */
+    float* d_msg;                     /* [n_atoms][16][C] */
+    float* d_mid;                     /* [n_atoms][max mid_dim][C] */
+    float* d_x;                       /* [n_atoms][in_dim(1)][C] */
+    float* node_energy;               /* [n_atoms] */
+    float* atom_virial;               /* [n_atoms][6] */
+    float* force_acc;                 /* [n_atoms][3] */
+    double* partial;                  /* [>= 1024 * 8] block partial sums */
+    /* outputs */
+    double* energy;                   /* [1] */
+    float* forces;                    /* [n_atoms][3] */
+    float* stress;                    /* [9] */
+    uint32_t* status;                 /* [1] */
+} fmb_work_t;
+
+/* MACEForceField.__call__ (fastmace/model/forces.py:1127-1136,1220-1240): energy (float64), forces and stress of the
+ * compacted edges in `nl` at float64 `positions`; analytic backward instead of autograd
+ * (fastmace/rewrites/engine.py:122-192 for the definitions). Graph-capturable: no host synchronisation, reads the
+ * edge count from the device. */
+FMB_API int fmb_forces(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, const double* positions,
+               fmb_stream_t stream);
+
+/* Individual stages, exported for kernel-level parity tests (same arguments as inside fmb_forces). */
+FMB_API int fmb_edge_features(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, const double* positions,
+                      fmb_stream_t stream);
+FMB_API int fmb_forward(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, fmb_stream_t stream);
+FMB_API int fmb_backward(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, fmb_stream_t stream);
+
+/* C[M, N] = A[M, K] B[K, N] in fp32 (rows of A and C addressed as batch/row strides); exported for tests.
+ * impl 0: SIMT FMA kernel; impl 1: tcgen05 3xTF32 kernel (K, N multiples of 64; falls back to an error otherwise). */
+FMB_API int fmb_gemm(const float* a, const float* b, float* c, int m, int n, int k, int accumulate, int impl,
+             fmb_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------ Langevin
+ * Replaces Langevin.first_half / second_half (fastmace/integrators/langevin.py:233-263) and the fused stage
+ * (fastmace/kernels/triton/fused_integrator.py:47-133). All float64. */
+typedef struct {
+    int32_t n_atoms;
+    int32_t fix_com;                  /* 0 off, 1 ASE projection, 2 mass-weighted projection */
+    double dt;
+    double c1;
+    double c2;
+    double* positions;                /* [n_atoms, 3] */
+    double* velocities;
+    const double* forces;
+    const double* masses;             /* [n_atoms] */
+    const double* c3_unit;            /* [n_atoms] */
+    const double* c4_unit;
+    const double* c5_unit;
+    const double* sqrt_kT;            /* [1] */
+    const double* noise;              /* [steps, 2, n_atoms, 3] drawn-ahead batch: xi then eta */
+    const int32_t* noise_cursor;      /* [1] row of `noise` this step reads (device counter) */
+    double* x_old;
+    double* rnd_pos;
+    double* rnd_vel;
+    double* partial;                  /* [>= 1024 * 8] */
+    int32_t* noise_cursor_rw;         /* same address as noise_cursor; incremented by the second half */
+} fmb_langevin_t;
+
+FMB_API int fmb_langevin_first_half(const fmb_langevin_t* lv, fmb_stream_t stream);
+FMB_API int fmb_langevin_second_half(const fmb_langevin_t* lv, fmb_stream_t stream);
+/* state.forces/energy/stress <- ForceOutput (fastmace/engine/graph.py:1125-1131): fp32 -> float64 copies. */
+FMB_API int fmb_commit_forces(const fmb_work_t* work, double* forces64, double* energy64, double* stress64,
+                      fmb_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,155 @@
+"""Energy / forces / stress of the CUDA path against the CPU oracle, through the C ABI (B200ForceField)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import mace_oracle as mo
+from oracle import neighbours_oracle as nlo
+
+pytestmark = pytest.mark.gpu
+
+# north-star tolerances: energy per atom, force component, stress component
+TOL_E, TOL_F, TOL_S = 1e-5, 1e-4, 1e-6
+
+
+def _case(name):
+    from fastmace_b200.model import LARGE, MEDIUM, SMALL, init_weights
+    from fastmace_b200.structures import fcc_alloy, nacl
+    if name == "small":
+        return SMALL, init_weights(SMALL, 0), nacl((2, 2, 2), 0.05, 0)
+    if name == "medium":
+        return MEDIUM, init_weights(MEDIUM, 1), nacl((2, 2, 2), 0.05, 1)
+    if name == "medium216":
+        return MEDIUM, init_weights(MEDIUM, 1), nacl((3, 3, 3), 0.05, 1)
+    if name == "large":
+        import dataclasses
+        spec = dataclasses.replace(LARGE, avg_num_neighbors=54.0)
+        return spec, init_weights(spec, 2), fcc_alloy((4, 4, 4), 0.1, 2)
+    raise KeyError(name)
+
+
+def _oracle(spec, weights, s, dtype=torch.float64, keep=None):
+    snd, rcv, u = nlo.build(s.positions, s.cell, spec.r_cut, 0.0)
+    return mo.evaluate(spec, weights, s.positions, s.cell, s.numbers, snd, rcv, u, dtype=dtype, keep=keep)
+
+
+def _report(name, e, f, st, e_ref, f_ref, s_ref, natoms):
+    de = abs(e - float(e_ref)) / natoms
+    df = np.abs(f - f_ref.numpy()).max()
+    ds = np.abs(st - s_ref.numpy()).max()
+    fscale = np.abs(f_ref.numpy()).max()
+    print(f"{name}: |dE|/atom {de:.3e}  max|dF| {df:.3e} (max|F| {fscale:.3e})  max|dS| {ds:.3e}")
+    return de, df, ds, fscale
+
+
+@pytest.mark.parametrize("name", ["small", "medium", "large"])
+def test_energy_forces_stress_against_oracle(name):
+    from fastmace_b200.forcefield import B200ForceField
+    spec, weights, s = _case(name)
+    ff = B200ForceField(spec, weights, s.numbers, s.cell, compute_stress=True)
+    e, f, st = ff.evaluate(s, stress=True)
+    e_ref, f_ref, s_ref = _oracle(spec, weights, s)
+    de, df, ds, fscale = _report(name, e, f, st, e_ref, f_ref, s_ref, s.natoms)
+    assert de <= TOL_E and df <= TOL_F and ds <= TOL_S
+    # the random-init models give small forces, so also hold a relative bound (fp32 rounding, not a wrong term)
+    assert df <= 2e-4 * fscale + 1e-7
+    assert ds <= 2e-4 * np.abs(s_ref.numpy()).max() + 1e-9
+    assert abs(e - float(e_ref)) <= 2e-5 * abs(float(e_ref)) + 1e-6
+
+
+def test_stage_intermediates_against_oracle():
+    """Each stage of the forward pass against the oracle's tensors (fp32 oracle), to localise a wrong kernel."""
+    from fastmace_b200 import so3
+    from fastmace_b200.codegen import message_slots
+    from fastmace_b200.forcefield import B200ForceField
+    spec, weights, s = _case("medium")
+    keep = {}
+    _oracle(spec, weights, s, dtype=torch.float64, keep=keep)
+    ff = B200ForceField(spec, weights, s.numbers, s.cell, compute_stress=True)
+    ff.evaluate(s, stress=True)
+    nl = ff.neighbours
+    count = int(nl.count.item())
+    ei = nl.edge_index.cpu().numpy()[:, :count]
+    # the oracle's edges are sorted the same way (receiver, sender, image) at skin 0 -> same order as compacted
+    snd, rcv, u = nlo.build(s.positions, s.cell, spec.r_cut, 0.0)
+    assert count == len(snd) and np.array_equal(ei[0], snd) and np.array_equal(ei[1], rcv)
+
+    def close(a, b, what, rtol=2e-5):
+        a, b = np.asarray(a, dtype=np.float64), np.asarray(b, dtype=np.float64)
+        scale = np.abs(b).max() + 1e-30
+        err = np.abs(a - b).max() / scale
+        print(f"{what}: rel err {err:.2e} (scale {scale:.2e})")
+        assert err < rtol, what
+
+    vec = ff.buf["edge_vec"].cpu().numpy()[:count]
+    close(vec[:, :3] * vec[:, 3:4], keep["vectors"].numpy(), "edge vectors")
+    close(ff.buf["edge_sh"].cpu().numpy()[:count], keep["sh"].numpy(), "spherical harmonics")
+    n, c = s.natoms, spec.channels
+    hid = (spec.hidden_lmax + 1) ** 2
+    for t in range(2):
+        close(ff.buf["msg"][t].cpu().numpy(), keep[f"l{t}.message"].numpy(), f"layer {t} message")
+    h = ff.buf["h"].cpu().numpy()
+    close(h[:n * hid].reshape(n, hid, c), keep["l0.h"].numpy(), "layer 0 features")
+    close(h[n * hid:].reshape(n, 1, c), keep["l1.h"].numpy(), "layer 1 features")
+    close(ff.buf["x"].cpu().numpy(), keep["l1.x"].numpy(), "layer 1 linear_up")
+    # the scattered message of the last layer is still in `mid` ... overwritten by the backward? no: d_mid is separate
+    paths = spec.paths(1)
+    slots, _ = message_slots(paths)
+    mid = ff.buf["mid"].cpu().numpy()
+    ref = keep["l1.mid"].numpy()
+    perm = np.zeros(so3.mid_dim(paths), dtype=np.int64)
+    for p, path in enumerate(paths):
+        for m in range(2 * path["l_out"] + 1):
+            perm[path["out_off"] + m] = slots[(p, m)]
+    close(mid[:, perm, :], ref, "layer 1 scattered message")
+    close(ff.buf["node_energy"].cpu().numpy(), keep["node_energy"].numpy(), "node energies")
+
+
+def test_chunked_edges_give_the_same_result():
+    from fastmace_b200.forcefield import B200ForceField
+    spec, weights, s = _case("medium")
+    whole = B200ForceField(spec, weights, s.numbers, s.cell, compute_stress=True)
+    e0, f0, s0 = whole.evaluate(s, stress=True)
+    chunked = B200ForceField(spec, weights, s.numbers, s.cell, compute_stress=True, chunk_edges=300)
+    e1, f1, s1 = chunked.evaluate(s, stress=True)
+    assert abs(e0 - e1) <= 1e-9 * max(1.0, abs(e0))
+    assert np.abs(f0 - f1).max() <= 1e-7 and np.abs(s0 - s1).max() <= 1e-9
+
+
+def test_repeat_calls_are_bitwise_identical():
+    from fastmace_b200.forcefield import B200ForceField
+    spec, weights, s = _case("medium")
+    ff = B200ForceField(spec, weights, s.numbers, s.cell, compute_stress=True)
+    x = torch.tensor(s.positions, device="cuda")
+    ff.rebuild(x); ff.compact(x); ff.use_edges(int(ff.edge_count))
+    a = ff(x)
+    e0, f0, s0 = a.energy.clone(), a.forces.clone(), a.stress.clone()
+    b = ff(x)
+    assert torch.equal(e0, b.energy) and torch.equal(f0, b.forces) and torch.equal(s0, b.stress)
+
+
+def test_medium_216_atoms():
+    from fastmace_b200.forcefield import B200ForceField
+    spec, weights, s = _case("medium216")
+    ff = B200ForceField(spec, weights, s.numbers, s.cell, compute_stress=True)
+    e, f, st = ff.evaluate(s, stress=True)
+    e_ref, f_ref, s_ref = _oracle(spec, weights, s, dtype=torch.float32)
+    de, df, ds, fscale = _report("medium216 vs fp32 oracle", e, f, st, e_ref, f_ref, s_ref, s.natoms)
+    assert de <= TOL_E and df <= TOL_F and ds <= TOL_S
+    assert df <= 5e-4 * fscale + 1e-7
+
+
+def test_gemm_simt_against_torch():
+    import ctypes
+    from fastmace_b200 import _lib
+    lib = _lib.load()
+    torch.manual_seed(0)
+    for m, n, k in [(1000, 128, 128), (257, 256, 64), (4096, 1280, 64), (77, 128, 384)]:
+        a = torch.randn(m, k, device="cuda")
+        b = torch.randn(k, n, device="cuda")
+        c = torch.zeros(m, n, device="cuda")
+        _lib.check(lib.fmb_gemm(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, 0, 0, _lib.current_stream()), "gemm")
+        ref = (a.double() @ b.double()).float()
+        assert (c - ref).abs().max().item() <= 1e-4 * ref.abs().max().item()
+        _lib.check(lib.fmb_gemm(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, 1, 0, _lib.current_stream()), "gemm")
+        assert (c - 2 * ref).abs().max().item() <= 2e-4 * ref.abs().max().item()

@@ -1,0 +1,324 @@
+"""Benchmark of the MD hot path: atom-steps/s of Langevin NVT steps (neighbour check + compaction + energy, forces and
+stress + both half kicks) of the random-initialised MACE "medium" model on 1,944-atom NaCl.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Prints ONE JSON line. ``value`` is the throughput of captured whole-step graphs with the noise already resident on
+the device (timed with CUDA events on the replay stream); ``e2e`` is the same metric through the public API
+(``B200Engine.step``) with the noise drawn on the host and uploaded from pinned memory and a device-to-host read of
+the step's energy inside the timed region. ``roofline`` describes the stage with the largest share of the force call,
+timed with CUDA events in an eager pass; ``cpu_baseline`` times the CPU oracle on the box's host cores on a bounded
+sample. ``--impl reference`` times that CPU path alone (the third-party model the reference calls is not
+installable here, so the CPU arm is the oracle port).
+
+With N > 1 (launched under torch.distributed.run) every rank steps its own replica of the workload and the value is
+the aggregate (weak scaling, no data-path collective).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np
+import torch
+
+WORKLOADS = {
+    # name: (model, structure builder args, temperature, avg_num_neighbors)
+    "medium_nacl_1944_langevin": dict(model="medium", seed=1, repeat=(9, 9, 3), sigma=0.05, temperature=300.0),
+    "small_nacl_216_langevin": dict(model="small", seed=0, repeat=(3, 3, 3), sigma=0.05, temperature=300.0),
+}
+DEFAULT_WORKLOAD = "medium_nacl_1944_langevin"
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as handle:
+            p = json.load(handle)
+        return dict(hbm_gbs=float(p["hbm_gbs"]), bf16_tflops=float(p["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, sm_max, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for row in self.rows:
+            try:
+                sm.append(float(row[1]))
+                sm_max = float(row[2])
+            except (ValueError, IndexError):
+                continue
+            for name, cell in zip(names, row[5:9]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=sm_max, reasons=sorted(reasons),
+                    samples=len(sm))
+
+
+def build_problem(workload: str, device):
+    import dataclasses
+
+    from fastmace_b200.engine import B200Engine
+    from fastmace_b200.forcefield import B200ForceField
+    from fastmace_b200.langevin import IntegratorConfig, Langevin
+    from fastmace_b200.model import SPECS, init_weights
+    from fastmace_b200.state import SimulationState
+    from fastmace_b200.structures import nacl
+
+    w = WORKLOADS[workload]
+    spec = dataclasses.replace(SPECS[w["model"]], avg_num_neighbors=32.0)
+    weights = init_weights(spec, w["seed"])
+    structure = nacl(w["repeat"], w["sigma"], w["seed"]).with_velocities(w["temperature"], w["seed"] + 100)
+    ff = B200ForceField(spec, weights, structure.numbers, structure.cell, compute_stress=True, device=device)
+    state = SimulationState.from_structure(structure, ff.device, seed=w["seed"], compute_stress=True)
+    integrator = Langevin(state, IntegratorConfig(timestep_fs=1.0), temperature_K=w["temperature"])
+    engine = B200Engine(ff, integrator, state, mode="graph", check_every=0)
+    return spec, weights, structure, ff, state, integrator, engine
+
+
+def stage_bytes(spec, n_atoms: int, n_edges: int) -> dict:
+    """Algorithmic (compulsory) bytes per force call of each timed stage: every operand read or written once."""
+    c = spec.channels
+    out = {}
+    hid = (spec.hidden_lmax + 1) ** 2
+    p0, p1 = len(spec.paths(0)), len(spec.paths(1))
+    from fastmace_b200 import so3
+    m0, m1 = so3.mid_dim(spec.paths(0)), so3.mid_dim(spec.paths(1))
+    out["edge_features"] = n_edges * (4 + 12 + 16 + 64 + 2 * 2 * 64 * 4) + n_atoms * 24
+    # forward: w of both layers; backward: w and dw/dr of both layers; each row reads 64 hidden values
+    out["radial_gemm"] = n_edges * ((p0 + p1) * c * 4 * 3 + 6 * 64 * 4)
+    out["tp_forward_l0"] = n_edges * (p0 * c * 4 + 64 + 4) + n_atoms * m0 * c * 4
+    out["tp_forward_l1"] = n_edges * (p1 * c * 4 + 64 + 4) + n_atoms * (m1 + hid) * c * 4
+    out["tp_backward_l0"] = n_edges * (2 * p0 * c * 4 + 64 + 16 + 4) + n_atoms * (m0 * c * 4 + 36)
+    out["tp_backward_l1"] = n_edges * (2 * p1 * c * 4 + 64 + 16 + 4) + n_atoms * ((m1 + 2 * hid) * c * 4 + 36)
+    return out
+
+
+def cpu_oracle_sample(repeats: int = 2):
+    """One energy + forces + stress evaluation of the CPU oracle (fp32, all host threads) on the 216-atom NaCl cell of
+    the medium model; per-atom cost does not depend on the cell size. Returns (atom-steps/s, threads, description)."""
+    import dataclasses
+
+    from fastmace_b200.model import MEDIUM, init_weights
+    from fastmace_b200.structures import nacl
+    from oracle import mace_oracle, neighbours_oracle
+
+    spec = dataclasses.replace(MEDIUM, avg_num_neighbors=32.0)
+    weights = init_weights(spec, 1)
+    s = nacl((3, 3, 3), 0.05, 1)
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    times = []
+    for k in range(repeats + 1):
+        t0 = time.perf_counter()
+        snd, rcv, u = neighbours_oracle.build(s.positions, s.cell, spec.r_cut, 0.0)
+        mace_oracle.evaluate(spec, weights, s.positions, s.cell, s.numbers, snd, rcv, u, dtype=torch.float32)
+        if k:                       # the first call builds the coupling tables
+            times.append(time.perf_counter() - t0)
+    seconds = statistics.median(times)
+    return s.natoms / seconds, threads, (f"{len(times)} energy+forces+stress evaluations of the fp32 CPU oracle on "
+                                         f"216-atom NaCl, medium model, median {seconds:.2f} s each")
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    value, threads, sample = cpu_oracle_sample(max(1, min(args.steps, 3)))
+    line = dict(metric="md_atom_steps_per_s", value=value, unit="atom-steps/s", n_gpus=args.gpus, steps=args.steps,
+                warmup=args.warmup, ms_per_step=1e3 * 1944 / value, higher_is_better=True, scaling="weak",
+                vs_baseline=None, dtype="f32", data="synthetic", impl="reference",
+                config=dict(workload=args.workload, note="CPU oracle port of the force call; the third-party model the "
+                            "reference evaluates (mace-torch) cannot be installed here"),
+                cpu_baseline=dict(value=value, unit="atom-steps/s", cores=threads, kind="port", sample=sample),
+                e2e=dict(value=value, unit="atom-steps/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line))
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=1000)
+    parser.add_argument("--warmup", type=int, default=100)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    from fastmace_b200 import _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise _lib.Fmb200Error("bench.py needs a CUDA device (there is no CPU path for the product)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    lib = _lib.load()
+
+    spec, weights, structure, ff, state, integrator, engine = build_problem(args.workload, device)
+    n_atoms = structure.natoms
+    warmup = max(3, args.warmup)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---------------------------------------------------------------- device-resident throughput (value)
+    launches_before = lib.fmb_launch_count()
+    engine.run(1)                      # captures the step graph
+    launches_per_step = None
+    for _ in range(warmup - 1):
+        engine.step()
+    engine.flush()
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    total_ms, done = 0.0, 0
+    block = integrator.noise_batch
+    while done < args.steps:
+        todo = min(block, args.steps - done)
+        # refill the drawn-ahead noise outside the timed region: `value` has its inputs resident in HBM
+        integrator.refill(state)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(todo):
+            engine.graph.replay()
+        stop.record()
+        stop.synchronize()
+        total_ms += start.elapsed_time(stop)
+        state.rng.cursor = integrator.noise_batch   # used up as far as the host is concerned
+        done += todo
+    clocks = sampler.stop()
+    engine.flush()
+    if world > 1:
+        t = torch.tensor([total_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    value = world * n_atoms * args.steps / (total_ms * 1e-3)
+
+    # ---------------------------------------------------------------- end to end through the public API (e2e)
+    pinned = torch.zeros(args.steps, dtype=torch.float64).pin_memory()
+    state.rng.cursor = integrator.noise_batch
+    barrier()
+    t0 = time.perf_counter()
+    start.record()
+    for k in range(args.steps):
+        engine.step()                                   # host noise draw + upload when the batch runs out
+        pinned[k:k + 1].copy_(state.energy, non_blocking=True)
+    stop.record()
+    stop.synchronize()
+    e2e_ms = start.elapsed_time(stop)
+    engine.flush()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    e2e_ms = max(e2e_ms, wall_ms)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = world * n_atoms * args.steps / (e2e_ms * 1e-3)
+    assert bool(torch.isfinite(pinned).all()), "non-finite energies in the end-to-end run"
+
+    # ---------------------------------------------------------------- launches per step and per-stage timing
+    before = lib.fmb_launch_count()
+    engine._device_step()
+    torch.cuda.synchronize()
+    launches_per_step = int(lib.fmb_launch_count() - before)
+    n_edges = int(ff.edge_count.item())
+    lib.fmb_profile_enable(1)
+    profile_calls = 20
+    for _ in range(3):
+        ff(state.positions)
+    _lib.profile_read()
+    for _ in range(profile_calls):
+        ff(state.positions)
+    stages = _lib.profile_read()
+    lib.fmb_profile_enable(0)
+    stage_ms = {k: v[0] / profile_calls for k, v in stages.items()}
+    force_ms = sum(stage_ms.values())
+    algo = stage_bytes(spec, n_atoms, n_edges)
+    top = max((k for k in stage_ms if k in algo), key=lambda k: stage_ms[k])
+    pk = peaks()
+    achieved = algo[top] / (stage_ms[top] * 1e-3) / 1e9
+    roofline = dict(bound="hbm", kernel=top, achieved=achieved, peak=pk["hbm_gbs"], unit="GB/s",
+                    frac=achieved / pk["hbm_gbs"], traffic=None, peak_source=pk["source"],
+                    ms_per_launch=stage_ms[top] / max(1, stages[top][1] // profile_calls),
+                    algorithmic_bytes=algo[top], share_of_force_call=stage_ms[top] / force_ms,
+                    stage_ms={k: round(v, 5) for k, v in stage_ms.items()})
+
+    line = dict(metric="md_atom_steps_per_s", value=value, unit="atom-steps/s", n_gpus=world, steps=args.steps,
+                warmup=warmup, ms_per_step=ms_per_step, us_per_step=1e3 * ms_per_step, higher_is_better=True,
+                scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
+                config=dict(workload=args.workload, atoms=n_atoms, edges=n_edges, model=WORKLOADS[args.workload]["model"],
+                            integrator="langevin_nvt_1fs_0.01perfs", parallelism=f"replicas{world}" if world > 1 else "1gpu",
+                            l2="per-step working set (radial weight tensors, > 600 MB) exceeds the 126 MB L2; no flush",
+                            neighbour_rebuilds=ff.neighbours.rebuilds),
+                clocks=clocks,
+                e2e=dict(value=e2e_value, unit="atom-steps/s", h2d_bytes_per_step=2 * n_atoms * 3 * 8,
+                         d2h_bytes_per_step=8, ms_per_step=e2e_ms / args.steps),
+                gpu_launches=launches_per_step * args.steps, launches_per_step=launches_per_step,
+                roofline=roofline)
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu_value, threads, sample = cpu_oracle_sample(2)
+        line["cpu_baseline"] = dict(value=cpu_value, unit="atom-steps/s", cores=threads, kind="port", sample=sample)
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -22,9 +22,9 @@ STATUS_ROW_OVERFLOW = 2
 STATUS_BIN_OVERFLOW = 4
 STATUS_NONFINITE = 8
 
-EXPORTS = ("fmb_version", "fmb_last_error", "fmb_sizeof", "fmb_nl_build", "fmb_nl_compact", "fmb_nl_needs_rebuild",
+EXPORTS = ("fmb_version", "fmb_last_error", "fmb_sizeof", "fmb_launch_count", "fmb_nl_build", "fmb_nl_compact", "fmb_nl_needs_rebuild",
            "fmb_forces", "fmb_edge_features", "fmb_forward", "fmb_backward", "fmb_gemm", "fmb_langevin_first_half",
-           "fmb_langevin_second_half", "fmb_commit_forces")
+           "fmb_langevin_second_half", "fmb_commit_forces", "fmb_profile_enable", "fmb_profile_read")
 
 
 class Fmb200Error(RuntimeError):
@@ -87,6 +87,9 @@ class LangevinStruct(ctypes.Structure):
     ]
 
 
+STAGES = ("edge_features", "radial_gemm", "tp_forward_l0", "tp_forward_l1", "node_linears", "symcon_forward",
+          "symcon_backward", "tp_backward_l1", "tp_backward_l0", "readout_reduce")
+
 _LIB = None
 
 
@@ -101,6 +104,7 @@ def load() -> ctypes.CDLL:
     lib = ctypes.CDLL(LIB_PATH)
     lib.fmb_last_error.restype = c_char_p
     lib.fmb_sizeof.argtypes = [c_int]
+    lib.fmb_launch_count.restype = ctypes.c_longlong
     for which, struct in enumerate((NlStruct, ModelStruct, WorkStruct, LangevinStruct)):
         if lib.fmb_sizeof(which) != ctypes.sizeof(struct):
             raise Fmb200Error(f"struct {struct.__name__} is {ctypes.sizeof(struct)} bytes here, "
@@ -117,6 +121,8 @@ def load() -> ctypes.CDLL:
     lib.fmb_langevin_first_half.argtypes = [POINTER(LangevinStruct), P]
     lib.fmb_langevin_second_half.argtypes = [POINTER(LangevinStruct), P]
     lib.fmb_commit_forces.argtypes = [POINTER(WorkStruct), P, P, P, P]
+    lib.fmb_profile_enable.argtypes = [c_int]
+    lib.fmb_profile_read.argtypes = [POINTER(c_float), POINTER(c_int), c_int]
     _LIB = lib
     return lib
 
@@ -125,6 +131,17 @@ def check(status: int, what: str) -> None:
     if status != 0:
         text = load().fmb_last_error()
         raise Fmb200Error(f"{what} failed with status {status}: {text.decode() if text else ''}")
+
+
+def profile_read() -> dict:
+    """{stage: (milliseconds, spans)} accumulated since the last read (needs fmb_profile_enable(1))."""
+    lib = load()
+    ms = (c_float * len(STAGES))()
+    spans = (c_int * len(STAGES))()
+    n = lib.fmb_profile_read(ms, spans, len(STAGES))
+    if n != len(STAGES):
+        raise Fmb200Error(f"fmb_profile_read returned {n}")
+    return {name: (float(ms[k]), int(spans[k])) for k, name in enumerate(STAGES)}
 
 
 def current_stream() -> int:

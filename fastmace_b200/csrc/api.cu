@@ -2,6 +2,7 @@
 
 #include "fmb_common.cuh"
 
+#include <atomic>
 #include <mutex>
 #include <string>
 
@@ -10,7 +11,10 @@ namespace fmb {
 namespace {
 std::mutex g_mutex;
 std::string g_error;
+std::atomic<long long> g_launches{0};
 }  // namespace
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 void set_error(const char* what, cudaError_t err, const char* file, int line) {
     std::lock_guard<std::mutex> lock(g_mutex);
@@ -42,3 +46,5 @@ extern "C" FMB_API int fmb_sizeof(int which) {
         default: return -1;
     }
 }
+
+extern "C" FMB_API long long fmb_launch_count(void) { return fmb::g_launches.load(); }

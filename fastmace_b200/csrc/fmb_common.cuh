@@ -10,6 +10,7 @@
 namespace fmb {
 
 void set_error(const char* what, cudaError_t err, const char* file, int line);
+void count_launch();
 void set_error_text(const char* text);
 
 #define FMB_CUDA_CHECK(expr)                                            \
@@ -21,7 +22,11 @@ void set_error_text(const char* text);
         }                                                               \
     } while (0)
 
-#define FMB_LAUNCH_CHECK() FMB_CUDA_CHECK(cudaGetLastError())
+#define FMB_LAUNCH_CHECK()                  \
+    do {                                    \
+        ::fmb::count_launch();              \
+        FMB_CUDA_CHECK(cudaGetLastError()); \
+    } while (0)
 
 #define FMB_REQUIRE(cond, text)                  \
     do {                                         \

@@ -10,10 +10,43 @@
 #include "stages.cuh"
 
 #include <cmath>
+#include <vector>
 
 namespace fmb {
 
 namespace {
+
+// Optional per-stage CUDA-event timing of eager (not captured) calls, for the benchmark's roofline figures.
+enum Stage { kStEdge = 0, kStRadial, kStTpFwd0, kStTpFwd1, kStLinear, kStSymFwd, kStSymBwd, kStTpBwd1, kStTpBwd0,
+             kStReadout, kStages };
+
+struct StageTimer {
+    bool on = false;
+    struct Span { int stage; cudaEvent_t a, b; };
+    std::vector<Span> spans;
+    std::vector<cudaEvent_t> pool;
+    cudaEvent_t event() {
+        if (!pool.empty()) { cudaEvent_t e = pool.back(); pool.pop_back(); return e; }
+        cudaEvent_t e;
+        cudaEventCreate(&e);
+        return e;
+    }
+} g_timer;
+
+struct StageScope {
+    cudaStream_t stream;
+    cudaEvent_t b = nullptr;
+    StageScope(cudaStream_t s, int stage) : stream(s) {
+        if (!g_timer.on) return;
+        cudaEvent_t a = g_timer.event();
+        b = g_timer.event();
+        cudaEventRecord(a, stream);
+        g_timer.spans.push_back({stage, a, b});
+    }
+    ~StageScope() {
+        if (b) cudaEventRecord(b, stream);
+    }
+};
 
 inline int dim_of(int lmax) { return (lmax + 1) * (lmax + 1); }
 
@@ -65,6 +98,7 @@ const float* hidden_of(const Ctx& c, int layer, int tangent) {
 int radial_weights(const Ctx& c, int layer, long long e0, bool with_tangent) {
     const fmb_layer_t& L = c.m->layer[layer];
     const long long rows = std::min<long long>(c.chunk, c.count_cap - e0);
+    StageScope scope(c.stream, kStRadial);
     for (int tangent = 0; tangent < (with_tangent ? 2 : 1); ++tangent) {
         GemmArgs g;
         g.a = hidden_of(c, layer, tangent) + e0 * kRadial;
@@ -87,6 +121,7 @@ int radial_weights(const Ctx& c, int layer, long long e0, bool with_tangent) {
 int block_linear(const Ctx& c, const float* in, long long in_atom, long long in_off, int k, const float* weight,
                  float* out, long long out_atom, long long out_off, int n_out, int l, int accumulate,
                  const int32_t* batch_species = nullptr, int select = -1) {
+    StageScope scope(c.stream, kStLinear);
     GemmArgs g;
     const int nm = 2 * l + 1;
     g.a = in + in_off;
@@ -146,13 +181,18 @@ int forward_layer(const Ctx& c, int layer) {
         t.chunk_e0 = e0; t.chunk_edges = c.chunk;
         t.count = (const long long*)c.nl->count; t.row_ptr = c.nl->edge_row_ptr; t.senders = c.nl->edge_index;
         t.species = c.w->species; t.x = x; t.edge_sh = c.w->edge_sh; t.tp_w = c.w->tp_w; t.mid = c.w->mid;
+        StageScope scope(c.stream, layer == 0 ? kStTpFwd0 : kStTpFwd1);
         FMB_TRY(tp_forward_launch(t, c.stream));
     }
     float* msg = msg_of(c, layer);
     for (int l = 0; l <= 3; ++l)
         FMB_TRY(block_linear(c, c.w->mid, (long long)ml.mid_dim * kC, (long long)ml.base[l] * kC, ml.segs[l] * kC,
                              L.w_lin + lin_weight_offset(ml, l), msg, (long long)kNSH * kC, (long long)l * l * kC, kC, l, 0));
-    FMB_TRY(symcon_forward(c.n, L.n_sc_terms, out_dim, L.sc_terms, L.sc_coef, c.w->species, msg, c.w->basis, c.stream));
+    {
+        StageScope scope(c.stream, kStSymFwd);
+        FMB_TRY(symcon_forward(c.n, L.n_sc_terms, out_dim, L.sc_terms, L.sc_coef, c.w->species, msg, c.w->basis,
+                               c.stream));
+    }
     for (int l = 0; l <= L.l_out_max; ++l)
         FMB_TRY(block_linear(c, c.w->basis, (long long)out_dim * kC, (long long)l * l * kC, kC,
                              L.w_prod + (long long)l * kC * kC, h_out, (long long)out_dim * kC, (long long)l * l * kC,
@@ -177,8 +217,11 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
                                      L.w_skip_t + ((long long)l * c.m->n_species + z) * kC * kC, d_h_in,
                                      (long long)c.hidden_dim * kC, (long long)l * l * kC, kC, l, 1, c.w->species, z));
     }
-    FMB_TRY(symcon_backward(c.n, L.n_sc_terms, out_dim, L.sc_terms, L.sc_coef, c.w->species, msg_of(c, layer),
-                            c.w->d_basis, c.w->d_msg, c.stream));
+    {
+        StageScope scope(c.stream, kStSymBwd);
+        FMB_TRY(symcon_backward(c.n, L.n_sc_terms, out_dim, L.sc_terms, L.sc_coef, c.w->species, msg_of(c, layer),
+                                c.w->d_basis, c.w->d_msg, c.stream));
+    }
     for (int l = 0; l <= 3; ++l)
         FMB_TRY(block_linear(c, c.w->d_msg, (long long)kNSH * kC, (long long)l * l * kC, kC,
                              L.w_lin_t + lin_weight_offset(ml, l), c.w->d_mid, (long long)ml.mid_dim * kC,
@@ -194,6 +237,7 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
         t.edge_sh = c.w->edge_sh; t.edge_vec = c.w->edge_vec; t.tp_w = c.w->tp_w;
         t.d_mid = c.w->d_mid; t.d_x = c.w->d_x; t.force_acc = c.w->force_acc; t.atom_virial = c.w->atom_virial;
         t.first_layer_of_pass = first_layer_of_pass;
+        StageScope scope(c.stream, layer == 0 ? kStTpBwd0 : kStTpBwd1);
         FMB_TRY(tp_backward_launch(t, c.stream));
     }
     if (layer > 0) {
@@ -237,6 +281,7 @@ using namespace fmb;
 extern "C" FMB_API int fmb_edge_features(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work,
                                  const double* positions, fmb_stream_t stream) {
     FMB_REQUIRE(model && nl && work && positions, "fmb_edge_features: null argument");
+    StageScope scope((cudaStream_t)stream, kStEdge);
     return edge_features(model, nl, work, positions, (cudaStream_t)stream);
 }
 
@@ -246,6 +291,7 @@ extern "C" FMB_API int fmb_forward(const fmb_model_t* model, const fmb_nl_t* nl,
     FMB_TRY(forward_layer(c, 0));
     FMB_TRY(forward_layer(c, 1));
     // readout; the gradient of the last layer's scalars is parked in `basis` (free after the forward pass)
+    StageScope scope(c.stream, kStReadout);
     FMB_TRY(readout(model, c.n, h_of(c, 0), h_of(c, 1), work->node_energy, work->d_h, work->basis, c.stream));
     return FMB_OK;
 }
@@ -255,6 +301,7 @@ extern "C" FMB_API int fmb_backward(const fmb_model_t* model, const fmb_nl_t* nl
     FMB_TRY(make_ctx(c, model, nl, work, (cudaStream_t)stream));
     FMB_TRY(backward_layer(c, 1, work->basis, work->d_h, 1));
     FMB_TRY(backward_layer(c, 0, work->d_h, nullptr, 0));
+    StageScope scope(c.stream, kStReadout);
     FMB_TRY(reduce_outputs(model, work, cell_volume(nl), c.stream));
     return FMB_OK;
 }
@@ -279,4 +326,25 @@ extern "C" FMB_API int fmb_commit_forces(const fmb_work_t* work, double* forces6
                                  fmb_stream_t stream) {
     FMB_REQUIRE(work && forces64 && energy64, "fmb_commit_forces: null argument");
     return commit_forces(work, forces64, energy64, work->compute_stress ? stress64 : nullptr, (cudaStream_t)stream);
+}
+
+extern "C" FMB_API int fmb_profile_enable(int on) {
+    g_timer.on = on != 0;
+    return FMB_OK;
+}
+
+extern "C" FMB_API int fmb_profile_read(float* ms, int* spans, int n) {
+    FMB_REQUIRE(ms && spans && n >= kStages, "fmb_profile_read: need room for every stage");
+    for (int k = 0; k < n; ++k) { ms[k] = 0.0f; spans[k] = 0; }
+    for (auto& span : g_timer.spans) {
+        FMB_CUDA_CHECK(cudaEventSynchronize(span.b));
+        float t = 0.0f;
+        FMB_CUDA_CHECK(cudaEventElapsedTime(&t, span.a, span.b));
+        ms[span.stage] += t;
+        spans[span.stage] += 1;
+        g_timer.pool.push_back(span.a);
+        g_timer.pool.push_back(span.b);
+    }
+    g_timer.spans.clear();
+    return kStages;
 }

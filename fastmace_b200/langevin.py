@@ -1,0 +1,174 @@
+"""ASE's ``Langevin`` (NVT, fixed cell) as two device stages: the interface of FastMACE's integrator
+(``fastmace/integrators/langevin.py:157-263``; ``Integrator`` ABC ``fastmace/integrators/base.py:48-178``) over
+``fmb_langevin_first_half`` / ``fmb_langevin_second_half``.
+
+Same coefficients (``langevin.py:184-198``), same noise source and order: NumPy ``default_rng(seed)`` on the host,
+``standard_normal((k, 2, N, 3))`` per batch (per step ``xi`` then ``eta``), uploaded ``noise_batch`` steps at a time
+and capped at 64 MiB (``langevin.py:31-45``). The kernels pick the step's row through a device-side cursor, so a
+captured step needs no per-step host copy; the next batch is drawn on a background thread into pinned memory while
+the current one is consumed (``langevin.py:67-89``).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import dataclasses
+import math
+import threading
+
+import numpy as np
+import torch
+
+from . import _lib
+from .state import SimulationState
+from .structures import FS, KB
+
+NOISE_BATCH_BYTES = 64 * 2 ** 20
+
+
+@dataclasses.dataclass(frozen=True)
+class IntegratorConfig:
+    """The fields of the reference's ``IntegratorConfig`` the Langevin path reads (``fastmace/config.py:471-512``).
+    ``friction`` is in inverse ASE time units (0.01 / fs = 0.01 / FS)."""
+    timestep_fs: float = 1.0
+    friction: float = 0.01 / FS
+    fixcm: bool = True
+    fixcm_projection: str = "mass_weighted"      # or "ase"
+    noise_batch: int = 256
+    ensemble: str = "nvt"
+
+
+def noise_steps(limit: int, numbers: int) -> int:
+    """Steps per drawn-ahead batch (``langevin.py:41-45``)."""
+    return max(1, min(limit, NOISE_BATCH_BYTES // (8 * numbers)))
+
+
+class Langevin:
+    def __init__(self, state: SimulationState, config: IntegratorConfig | None = None, *, temperature_K: float = 0.0,
+                 force_buffer: torch.Tensor | None = None):
+        self.lib = _lib.load()
+        config = config or IntegratorConfig()
+        if config.ensemble != "nvt":
+            raise ValueError("Langevin integrates the 'nvt' ensemble")
+        self.config = config
+        self.dt = config.timestep_fs * FS
+        self.natoms = state.natoms
+        self.noise_batch = noise_steps(config.noise_batch, 6 * self.natoms)
+        dev = state.positions.device
+        f64 = dict(dtype=torch.float64, device=dev)
+        dt, fr = self.dt, config.friction
+        self.fr = fr
+        self.c1 = dt / 2.0 - dt * dt * fr / 8.0
+        self.c2 = dt * fr / 2 - dt * dt * fr * fr / 8.0
+        masses = state.masses.reshape(-1)
+        sigma_unit = torch.sqrt(2 * fr / masses)
+        self.c3_unit = (math.sqrt(dt) * sigma_unit / 2.0 - dt ** 1.5 * fr * sigma_unit / 8.0).contiguous()
+        self.c5_unit = (dt ** 1.5 * sigma_unit / (2 * math.sqrt(3))).contiguous()
+        self.c4_unit = (fr / 2.0 * self.c5_unit).contiguous()
+        self.masses = masses.contiguous()
+        self.x_old = torch.zeros_like(state.positions)
+        self.rnd_pos = torch.zeros_like(state.positions)
+        self.rnd_vel = torch.zeros_like(state.positions)
+        self.partial = torch.zeros(128 * 16, **f64)
+        self.sqrt_kT = torch.zeros((), **f64)
+        self.cursor_dev = torch.zeros((), dtype=torch.int32, device=dev)
+        shape = (self.noise_batch, 2, self.natoms, 3)
+        state.rng.batch = torch.zeros(shape, **f64)
+        state.rng.cursor = self.noise_batch        # used up: the first step refills
+        self._staging = [torch.empty(shape, dtype=torch.float64).pin_memory() if dev.type == "cuda"
+                         else torch.empty(shape, dtype=torch.float64) for _ in range(2)]
+        self._staging_events = [torch.cuda.Event() if dev.type == "cuda" else None for _ in range(2)]
+        self._next = 0
+        self._ahead: threading.Thread | None = None
+        self.set_temperature(temperature_K)
+        self.struct = _lib.LangevinStruct()
+        s = self.struct
+        s.n_atoms = self.natoms
+        s.fix_com = 0 if not config.fixcm else (2 if config.fixcm_projection == "mass_weighted" else 1)
+        s.dt, s.c1, s.c2 = self.dt, self.c1, self.c2
+        s.positions, s.velocities = state.positions.data_ptr(), state.velocities.data_ptr()
+        s.forces = (force_buffer if force_buffer is not None else state.forces).data_ptr()
+        s.masses = self.masses.data_ptr()
+        s.c3_unit, s.c4_unit, s.c5_unit = self.c3_unit.data_ptr(), self.c4_unit.data_ptr(), self.c5_unit.data_ptr()
+        s.sqrt_kT = self.sqrt_kT.data_ptr()
+        s.noise = state.rng.batch.data_ptr()
+        s.noise_cursor = self.cursor_dev.data_ptr()
+        s.noise_cursor_rw = self.cursor_dev.data_ptr()
+        s.x_old, s.rnd_pos, s.rnd_vel = self.x_old.data_ptr(), self.rnd_pos.data_ptr(), self.rnd_vel.data_ptr()
+        s.partial = self.partial.data_ptr()
+
+    @property
+    def variable_cell(self) -> bool:
+        return False
+
+    def set_temperature(self, temperature_K: float) -> None:
+        self.temperature_K = float(temperature_K)
+        self.sqrt_kT.fill_(math.sqrt(KB * temperature_K))
+
+    # ------------------------------------------------------------------ noise
+    def _draw_into(self, generator: np.random.Generator, slot: int) -> None:
+        np.copyto(self._staging[slot].numpy(),
+                  generator.standard_normal(size=(self.noise_batch, 2, self.natoms, 3)))
+
+    def _start_draw_ahead(self, state: SimulationState) -> None:
+        slot = self._next
+        event = self._staging_events[slot]
+        if event is not None:
+            event.synchronize()       # the copy that last read this buffer has finished
+        self._ahead = threading.Thread(target=self._draw_into, args=(state.rng.generator, slot), daemon=True)
+        self._ahead.start()
+
+    def refill(self, state: SimulationState) -> None:
+        """Upload the next drawn-ahead batch (drawing it now if no draw is in flight), rewind the cursors and start
+        drawing the batch after it on the background thread."""
+        rng = state.rng
+        if self._ahead is None:
+            self._draw_into(rng.generator, self._next)
+        else:
+            self._ahead.join()
+        slot = self._next
+        rng.batch.copy_(self._staging[slot], non_blocking=True)
+        if self._staging_events[slot] is not None:
+            self._staging_events[slot].record()
+        self.cursor_dev.zero_()
+        rng.cursor = 0
+        self._next = 1 - slot
+        self._start_draw_ahead(state)
+
+    def prepare_step(self, state: SimulationState) -> None:
+        """Refill the noise batch when it is used up (host; between replays) and advance the host cursor."""
+        if state.rng.cursor == self.noise_batch:
+            self.refill(state)
+        state.rng.cursor += 1
+
+    def upload_noise(self, state: SimulationState, rows: np.ndarray) -> None:
+        """Replace the batch by ``rows`` (k <= noise_batch steps) and rewind the cursor: for tests and for
+        runs whose noise is resident before the timed region."""
+        k = rows.shape[0]
+        state.rng.batch[:k].copy_(torch.from_numpy(np.ascontiguousarray(rows)))
+        self.cursor_dev.zero_()
+        state.rng.cursor = 0
+
+    # ------------------------------------------------------------------ stages (graph-capturable)
+    def first_half(self, state: SimulationState) -> None:
+        _lib.check(self.lib.fmb_langevin_first_half(ctypes.byref(self.struct), _lib.current_stream()),
+                   "fmb_langevin_first_half")
+
+    def second_half(self, state: SimulationState) -> None:
+        _lib.check(self.lib.fmb_langevin_second_half(ctypes.byref(self.struct), _lib.current_stream()),
+                   "fmb_langevin_second_half")
+
+    def mid_step_tensors(self, state: SimulationState):
+        return (state.velocities,)
+
+    def buffers(self, state: SimulationState):
+        return dict(positions=state.positions, velocities=state.velocities, x_old=self.x_old, rnd_pos=self.rnd_pos,
+                    rnd_vel=self.rnd_vel)
+
+    def output_values(self, state: SimulationState):
+        kinetic = (0.5 * (state.masses * state.velocities ** 2).sum()).reshape(1)
+        return dict(positions=state.positions, momenta=state.velocities * state.masses, forces=state.forces,
+                    energy=state.energy.reshape(-1)[:1], kinetic=kinetic)
+
+
+__all__ = ["Langevin", "IntegratorConfig", "noise_steps", "NOISE_BATCH_BYTES"]

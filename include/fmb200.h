@@ -47,6 +47,8 @@ FMB_API const char* fmb_last_error(void);
 /* sizeof of the structs below, for the host binding to verify its mirror: which = 0 fmb_nl_t, 1 fmb_model_t,
  * 2 fmb_work_t, 3 fmb_langevin_t */
 FMB_API int fmb_sizeof(int which);
+/* kernels this library has launched (or captured into a graph) in this process so far */
+FMB_API long long fmb_launch_count(void);
 
 /* ------------------------------------------------------------------------------------------------ neighbour list
  * Replaces SkinNeighbourList (fastmace/neighbors/skin.py:164-747) with sort_receivers on and no sender groups.
@@ -193,6 +195,14 @@ FMB_API int fmb_backward(const fmb_model_t* model, const fmb_nl_t* nl, const fmb
  * impl 0: SIMT FMA kernel; impl 1: tcgen05 3xTF32 kernel (K, N multiples of 64; falls back to an error otherwise). */
 FMB_API int fmb_gemm(const float* a, const float* b, float* c, int m, int n, int k, int accumulate, int impl,
              fmb_stream_t stream);
+
+/* Per-stage CUDA-event timing of eager (not captured) force calls, the counterpart of the reference's stage
+ * breakdown tool (tools/step_breakdown.py: CUDA events around each stage). Stages, in order: edge features, radial
+ * weight GEMMs, tensor product forward layer 0 / layer 1, per-irrep linears, symmetric contraction forward /
+ * backward, tensor product backward layer 1 / layer 0, readout + reductions. fmb_profile_read synchronises, fills
+ * the milliseconds and the number of timed spans per stage since the last read, and returns the stage count. */
+FMB_API int fmb_profile_enable(int on);
+FMB_API int fmb_profile_read(float* ms, int* spans, int n);
 
 /* ------------------------------------------------------------------------------------------------ Langevin
  * Replaces Langevin.first_half / second_half (fastmace/integrators/langevin.py:233-263) and the fused stage

@@ -22,7 +22,8 @@ STATUS_ROW_OVERFLOW = 2
 STATUS_BIN_OVERFLOW = 4
 STATUS_NONFINITE = 8
 
-EXPORTS = ("fmb_version", "fmb_last_error", "fmb_sizeof", "fmb_launch_count", "fmb_nl_build", "fmb_nl_compact", "fmb_nl_needs_rebuild",
+EXPORTS = ("fmb_version", "fmb_last_error", "fmb_sizeof", "fmb_launch_count", "fmb_nl_build", "fmb_nl_compact", "fmb_nl_compact_static",
+           "fmb_nl_needs_rebuild",
            "fmb_forces", "fmb_edge_features", "fmb_forward", "fmb_backward", "fmb_gemm", "fmb_langevin_first_half",
            "fmb_langevin_second_half", "fmb_commit_forces", "fmb_profile_enable", "fmb_profile_read")
 
@@ -112,6 +113,7 @@ def load() -> ctypes.CDLL:
     P = c_void_p
     lib.fmb_nl_build.argtypes = [POINTER(NlStruct), P, c_int, P]
     lib.fmb_nl_compact.argtypes = [POINTER(NlStruct), P, P]
+    lib.fmb_nl_compact_static.argtypes = [POINTER(NlStruct), P, P]
     lib.fmb_nl_needs_rebuild.argtypes = [POINTER(NlStruct), P, c_double, P]
     lib.fmb_forces.argtypes = [POINTER(ModelStruct), POINTER(NlStruct), POINTER(WorkStruct), P, P]
     lib.fmb_edge_features.argtypes = [POINTER(ModelStruct), POINTER(NlStruct), POINTER(WorkStruct), P, P]

@@ -99,6 +99,15 @@ FMB_API int fmb_nl_build(const fmb_nl_t* nl, const double* positions, int only_i
 /* skin.py:702-729 (compact): stable partition, inside-cutoff first; writes edge_index, unit_shifts, shifts, count and
  * edge_row_ptr. */
 FMB_API int fmb_nl_compact(const fmb_nl_t* nl, const double* positions, fmb_stream_t stream);
+/* No counterpart in the reference. fmb_nl_compact for hosts that cannot hand over scratch memory (a driver whose
+ * device pool is frozen once its step graphs exist, a plugin arena that forbids allocation while stepping): the
+ * per-receiver counts and scan sums live in one device array inside the library (about 1 MiB per GPU, held until the
+ * process exits) and nothing is allocated. nl->edge_row_count and nl->scan_scratch are ignored; everything else is as
+ * for fmb_nl_compact. Lists above FMB_STATIC_COMPACT_MAX_ATOMS atoms are refused (FMB_ERR_ARG). The first call on a
+ * device resolves the array's address and should be made outside stream capture. All calls on a GPU share the
+ * array: run them on one stream (or order them), overlapping calls race. */
+#define FMB_STATIC_COMPACT_MAX_ATOMS 262144
+FMB_API int fmb_nl_compact_static(const fmb_nl_t* nl, const double* positions, fmb_stream_t stream);
 /* skin.py:685-693 (needs_rebuild, fixed cell): rebuild_flag = max_i |x_i - x_ref,i|^2 > (fraction * skin / 2)^2. */
 FMB_API int fmb_nl_needs_rebuild(const fmb_nl_t* nl, const double* positions, double fraction, fmb_stream_t stream);
 

@@ -21,6 +21,7 @@ STATUS_CAND_OVERFLOW = 1
 STATUS_ROW_OVERFLOW = 2
 STATUS_BIN_OVERFLOW = 4
 STATUS_NONFINITE = 8
+STATUS_TENSOR_TIMEOUT = 16
 
 EXPORTS = ("fmb_version", "fmb_last_error", "fmb_sizeof", "fmb_launch_count", "fmb_nl_build", "fmb_nl_compact", "fmb_nl_compact_static",
            "fmb_nl_needs_rebuild",
@@ -54,7 +55,7 @@ class LayerStruct(ctypes.Structure):
         ("rad_w", c_void_p * 4), ("x_species", c_void_p), ("sc_species", c_void_p), ("w_up", c_void_p),
         ("w_up_t", c_void_p), ("w_skip", c_void_p), ("w_skip_t", c_void_p), ("w_lin", c_void_p),
         ("w_lin_t", c_void_p), ("w_prod", c_void_p), ("w_prod_t", c_void_p), ("sc_terms", c_void_p),
-        ("sc_coef", c_void_p), ("w_readout", c_void_p),
+        ("sc_coef", c_void_p), ("w_readout", c_void_p), ("tc", c_void_p * 9),
     ]
 
 
@@ -119,7 +120,7 @@ def load() -> ctypes.CDLL:
     lib.fmb_edge_features.argtypes = [POINTER(ModelStruct), POINTER(NlStruct), POINTER(WorkStruct), P, P]
     lib.fmb_forward.argtypes = [POINTER(ModelStruct), POINTER(NlStruct), POINTER(WorkStruct), P]
     lib.fmb_backward.argtypes = [POINTER(ModelStruct), POINTER(NlStruct), POINTER(WorkStruct), P]
-    lib.fmb_gemm.argtypes = [P, P, P, c_int, c_int, c_int, c_int, c_int, P]
+    lib.fmb_gemm.argtypes = [P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P]
     lib.fmb_langevin_first_half.argtypes = [POINTER(LangevinStruct), P]
     lib.fmb_langevin_second_half.argtypes = [POINTER(LangevinStruct), P]
     lib.fmb_commit_forces.argtypes = [POINTER(WorkStruct), P, P, P, P]

@@ -99,11 +99,18 @@ int radial_weights(const Ctx& c, int layer, long long e0, bool with_tangent) {
     const fmb_layer_t& L = c.m->layer[layer];
     const long long rows = std::min<long long>(c.chunk, c.count_cap - e0);
     StageScope scope(c.stream, kStRadial);
-    for (int tangent = 0; tangent < (with_tangent ? 2 : 1); ++tangent) {
-        GemmArgs g;
+    GemmArgs list[2];
+    const int count = with_tangent ? 2 : 1;
+    for (int tangent = 0; tangent < count; ++tangent) {
+        GemmArgs& g = list[tangent];
         g.a = hidden_of(c, layer, tangent) + e0 * kRadial;
         g.a_bs = kRadial;
         g.b = L.rad_w[3];
+        if (L.tc[0]) {
+            g.bt_hi = L.tc[0];
+            g.bt_lo = L.tc[0] + (long long)kRadial * L.n_paths * kC;
+        }
+        g.error_word = c.w->status;
         g.c = c.w->tp_w + (long long)tangent * c.chunk * L.n_paths * kC;
         g.c_bs = (long long)L.n_paths * kC;
         g.m = (int)rows;
@@ -111,29 +118,45 @@ int radial_weights(const Ctx& c, int layer, long long e0, bool with_tangent) {
         g.k = kRadial;
         g.m_limit = (const long long*)c.nl->count;
         g.m_limit_offset = e0;
-        const int rc = gemm(g, c.stream);
-        if (rc) return rc;
     }
-    return FMB_OK;
+    return gemm_batch(list, count, c.stream);
 }
 
-// per-irrep linear: rows (atom, m) of block l; in/out strides in floats per atom
-int block_linear(const Ctx& c, const float* in, long long in_atom, long long in_off, int k, const float* weight,
-                 float* out, long long out_atom, long long out_off, int n_out, int l, int accumulate,
-                 const int32_t* batch_species = nullptr, int select = -1) {
-    StageScope scope(c.stream, kStLinear);
-    GemmArgs g;
+// A group of independent per-irrep linears that go out as one launch.
+struct LinearBatch {
+    GemmArgs list[32];
+    int count = 0;
+};
+
+// `twin`: base of the weight array's tensor-core twin (or null); the block's twin starts at twice its float offset
+void block_linear(LinearBatch& batch, const Ctx& c, const float* in, long long in_atom, long long in_off, int k,
+                  const float* base, const float* twin, long long w_off, float* out, long long out_atom,
+                  long long out_off, int n_out, int l, int accumulate, const int32_t* batch_species = nullptr,
+                  int select = -1) {
+    GemmArgs& g = batch.list[batch.count++];
     const int nm = 2 * l + 1;
     g.a = in + in_off;
     g.a_nm = nm; g.a_bs = in_atom; g.a_rs = k;
-    g.b = weight;
+    g.b = base + w_off;
+    if (twin) {
+        g.bt_hi = twin + 2 * w_off;
+        g.bt_lo = g.bt_hi + (long long)k * n_out;
+    }
+    g.error_word = c.w->status;
     g.c = out + out_off;
     g.c_nm = nm; g.c_bs = out_atom; g.c_rs = n_out;
     g.m = c.n * nm; g.n = n_out; g.k = k;
     g.accumulate = accumulate;
     g.batch_species = batch_species;
     g.select = select;
-    return gemm(g, c.stream);
+}
+
+int run_linears(const Ctx& c, LinearBatch& batch) {
+    if (batch.count == 0) return FMB_OK;
+    StageScope scope(c.stream, kStLinear);
+    const int rc = gemm_batch(batch.list, batch.count, c.stream);
+    batch.count = 0;
+    return rc;
 }
 
 long long lin_weight_offset(const MidLayout& ml, int l) {
@@ -155,22 +178,23 @@ int forward_layer(const Ctx& c, int layer) {
     const int in_dim = dim_of(L.l_in_max), out_dim = dim_of(L.l_out_max);
     float* h_out = h_of(c, layer);
     const float* x = nullptr;
+    LinearBatch lb;
     if (layer == 0) {
         FMB_TRY(fill_from_species(c.n, out_dim * kC, c.w->species, L.sc_species, h_out, c.stream));
         x = L.x_species;
     } else {
         const float* h_in = h_of(c, layer - 1);
         const int h_in_dim = c.hidden_dim;
-        // species-dependent skip: one masked GEMM per present species and irrep, each row written exactly once
+        // species-dependent skip: one row-masked GEMM per present species and irrep, each row written exactly once
         for (int l = 0; l <= L.skip_lmax; ++l)
             for (int z = 0; z < c.m->n_species; ++z)
-                FMB_TRY(block_linear(c, h_in, (long long)h_in_dim * kC, (long long)l * l * kC, kC,
-                                     L.w_skip + ((long long)l * c.m->n_species + z) * kC * kC, h_out,
-                                     (long long)out_dim * kC, (long long)l * l * kC, kC, l, 0, c.w->species, z));
+                block_linear(lb, c, h_in, (long long)h_in_dim * kC, (long long)l * l * kC, kC, L.w_skip, L.tc[3],
+                             ((long long)l * c.m->n_species + z) * kC * kC, h_out, (long long)out_dim * kC,
+                             (long long)l * l * kC, kC, l, 0, c.w->species, z);
         for (int l = 0; l <= L.l_in_max; ++l)
-            FMB_TRY(block_linear(c, h_in, (long long)h_in_dim * kC, (long long)l * l * kC, kC,
-                                 L.w_up + (long long)l * kC * kC, c.w->x, (long long)in_dim * kC,
-                                 (long long)l * l * kC, kC, l, 0));
+            block_linear(lb, c, h_in, (long long)h_in_dim * kC, (long long)l * l * kC, kC, L.w_up, L.tc[1],
+                         (long long)l * kC * kC, c.w->x, (long long)in_dim * kC, (long long)l * l * kC, kC, l, 0);
+        FMB_TRY(run_linears(c, lb));
         x = c.w->x;
     }
     for (int k = 0; k < c.n_chunks; ++k) {
@@ -186,17 +210,18 @@ int forward_layer(const Ctx& c, int layer) {
     }
     float* msg = msg_of(c, layer);
     for (int l = 0; l <= 3; ++l)
-        FMB_TRY(block_linear(c, c.w->mid, (long long)ml.mid_dim * kC, (long long)ml.base[l] * kC, ml.segs[l] * kC,
-                             L.w_lin + lin_weight_offset(ml, l), msg, (long long)kNSH * kC, (long long)l * l * kC, kC, l, 0));
+        block_linear(lb, c, c.w->mid, (long long)ml.mid_dim * kC, (long long)ml.base[l] * kC, ml.segs[l] * kC, L.w_lin,
+                     L.tc[5], lin_weight_offset(ml, l), msg, (long long)kNSH * kC, (long long)l * l * kC, kC, l, 0);
+    FMB_TRY(run_linears(c, lb));
     {
         StageScope scope(c.stream, kStSymFwd);
         FMB_TRY(symcon_forward(c.n, L.n_sc_terms, out_dim, L.sc_terms, L.sc_coef, c.w->species, msg, c.w->basis,
                                c.stream));
     }
     for (int l = 0; l <= L.l_out_max; ++l)
-        FMB_TRY(block_linear(c, c.w->basis, (long long)out_dim * kC, (long long)l * l * kC, kC,
-                             L.w_prod + (long long)l * kC * kC, h_out, (long long)out_dim * kC, (long long)l * l * kC,
-                             kC, l, 1));
+        block_linear(lb, c, c.w->basis, (long long)out_dim * kC, (long long)l * l * kC, kC, L.w_prod, L.tc[7],
+                     (long long)l * kC * kC, h_out, (long long)out_dim * kC, (long long)l * l * kC, kC, l, 1);
+    FMB_TRY(run_linears(c, lb));
     return FMB_OK;
 }
 
@@ -206,26 +231,28 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
     const fmb_layer_t& L = c.m->layer[layer];
     const MidLayout ml = mid_layout(L.l_in_max);
     const int in_dim = dim_of(L.l_in_max), out_dim = dim_of(L.l_out_max);
+    LinearBatch lb;
     for (int l = 0; l <= L.l_out_max; ++l)
-        FMB_TRY(block_linear(c, d_h_out, (long long)out_dim * kC, (long long)l * l * kC, kC,
-                             L.w_prod_t + (long long)l * kC * kC, c.w->d_basis, (long long)out_dim * kC,
-                             (long long)l * l * kC, kC, l, 0));
+        block_linear(lb, c, d_h_out, (long long)out_dim * kC, (long long)l * l * kC, kC, L.w_prod_t, L.tc[8],
+                     (long long)l * kC * kC, c.w->d_basis, (long long)out_dim * kC, (long long)l * l * kC, kC, l, 0);
     if (layer > 0) {
         for (int l = 0; l <= L.skip_lmax; ++l)
             for (int z = 0; z < c.m->n_species; ++z)
-                FMB_TRY(block_linear(c, d_h_out, (long long)out_dim * kC, (long long)l * l * kC, kC,
-                                     L.w_skip_t + ((long long)l * c.m->n_species + z) * kC * kC, d_h_in,
-                                     (long long)c.hidden_dim * kC, (long long)l * l * kC, kC, l, 1, c.w->species, z));
+                block_linear(lb, c, d_h_out, (long long)out_dim * kC, (long long)l * l * kC, kC, L.w_skip_t, L.tc[4],
+                             ((long long)l * c.m->n_species + z) * kC * kC, d_h_in, (long long)c.hidden_dim * kC,
+                             (long long)l * l * kC, kC, l, 1, c.w->species, z);
     }
+    FMB_TRY(run_linears(c, lb));
     {
         StageScope scope(c.stream, kStSymBwd);
         FMB_TRY(symcon_backward(c.n, L.n_sc_terms, out_dim, L.sc_terms, L.sc_coef, c.w->species, msg_of(c, layer),
                                 c.w->d_basis, c.w->d_msg, c.stream));
     }
     for (int l = 0; l <= 3; ++l)
-        FMB_TRY(block_linear(c, c.w->d_msg, (long long)kNSH * kC, (long long)l * l * kC, kC,
-                             L.w_lin_t + lin_weight_offset(ml, l), c.w->d_mid, (long long)ml.mid_dim * kC,
-                             (long long)ml.base[l] * kC, ml.segs[l] * kC, l, 0));
+        block_linear(lb, c, c.w->d_msg, (long long)kNSH * kC, (long long)l * l * kC, kC, L.w_lin_t, L.tc[6],
+                     lin_weight_offset(ml, l), c.w->d_mid, (long long)ml.mid_dim * kC, (long long)ml.base[l] * kC,
+                     ml.segs[l] * kC, l, 0);
+    FMB_TRY(run_linears(c, lb));
     for (int k = 0; k < c.n_chunks; ++k) {
         const long long e0 = (long long)k * c.chunk;
         FMB_TRY(radial_weights(c, layer, e0, true));
@@ -242,9 +269,9 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
     }
     if (layer > 0) {
         for (int l = 0; l <= L.l_in_max; ++l)
-            FMB_TRY(block_linear(c, c.w->d_x, (long long)in_dim * kC, (long long)l * l * kC, kC,
-                                 L.w_up_t + (long long)l * kC * kC, d_h_in, (long long)c.hidden_dim * kC,
-                                 (long long)l * l * kC, kC, l, 1));
+            block_linear(lb, c, c.w->d_x, (long long)in_dim * kC, (long long)l * l * kC, kC, L.w_up_t, L.tc[2],
+                         (long long)l * kC * kC, d_h_in, (long long)c.hidden_dim * kC, (long long)l * l * kC, kC, l, 1);
+        FMB_TRY(run_linears(c, lb));
     }
     return FMB_OK;
 }
@@ -314,10 +341,10 @@ extern "C" FMB_API int fmb_forces(const fmb_model_t* model, const fmb_nl_t* nl, 
     return FMB_OK;
 }
 
-extern "C" FMB_API int fmb_gemm(const float* a, const float* b, float* c, int m, int n, int k, int accumulate, int impl,
-                        fmb_stream_t stream) {
+extern "C" FMB_API int fmb_gemm(const float* a, const float* b, const float* bt_hi, const float* bt_lo, float* c, int m,
+                                int n, int k, int accumulate, int impl, uint32_t* status, fmb_stream_t stream) {
     GemmArgs g;
-    g.a = a; g.b = b; g.c = c; g.m = m; g.n = n; g.k = k;
+    g.a = a; g.b = b; g.bt_hi = bt_hi; g.bt_lo = bt_lo; g.error_word = status; g.c = c; g.m = m; g.n = n; g.k = k;
     g.a_bs = k; g.c_bs = n; g.accumulate = accumulate;
     return impl == 1 ? gemm_tc(g, (cudaStream_t)stream) : gemm_simt(g, (cudaStream_t)stream);
 }

@@ -11,6 +11,10 @@ namespace fmb {
 struct GemmArgs {
     const float* a = nullptr;
     const float* b = nullptr;
+    // optional tensor-core operands: B transposed ([n][k], K contiguous) and split into tf32 hi / lo parts
+    const float* bt_hi = nullptr;
+    const float* bt_lo = nullptr;
+    uint32_t* error_word = nullptr;   // device status word for bounded-wait failures
     float* c = nullptr;
     int m = 0, n = 0, k = 0;
     int a_nm = 1;
@@ -22,7 +26,6 @@ struct GemmArgs {
     // optional: rows at or beyond *m_limit - m_limit_offset (a device scalar, e.g. the edge count) are skipped
     const long long* m_limit = nullptr;
     long long m_limit_offset = 0;
-    int m_limit_scale = 1;            // rows per counted unit (2 when values and tangents are stacked)
     // optional: only batches whose species equals `select` are written (species-dependent linear)
     const int32_t* batch_species = nullptr;
     int select = -1;
@@ -31,6 +34,10 @@ struct GemmArgs {
 int gemm_simt(const GemmArgs& args, cudaStream_t stream);
 // tcgen05 / TMEM 3xTF32 kernel; returns FMB_ERR_UNSUPPORTED for shapes it does not take.
 int gemm_tc(const GemmArgs& args, cudaStream_t stream);
+// several GEMMs (at most 8) in one launch of the tensor-core kernel; FMB_ERR_UNSUPPORTED if any does not qualify
+int gemm_tc_batch(const GemmArgs* list, int count, cudaStream_t stream);
+// the same through whichever kernel applies (one launch when the tensor-core kernel takes them all)
+int gemm_batch(const GemmArgs* list, int count, cudaStream_t stream);
 // picks gemm_tc when it applies and FMB_GEMM selects it, else gemm_simt
 int gemm(const GemmArgs& args, cudaStream_t stream);
 

@@ -25,6 +25,25 @@ def _f64(t: torch.Tensor) -> torch.Tensor:
     return t.detach().to(torch.float64).cpu()
 
 
+def tf32_round(x: torch.Tensor) -> torch.Tensor:
+    """fp32 -> nearest tf32 (10-bit mantissa, ties away from zero, like cvt.rna.tf32.f32), returned as fp32."""
+    bits = x.contiguous().view(torch.int32)
+    return ((bits + 0x1000) & ~0x1fff).view(torch.float32)
+
+
+def tensor_core_twin(blocks) -> torch.Tensor:
+    """For a list of fp32 [K][N] weight blocks: the concatenation of, per block, the transposed block [N][K] rounded
+    to tf32 followed by the tf32-rounded remainder -- the operands of the 3xTF32 tensor-core GEMM. The twin of a
+    block that starts at float offset o of the concatenated weights starts at 2 o."""
+    out = []
+    for block in blocks:
+        bt = block.to(torch.float32).t().contiguous()
+        hi = tf32_round(bt)
+        lo = tf32_round(bt - hi)
+        out += [hi.reshape(-1), lo.reshape(-1)]
+    return torch.cat(out)
+
+
 def contraction_terms(spec: MaceSpec, weights, layer: int, species_z):
     """(terms int32 [T, 4], coef float64 [n_species, T, C]) of one layer's symmetric contraction, sorted by output."""
     c = spec.channels
@@ -100,6 +119,7 @@ class PackedModel:
             widths = (spec.num_bessel, *spec.radial_hidden, len(paths) * c)
             for i in range(4):
                 layer.rad_w[i] = self._put(f"l{t}.rad.{i}", w[f"l{t}.rad.{i}"] / math.sqrt(widths[i]))
+            layer.tc[0] = self._twin(f"l{t}.rad.3", [self.tensors[f"l{t}.rad.3"]])
             if t == 0:
                 x_species = h0 @ (w["l0.up.0"] / math.sqrt(c))
                 sc = torch.zeros(len(idx), spec.out_dim(0), c, dtype=torch.float64)
@@ -112,22 +132,31 @@ class PackedModel:
                 up = torch.stack([w[f"l{t}.up.{l}"] / math.sqrt(c) for l in range(spec.l_in_max(t) + 1)])
                 layer.w_up = self._put(f"l{t}.w_up", up)
                 layer.w_up_t = self._put(f"l{t}.w_up_t", up.transpose(1, 2))
+                layer.tc[1] = self._twin(f"l{t}.w_up", list(self.tensors[f"l{t}.w_up"]))
+                layer.tc[2] = self._twin(f"l{t}.w_up_t", list(self.tensors[f"l{t}.w_up_t"]))
                 skip = torch.stack([w[f"l{t}.skip.{l}"][:, idx, :].permute(1, 0, 2) / math.sqrt(c * n_el)
                                     for l in range(spec.skip_lmax(t) + 1)])     # [L, nz, C, C]
                 layer.w_skip = self._put(f"l{t}.w_skip", skip)
                 layer.w_skip_t = self._put(f"l{t}.w_skip_t", skip.transpose(2, 3))
-            lin, lin_t = [], []
+                layer.tc[3] = self._twin(f"l{t}.w_skip", list(self.tensors[f"l{t}.w_skip"].reshape(-1, c, c)))
+                layer.tc[4] = self._twin(f"l{t}.w_skip_t", list(self.tensors[f"l{t}.w_skip_t"].reshape(-1, c, c)))
+            lin, lin_t, lin_blocks = [], [], []
             for l_out in range(spec.sh_lmax + 1):
                 into = so3.paths_into(paths, l_out)
                 norm = 1.0 / math.sqrt(len(into) * c) / spec.avg_num_neighbors
                 block = torch.cat([w[f"l{t}.lin.{p}"] for p in into], dim=0) * norm   # [n_seg * C, C]
                 lin.append(block.reshape(-1))
                 lin_t.append(block.t().contiguous().reshape(-1))
+                lin_blocks.append(block.to(torch.float32))
             layer.w_lin = self._put(f"l{t}.w_lin", torch.cat(lin))
             layer.w_lin_t = self._put(f"l{t}.w_lin_t", torch.cat(lin_t))
+            layer.tc[5] = self._twin(f"l{t}.w_lin", lin_blocks)
+            layer.tc[6] = self._twin(f"l{t}.w_lin_t", [b.t().contiguous() for b in lin_blocks])
             prod = torch.stack([w[f"l{t}.prod.{big_l}"] / math.sqrt(c) for big_l in range(spec.l_out_max(t) + 1)])
             layer.w_prod = self._put(f"l{t}.w_prod", prod)
             layer.w_prod_t = self._put(f"l{t}.w_prod_t", prod.transpose(1, 2))
+            layer.tc[7] = self._twin(f"l{t}.w_prod", list(self.tensors[f"l{t}.w_prod"]))
+            layer.tc[8] = self._twin(f"l{t}.w_prod_t", list(self.tensors[f"l{t}.w_prod_t"]))
             terms, coefs = contraction_terms(spec, weights, t, species_z)
             layer.n_sc_terms = len(terms)
             layer.sc_terms = self._put(f"l{t}.sc_terms", torch.from_numpy(terms), dtype=torch.int32)
@@ -145,6 +174,13 @@ class PackedModel:
         self.tensors[name] = t
         return t.data_ptr()
 
+    def _twin(self, name: str, blocks) -> int:
+        """Tensor-core twin of fp32 [K][N] blocks that are already on the device (so the split is of the fp32 values
+        the SIMT path reads)."""
+        twin = tensor_core_twin([b.cpu() for b in blocks]).to(self.device)
+        self.tensors[name + ".tc"] = twin
+        return twin.data_ptr()
+
     def species_index(self, numbers) -> torch.Tensor:
         """[N] int32 index of each atom's species among the present ones."""
         lookup = {z: k for k, z in enumerate(self.species_z)}
@@ -154,4 +190,4 @@ class PackedModel:
         return ctypes.byref(self.struct)
 
 
-__all__ = ["PackedModel", "contraction_terms"]
+__all__ = ["PackedModel", "contraction_terms", "tensor_core_twin", "tf32_round"]

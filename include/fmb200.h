@@ -34,6 +34,7 @@ extern "C" {
 #define FMB_STATUS_ROW_OVERFLOW 2u    /* one receiver has more candidates than FMB_MAX_ROW */
 #define FMB_STATUS_BIN_OVERFLOW 4u    /* internal: cell-list bins inconsistent */
 #define FMB_STATUS_NONFINITE 8u       /* a non-finite energy was produced */
+#define FMB_STATUS_TENSOR_TIMEOUT 16u /* a tensor-core kernel gave up waiting for its own MMA completion barrier */
 
 #define FMB_MAX_ROW 1024              /* candidates per receiver the in-kernel sort can hold */
 #define FMB_MAX_LAYERS 2
@@ -136,6 +137,10 @@ typedef struct {
     const int32_t* sc_terms;          /* [n_sc_terms][4]: i, j, k (unused = -1), m_out */
     const float* sc_coef;             /* [n_species][n_sc_terms][C] */
     const float* w_readout;           /* non-last: [C] (scale folded); last: [C][16] then [16] */
+    /* tensor-core twins of the GEMM weights, in the order rad_w[3], w_up, w_up_t, w_skip, w_skip_t, w_lin, w_lin_t,
+     * w_prod, w_prod_t: for every [K][N] block at float offset o of the array, the twin holds at offset 2 o the
+     * transposed block [N][K] rounded to tf32 (hi) followed by the tf32 remainder (lo). Null = SIMT GEMM. */
+    const float* tc[9];
 } fmb_layer_t;
 
 typedef struct {
@@ -200,10 +205,11 @@ FMB_API int fmb_edge_features(const fmb_model_t* model, const fmb_nl_t* nl, cons
 FMB_API int fmb_forward(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, fmb_stream_t stream);
 FMB_API int fmb_backward(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, fmb_stream_t stream);
 
-/* C[M, N] = A[M, K] B[K, N] in fp32 (rows of A and C addressed as batch/row strides); exported for tests.
- * impl 0: SIMT FMA kernel; impl 1: tcgen05 3xTF32 kernel (K, N multiples of 64; falls back to an error otherwise). */
-FMB_API int fmb_gemm(const float* a, const float* b, float* c, int m, int n, int k, int accumulate, int impl,
-             fmb_stream_t stream);
+/* C[M, N] (+)= A[M, K] B[K, N] in fp32; exported for tests. impl 0: SIMT FMA kernel reading b ([K][N]); impl 1:
+ * tcgen05 3xTF32 kernel reading bt_hi / bt_lo (B transposed [N][K], split in tf32 hi and lo; K and N multiples of
+ * 64), status FMB_ERR_UNSUPPORTED otherwise. `status` (device word, may be null) receives FMB_STATUS_TENSOR_TIMEOUT. */
+FMB_API int fmb_gemm(const float* a, const float* b, const float* bt_hi, const float* bt_lo, float* c, int m, int n,
+                     int k, int accumulate, int impl, uint32_t* status, fmb_stream_t stream);
 
 /* Per-stage CUDA-event timing of eager (not captured) force calls, the counterpart of the reference's stage
  * breakdown tool (tools/step_breakdown.py: CUDA events around each stage). Stages, in order: edge features, radial

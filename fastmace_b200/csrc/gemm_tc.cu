@@ -24,15 +24,15 @@ namespace fmb {
 namespace {
 
 constexpr int TM = 128;          // rows per CTA tile (UMMA M)
-constexpr int TN = 64;           // columns per MMA tile (UMMA N)
+// UMMA N (the 64-, 128- or 256-row operand) is a template parameter: a 128x64x8 tf32 MMA occupies the tensor core for
+// about as long as a 128x256x8 one (measured: ~128 cycles per instruction at N = 64), so wide tiles are what reach
+// the tensor peak; narrow ones are kept for small N.
 constexpr int TK = 64;           // K elements staged per chunk
 constexpr int kThreads = 256;      // 8 warps: two per TMEM lane quadrant, each taking half of a tile's columns
-constexpr int kTmemCols = 128;         // two 64-column accumulators
 constexpr unsigned kSpinLimit = 1u << 24;
 
 constexpr int kTileBytesA = TM * TK * 4;   // 32 KB (one of hi / lo)
-constexpr int kTileBytesB = TN * TK * 4;   // 16 KB
-constexpr int kSmemBytes = 2 * kTileBytesA + 2 * kTileBytesB + 64 + 1024;
+template <int TN> constexpr int smem_bytes() { return 2 * kTileBytesA + 2 * TN * TK * 4 + 64 + 1024; }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -64,7 +64,8 @@ __device__ __forceinline__ uint64_t k_step(int k8) {
     return (uint64_t)(((k8 >> 2) * (ROWS * 128) + (k8 & 3) * 32) >> 4);
 }
 
-// instruction descriptor: D fp32, A and B tf32, both K-major, N = 64, M = 128
+// instruction descriptor: D fp32, A and B tf32, both K-major, N = TN, M = 128
+template <int TN>
 __device__ __forceinline__ uint32_t make_idesc() {
     return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
 }
@@ -154,9 +155,12 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t* v) {
 // rows, and accumulator lane = output column. A warp then stores 128 contiguous bytes of one output row per
 // instruction, which is what the wide radial-weight outputs ([edges][P*C]) need; without the swap every lane would
 // write into a different row.
-template <bool SWAP>
-__global__ void __launch_bounds__(kThreads, 2)
+template <bool SWAP, int TN>
+__global__ void __launch_bounds__(kThreads, TN <= 64 ? 2 : 1)
 k_gemm_tc(const __grid_constant__ Batch batch) {
+    constexpr int kTileBytesB = TN * TK * 4;
+    constexpr int kTmemCols = 2 * TN;          // two accumulators
+    constexpr int kRowSteps = TN / 64;         // staging steps of the TN-row operand (64 rows per step)
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // swizzle atoms are 1024-byte aligned
     uint8_t* a_hi = smem;
@@ -187,6 +191,14 @@ k_gemm_tc(const __grid_constant__ Batch batch) {
     const int nt_end = min(n_tiles, nt_begin + per);
     if (nt_begin >= nt_end) return;
     const int k = pr.k, k_chunks = k / TK;
+    // Everything the loops read from the problem record is copied into registers here: the record is selected with a
+    // run-time index, and reading its fields in the inner loops made the first version of this kernel five times slower.
+    float* const c_out = pr.c;
+    const RowMap cmap = pr.cmap;
+    const RowMap amap = pr.amap;
+    const int accumulate = pr.accumulate;
+    const int32_t* const batch_species = pr.batch_species;
+    const int select = pr.select;
     const float* __restrict__ a = pr.a;
     const float* __restrict__ bt_hi = pr.bt_hi;
     const float* __restrict__ bt_lo = pr.bt_lo;
@@ -205,7 +217,7 @@ k_gemm_tc(const __grid_constant__ Batch batch) {
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t idesc = make_idesc();
+    const uint32_t idesc = make_idesc<TN>();
     const uint32_t bar = smem_u32(mbar);
     uint32_t phase = 0;
     bool failed = false;
@@ -219,14 +231,14 @@ k_gemm_tc(const __grid_constant__ Batch batch) {
     const bool a_resident = k_chunks == 1;
 
     float4 ra[TM / 64][TK / 16];
-    float4 rbh[TK / 16], rbl[TK / 16];
+    float4 rbh[kRowSteps][TK / 16], rbl[SWAP ? 1 : kRowSteps][TK / 16];
 
     auto fetch_a = [&](int kc) {
 #pragma unroll
         for (int i = 0; i < TM / 64; ++i) {
             const int row = ld_row + 64 * i;
             const bool ok = row0 + row < m;
-            const float* src = a + (ok ? pr.amap(row0 + row) : 0) + kc * TK;
+            const float* src = a + (ok ? amap(row0 + row) : 0) + kc * TK;
 #pragma unroll
             for (int j = 0; j < TK / 16; ++j)
                 ra[i][j] = ok ? __ldg(reinterpret_cast<const float4*>(src) + ld_q + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -260,66 +272,84 @@ k_gemm_tc(const __grid_constant__ Batch batch) {
         }
     };
     auto fetch_b = [&](int nt, int kc) {
-        if (SWAP) {
-            const int row = nt * TN + ld_row;                      // an activation row (output row)
-            const bool ok = row < m;
-            const float* src = a + (ok ? pr.amap(row) : 0) + kc * TK;
 #pragma unroll
-            for (int j = 0; j < TK / 16; ++j)
-                rbh[j] = ok ? __ldg(reinterpret_cast<const float4*>(src) + ld_q + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
-        } else {
-            const long long src = (long long)(nt * TN + ld_row) * k + kc * TK;
+        for (int i = 0; i < kRowSteps; ++i) {
+            if (SWAP) {
+                const int row = nt * TN + ld_row + 64 * i;             // an activation row (output row)
+                const bool ok = row < m;
+                const float* src = a + (ok ? amap(row) : 0) + kc * TK;
 #pragma unroll
-            for (int j = 0; j < TK / 16; ++j) {
-                rbh[j] = __ldg(reinterpret_cast<const float4*>(bt_hi + src) + ld_q + 4 * j);
-                rbl[j] = __ldg(reinterpret_cast<const float4*>(bt_lo + src) + ld_q + 4 * j);
+                for (int j = 0; j < TK / 16; ++j)
+                    rbh[i][j] = ok ? __ldg(reinterpret_cast<const float4*>(src) + ld_q + 4 * j)
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+            } else {
+                const long long src = (long long)(nt * TN + ld_row + 64 * i) * k + kc * TK;
+#pragma unroll
+                for (int j = 0; j < TK / 16; ++j) {
+                    rbh[i][j] = __ldg(reinterpret_cast<const float4*>(bt_hi + src) + ld_q + 4 * j);
+                    rbl[SWAP ? 0 : i][j] = __ldg(reinterpret_cast<const float4*>(bt_lo + src) + ld_q + 4 * j);
+                }
             }
         }
     };
     auto store_b = [&]() {
 #pragma unroll
-        for (int j = 0; j < TK / 16; ++j) {
-            const uint32_t off = tile_offset<TN>(ld_row, (ld_q + 4 * j) * 4);
-            if (SWAP) {
-                split_store(rbh[j], b_hi, b_lo, off);
-            } else {
-                *reinterpret_cast<float4*>(b_hi + off) = rbh[j];
-                *reinterpret_cast<float4*>(b_lo + off) = rbl[j];
+        for (int i = 0; i < kRowSteps; ++i)
+#pragma unroll
+            for (int j = 0; j < TK / 16; ++j) {
+                const uint32_t off = tile_offset<TN>(ld_row + 64 * i, (ld_q + 4 * j) * 4);
+                if (SWAP) {
+                    split_store(rbh[i][j], b_hi, b_lo, off);
+                } else {
+                    *reinterpret_cast<float4*>(b_hi + off) = rbh[i][j];
+                    *reinterpret_cast<float4*>(b_lo + off) = rbl[SWAP ? 0 : i][j];
+                }
             }
-        }
     };
-    // Accumulator rows live one per thread (TMEM lane); warps w and w + 4 share a lane quadrant and take 32 of the
-    // tile's 64 columns each: 128 contiguous bytes of one output row per thread.
+    // Accumulator rows live one per thread (TMEM lane); warps w and w + 4 share a lane quadrant and take half of the
+    // tile's columns each, 32 at a time.
     auto epilogue = [&](int nt) {
         const int quadrant = warp & 3, half = warp >> 2;
         const int row = row0 + quadrant * 32 + lane;
-        const uint32_t taddr = tmem_base + ((uint32_t)(quadrant * 32) << 16) + (uint32_t)((nt & 1) * TN + half * 32);
-        uint32_t v[32];
-        tmem_load_32(taddr, v);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (SWAP) {
-            // lane = output column row0 + quadrant * 32 + lane; v[j] belongs to output row nt * 64 + half * 32 + j
-            const int out_row0 = nt * TN + half * 32;
-            float* dst = pr.c + row;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const int r = out_row0 + j;
-                if (r < m) {
-                    float* d = dst + pr.cmap(r);
-                    *d = pr.accumulate ? *d + __uint_as_float(v[j]) : __uint_as_float(v[j]);
-                }
-            }
-        } else if (row < m && !(pr.batch_species && pr.batch_species[row / pr.cmap.nm] != pr.select)) {
-            float4* dst = reinterpret_cast<float4*>(pr.c + pr.cmap(row) + nt * TN + half * 32);
+        for (int cc = 0; cc < TN / 64; ++cc) {
+            const int col_in_tile = half * (TN / 2) + cc * 32;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quadrant * 32) << 16) + (uint32_t)((nt & 1) * TN + col_in_tile);
+            uint32_t v[32];
+            tmem_load_32(taddr, v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (SWAP) {
+                // lane = output column `row`; v[j] belongs to output row nt * TN + col_in_tile + j. Plain rows
+                // (c_nm == 1, checked on the host): one pointer walks down the column with the row stride.
+                const int out_row0 = nt * TN + col_in_tile;
+                const long long ldc = cmap.bs;
+                float* d = c_out + row + (long long)out_row0 * ldc;
+                const int live = m - out_row0;          // rows of this chunk that exist
+                if (accumulate) {
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                float4 o = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
-                                       __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
-                if (pr.accumulate) {
-                    const float4 old = dst[q];
-                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                    for (int j = 0; j < 32; ++j) {
+                        if (j < live) *d += __uint_as_float(v[j]);
+                        d += ldc;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (j < live) *d = __uint_as_float(v[j]);
+                        d += ldc;
+                    }
                 }
-                dst[q] = o;
+            } else if (row < m && !(batch_species && batch_species[row / cmap.nm] != select)) {
+                float4* dst = reinterpret_cast<float4*>(c_out + cmap(row) + nt * TN + col_in_tile);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    float4 o = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
+                                           __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+                    if (accumulate) {
+                        const float4 old = dst[q];
+                        o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                    }
+                    dst[q] = o;
+                }
             }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -393,6 +423,20 @@ k_gemm_tc(const __grid_constant__ Batch batch) {
     }
 }
 
+
+template <bool SWAP, int TN>
+int launch(const Batch& batch, int tiles, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        FMB_CUDA_CHECK(cudaFuncSetAttribute(k_gemm_tc<SWAP, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            smem_bytes<TN>()));
+        configured = true;
+    }
+    k_gemm_tc<SWAP, TN><<<tiles, kThreads, smem_bytes<TN>(), stream>>>(batch);
+    FMB_LAUNCH_CHECK();
+    return FMB_OK;
+}
+
 }  // namespace
 
 int gemm_tc_batch(const GemmArgs* list, int count, cudaStream_t stream) {
@@ -404,17 +448,22 @@ int gemm_tc_batch(const GemmArgs* list, int count, cudaStream_t stream) {
     for (int q = 0; q < count; ++q) {
         const GemmArgs& g = list[q];
         if (!g.bt_hi || !g.bt_lo) return FMB_ERR_UNSUPPORTED;
-        if (g.n % TN != 0 || g.k % TK != 0 || g.k < TK) return FMB_ERR_UNSUPPORTED;
+        if (g.n % 64 != 0 || g.k % TK != 0 || g.k < TK) return FMB_ERR_UNSUPPORTED;
         FMB_REQUIRE(g.a && g.c, "gemm_tc: null operand");
     }
-    // Wide outputs of a single K chunk (the radial weights) run with the operand roles swapped; all problems of a
-    // launch must agree.
+    // Wide outputs of a single K chunk (the radial weights) run with the operand roles swapped and 256 rows per MMA;
+    // the others take 128-column tiles when N allows. All problems of a launch must agree.
     auto wants_swap = [](const GemmArgs& g) {
-        return g.k == TK && g.n % TM == 0 && g.n >= 4 * TM && !g.batch_species && g.m >= 4 * TM;
+        return g.k == TK && g.n % TM == 0 && g.n >= 4 * TM && !g.batch_species && g.m >= 4 * TM && g.c_nm == 1 &&
+               g.a_nm == 1;
     };
     const bool swap = wants_swap(list[0]);
-    for (int q = 1; q < count; ++q)
+    bool wide = true;
+    for (int q = 0; q < count; ++q) {
         if (wants_swap(list[q]) != swap) return FMB_ERR_UNSUPPORTED;
+        if (list[q].n % 128 != 0) wide = false;
+    }
+    const int tn = swap ? 256 : (wide ? 128 : 64);
     long long row_tiles_total = 0;
     for (int q = 0; q < count; ++q) row_tiles_total += ceil_div(std::max(list[q].m, 0), TM);
     for (int q = 0; q < count; ++q) {
@@ -429,33 +478,23 @@ int gemm_tc_batch(const GemmArgs* list, int count, cudaStream_t stream) {
         p.batch_species = g.batch_species; p.select = g.select;
         p.tile_begin = tiles;
         if (swap) {
-            // CTA = (128-column tile, a run of about eight 64-row tiles)
-            const int row_tiles = ceil_div(std::max(g.m, 0), TN);
-            p.n_split = std::max(1, ceil_div(row_tiles, 8));
+            // CTA = (128-column tile, a run of about four 256-row tiles)
+            const int row_tiles = ceil_div(std::max(g.m, 0), tn);
+            p.n_split = std::max(1, ceil_div(row_tiles, 4));
             tiles += (g.n / TM) * p.n_split;
         } else {
             // split the column tiles over several CTAs when there are too few row tiles to fill the GPU
-            const int n_tiles = g.n / TN;
-            int split = (n_tiles + 4) / 5;                   // about five column tiles per CTA keeps the waves even
+            const int n_tiles = g.n / tn;
+            int split = (n_tiles + 4) / 5;
             if (row_tiles_total < 2 * sms) split = n_tiles;
             p.n_split = std::max(1, std::min(split, n_tiles));
             tiles += ceil_div(std::max(g.m, 0), TM) * p.n_split;
         }
     }
     if (tiles == 0) return FMB_OK;
-    static bool configured = false;
-    if (!configured) {
-        FMB_CUDA_CHECK(cudaFuncSetAttribute(k_gemm_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        FMB_CUDA_CHECK(cudaFuncSetAttribute(k_gemm_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        configured = true;
-    }
-    if (swap) {
-        k_gemm_tc<true><<<tiles, kThreads, kSmemBytes, stream>>>(batch);
-    } else {
-        k_gemm_tc<false><<<tiles, kThreads, kSmemBytes, stream>>>(batch);
-    }
-    FMB_LAUNCH_CHECK();
-    return FMB_OK;
+    if (swap) return launch<true, 256>(batch, tiles, stream);
+    if (tn == 128) return launch<false, 128>(batch, tiles, stream);
+    return launch<false, 64>(batch, tiles, stream);
 }
 
 int gemm_tc(const GemmArgs& g, cudaStream_t stream) {

@@ -139,5 +139,102 @@ def main() -> str:
     return OUT
 
 
+
+
+# --------------------------------------------------------------------------------------------- symmetric contraction
+SYMCON_OUT = os.path.join(HERE, "csrc", "generated", "symcon_generated.cuh")
+
+
+def _emit_symcon(l_out_max: int) -> str:
+    """Straight-line forward and backward of the contraction polynomial for outputs 0..l_out_max.
+
+    ``cf`` points at this thread's coefficient column: term t is ``cf[t * 128]`` (table order = so3.contraction_keys).
+    Products of a degree-2 prefix are shared by the degree-3 monomials that extend it, as in the reference's generated
+    kernels (fastmace/kernels/cuda/sc_generated.py:65-107)."""
+    keys = so3.contraction_keys(l_out_max)
+    n_out = (l_out_max + 1) ** 2
+    index = {key: t for t, key in enumerate(keys)}
+    by_mono: dict[tuple, list] = {}
+    for (m_out, nu, mono), t in index.items():
+        by_mono.setdefault(mono, []).append((m_out, t))
+    deg1 = sorted(m for m in by_mono if len(m) == 1)
+    deg2 = sorted(m for m in by_mono if len(m) == 2)
+    deg3 = sorted(m for m in by_mono if len(m) == 3)
+    prefixes = sorted({m[:2] for m in deg3} | set(deg2))
+    fwd = [f"template <> struct SymconShape<{l_out_max}> {{ static constexpr int kTerms = {len(keys)}; "
+           f"static constexpr int kOut = {n_out}; }};",
+           f"template <> __device__ __forceinline__ void symcon_forward_body<{l_out_max}>(const float (&x)[16], "
+           f"const float* __restrict__ cf, float (&y)[{n_out}]) {{"]
+
+    def consume(mono, expr, lines):
+        for m_out, t in sorted(by_mono.get(mono, ())):
+            lines.append(f"    y[{m_out}] = fmaf(__ldg(cf + {t * 128}), {expr}, y[{m_out}]);")
+
+    for mono in deg1:
+        consume(mono, f"x[{mono[0]}]", fwd)
+    for pre in prefixes:
+        fwd.append(f"    {{ const float p = x[{pre[0]}] * x[{pre[1]}];")
+        consume(pre, "p", fwd)
+        for mono in (m for m in deg3 if m[:2] == pre):
+            consume(mono, f"(p * x[{mono[2]}])", fwd)
+        fwd.append("    }")
+    fwd += ["}", ""]
+    bwd = [f"template <> __device__ __forceinline__ void symcon_backward_body<{l_out_max}>(const float (&x)[16], "
+           f"const float* __restrict__ cf, const float (&g)[{n_out}], float (&dx)[16]) {{"]
+
+    def adjoint(mono):
+        return " + ".join(f"__ldg(cf + {t * 128}) * g[{m_out}]" for m_out, t in sorted(by_mono[mono]))
+
+    for mono in deg1:
+        bwd.append(f"    dx[{mono[0]}] += {adjoint(mono)};")
+    for pre in prefixes:
+        i, j = pre
+        extended = any(m[:2] == pre for m in deg3)
+        bwd.append(f"    {{ {f'const float p = x[{i}] * x[{j}]; ' if extended else ''}float hp = 0.0f;")
+        if pre in by_mono:
+            bwd.append(f"      hp += {adjoint(pre)};")
+        for mono in (m for m in deg3 if m[:2] == pre):
+            k = mono[2]
+            bwd.append(f"      {{ const float h = {adjoint(mono)}; dx[{k}] = fmaf(h, p, dx[{k}]); hp = fmaf(h, x[{k}], hp); }}")
+        bwd.append(f"      dx[{i}] = fmaf(hp, x[{j}], dx[{i}]); dx[{j}] = fmaf(hp, x[{i}], dx[{j}]);")
+        bwd.append("    }")
+    bwd += ["}", ""]
+    return "\n".join(fwd + bwd)
+
+
+def render_symcon() -> str:
+    head = ["// GENERATED by fastmace_b200/codegen.py from fastmace_b200/so3.py -- do not edit.",
+            "// Symmetric contraction (correlation 3) of the 16 message components as a polynomial per (atom, channel):",
+            "// y[M] = sum_t coef[species][t][channel] * monomial_t(x), terms in the order of so3.contraction_keys.",
+            "#pragma once",
+            "",
+            "namespace fmb {",
+            "",
+            "template <int LOUT> struct SymconShape;",
+            "template <int LOUT> __device__ __forceinline__ void symcon_forward_body(const float (&x)[16], "
+            "const float* __restrict__ cf, float (&y)[(LOUT + 1) * (LOUT + 1)]);",
+            "template <int LOUT> __device__ __forceinline__ void symcon_backward_body(const float (&x)[16], "
+            "const float* __restrict__ cf, const float (&g)[(LOUT + 1) * (LOUT + 1)], float (&dx)[16]);",
+            ""]
+    return "\n".join(head + [_emit_symcon(l) for l in (0, 1, 2)] + ["}  // namespace fmb", ""])
+
+
+def _write(path: str, text: str) -> None:
+    os.makedirs(os.path.dirname(path), exist_ok=True)
+    old = open(path).read() if os.path.exists(path) else None
+    if old != text:
+        with open(path, "w") as handle:
+            handle.write(text)
+
+
+_tp_main = main
+
+
+def main() -> str:  # noqa: F811  (both generated headers)
+    out = _tp_main()
+    _write(SYMCON_OUT, render_symcon())
+    return out
+
+
 if __name__ == "__main__":
     print(main())

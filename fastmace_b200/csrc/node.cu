@@ -7,80 +7,49 @@
 // model precision, reduced in float64, E0 in float64).
 
 #include "stages.cuh"
+#include "generated/symcon_generated.cuh"
 
 namespace fmb {
 
 namespace {
 
-// terms: [T][4] = (i, j, k, m_out); j or k < 0 for lower degrees; sorted by m_out. coef: [species][T][C].
+// One thread per (atom, channel); the polynomial is generated straight-line code (generated/symcon_generated.cuh):
+// 16 inputs and the outputs live in registers, each coefficient is one coalesced load from the [species][term][C] table.
+template <int LOUT>
 __global__ void __launch_bounds__(kC)
-k_symcon_forward(int n_atoms, int n_terms, int out_dim, const int4* __restrict__ terms, const float* __restrict__ coef,
-                 const int32_t* __restrict__ species, const float* __restrict__ msg, float* __restrict__ basis) {
-    __shared__ float xs[kNSH][kC];
+k_symcon_forward(int n_atoms, int n_terms, const float* __restrict__ coef, const int32_t* __restrict__ species,
+                 const float* __restrict__ msg, float* __restrict__ basis) {
+    constexpr int OUT = SymconShape<LOUT>::kOut;
     const int a = blockIdx.x, c = threadIdx.x;
     if (a >= n_atoms) return;
+    float x[kNSH], y[OUT];
 #pragma unroll
-    for (int k = 0; k < kNSH; ++k) xs[k][c] = msg[((long long)a * kNSH + k) * kC + c];
-    // each thread only reads its own column: no barrier needed
-    const float* cf = coef + (long long)species[a] * n_terms * kC + c;
-    float acc = 0.0f;
-    int cur = 0;
-    for (int t = 0; t < n_terms; ++t) {
-        const int4 term = __ldg(terms + t);
-        if (term.w != cur) {
-            basis[((long long)a * out_dim + cur) * kC + c] = acc;
-            for (int m = cur + 1; m < term.w; ++m) basis[((long long)a * out_dim + m) * kC + c] = 0.0f;
-            acc = 0.0f;
-            cur = term.w;
-        }
-        float v = __ldg(cf + (long long)t * kC) * xs[term.x][c];
-        if (term.y >= 0) v *= xs[term.y][c];
-        if (term.z >= 0) v *= xs[term.z][c];
-        acc += v;
-    }
-    basis[((long long)a * out_dim + cur) * kC + c] = acc;
-    for (int m = cur + 1; m < out_dim; ++m) basis[((long long)a * out_dim + m) * kC + c] = 0.0f;
+    for (int k = 0; k < kNSH; ++k) x[k] = msg[((long long)a * kNSH + k) * kC + c];
+#pragma unroll
+    for (int k = 0; k < OUT; ++k) y[k] = 0.0f;
+    symcon_forward_body<LOUT>(x, coef + (long long)species[a] * n_terms * kC + c, y);
+#pragma unroll
+    for (int k = 0; k < OUT; ++k) basis[((long long)a * OUT + k) * kC + c] = y[k];
 }
 
+template <int LOUT>
 __global__ void __launch_bounds__(kC)
-k_symcon_backward(int n_atoms, int n_terms, int out_dim, const int4* __restrict__ terms, const float* __restrict__ coef,
-                  const int32_t* __restrict__ species, const float* __restrict__ msg, const float* __restrict__ d_basis,
-                  float* __restrict__ d_msg) {
-    __shared__ float xs[kNSH][kC];
-    __shared__ float dx[kNSH][kC];
+k_symcon_backward(int n_atoms, int n_terms, const float* __restrict__ coef, const int32_t* __restrict__ species,
+                  const float* __restrict__ msg, const float* __restrict__ d_basis, float* __restrict__ d_msg) {
+    constexpr int OUT = SymconShape<LOUT>::kOut;
     const int a = blockIdx.x, c = threadIdx.x;
     if (a >= n_atoms) return;
+    float x[kNSH], dx[kNSH], g[OUT];
 #pragma unroll
     for (int k = 0; k < kNSH; ++k) {
-        xs[k][c] = msg[((long long)a * kNSH + k) * kC + c];
-        dx[k][c] = 0.0f;
-    }
-    const float* cf = coef + (long long)species[a] * n_terms * kC + c;
-    int cur = -1;
-    float g = 0.0f;
-    for (int t = 0; t < n_terms; ++t) {
-        const int4 term = __ldg(terms + t);
-        if (term.w != cur) {
-            cur = term.w;
-            g = d_basis[((long long)a * out_dim + cur) * kC + c];
-        }
-        const float p = __ldg(cf + (long long)t * kC) * g;
-        const float xi = xs[term.x][c];
-        if (term.y < 0) {
-            dx[term.x][c] += p;
-        } else if (term.z < 0) {
-            const float xj = xs[term.y][c];
-            dx[term.x][c] += p * xj;
-            dx[term.y][c] += p * xi;
-        } else {
-            const float xj = xs[term.y][c], xk = xs[term.z][c];
-            dx[term.x][c] += p * xj * xk;
-            dx[term.y][c] += p * xi * xk;
-            dx[term.z][c] += p * xi * xj;
-        }
+        x[k] = msg[((long long)a * kNSH + k) * kC + c];
+        dx[k] = 0.0f;
     }
 #pragma unroll
-    for (int k = 0; k < kNSH; ++k) d_msg[((long long)a * kNSH + k) * kC + c] = dx[k][c];
+    for (int k = 0; k < OUT; ++k) g[k] = d_basis[((long long)a * OUT + k) * kC + c];
+    symcon_backward_body<LOUT>(x, coef + (long long)species[a] * n_terms * kC + c, g, dx);
+#pragma unroll
+    for (int k = 0; k < kNSH; ++k) d_msg[((long long)a * kNSH + k) * kC + c] = dx[k];
 }
 
 // h[a][k][c] = table[species[a]][k][c]  (layer 0's species-only skip connection)
@@ -220,15 +189,32 @@ __global__ void k_commit(int n3, const float* __restrict__ forces, const double*
 
 int symcon_forward(int n_atoms, int n_terms, int out_dim, const int32_t* terms, const float* coef,
                    const int32_t* species, const float* msg, float* basis, cudaStream_t stream) {
-    k_symcon_forward<<<n_atoms, kC, 0, stream>>>(n_atoms, n_terms, out_dim, (const int4*)terms, coef, species, msg, basis);
+    (void)terms;
+#define FMB_SYM(L_)                                                                                              \
+    {                                                                                                            \
+        FMB_REQUIRE(n_terms == SymconShape<L_>::kTerms, "symcon: coefficient table does not match the kernel"); \
+        k_symcon_forward<L_><<<n_atoms, kC, 0, stream>>>(n_atoms, n_terms, coef, species, msg, basis);           \
+    }
+    if (out_dim == 1) FMB_SYM(0) else if (out_dim == 4) FMB_SYM(1) else if (out_dim == 9) FMB_SYM(2) else {
+        FMB_REQUIRE(false, "symcon: unsupported output irreps");
+    }
+#undef FMB_SYM
     FMB_LAUNCH_CHECK();
     return FMB_OK;
 }
 
 int symcon_backward(int n_atoms, int n_terms, int out_dim, const int32_t* terms, const float* coef,
                     const int32_t* species, const float* msg, const float* d_basis, float* d_msg, cudaStream_t stream) {
-    k_symcon_backward<<<n_atoms, kC, 0, stream>>>(n_atoms, n_terms, out_dim, (const int4*)terms, coef, species, msg,
-                                                  d_basis, d_msg);
+    (void)terms;
+#define FMB_SYM(L_)                                                                                                  \
+    {                                                                                                                \
+        FMB_REQUIRE(n_terms == SymconShape<L_>::kTerms, "symcon: coefficient table does not match the kernel");     \
+        k_symcon_backward<L_><<<n_atoms, kC, 0, stream>>>(n_atoms, n_terms, coef, species, msg, d_basis, d_msg);     \
+    }
+    if (out_dim == 1) FMB_SYM(0) else if (out_dim == 4) FMB_SYM(1) else if (out_dim == 9) FMB_SYM(2) else {
+        FMB_REQUIRE(false, "symcon: unsupported output irreps");
+    }
+#undef FMB_SYM
     FMB_LAUNCH_CHECK();
     return FMB_OK;
 }

@@ -60,6 +60,8 @@ def contraction_terms(spec: MaceSpec, weights, layer: int, species_z):
                 else:
                     merged[key] = value
     keys = sorted(merged)
+    if tuple(keys) != so3.contraction_keys(spec.l_out_max(layer), spec.correlation, spec.sh_lmax):
+        raise RuntimeError("contraction terms are not in the order the generated kernels expect")
     terms = np.full((len(keys), 4), -1, dtype=np.int32)
     coefs = np.zeros((len(species_z), len(keys), c), dtype=np.float64)
     for t, key in enumerate(keys):

@@ -282,6 +282,19 @@ def contraction_polynomial(correlation: int, l_out: int, l_in_max: int = LMAX_SH
     return monomials, m_out, weight, coefficient, len(trees)
 
 
+@functools.lru_cache(maxsize=None)
+def contraction_keys(l_out_max: int, correlation: int = 3, l_in_max: int = LMAX_SH):
+    """Sorted (output component, degree, sorted monomial) keys of the contraction polynomial for outputs 0..l_out_max:
+    the order of the per-(species, channel) coefficient table and of the generated kernels."""
+    keys = set()
+    for big_l in range(l_out_max + 1):
+        for nu in range(1, correlation + 1):
+            mono, m_out, _, _, _ = contraction_polynomial(nu, big_l, l_in_max)
+            for t in range(len(m_out)):
+                keys.add((big_l * big_l + int(m_out[t]), nu, tuple(int(i) for i in mono[t])))
+    return tuple(sorted(keys))
+
+
 def num_contraction_weights(correlation: int, l_out: int, l_in_max: int = LMAX_SH) -> int:
     return len(coupling_trees(correlation, l_out, l_in_max))
 
@@ -296,5 +309,5 @@ def random_rotation(seed: int) -> np.ndarray:
 
 
 __all__ = ["real_sh", "sh_l", "wigner_d", "wigner_3j", "tp_paths", "mid_dim", "paths_into", "coupling_trees",
-           "contraction_polynomial", "num_contraction_weights", "natural_parity", "sh_offset", "random_rotation",
+           "contraction_polynomial", "contraction_keys", "num_contraction_weights", "natural_parity", "sh_offset", "random_rotation",
            "NSH", "LMAX_SH"]

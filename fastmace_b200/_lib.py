@@ -26,7 +26,7 @@ STATUS_TENSOR_TIMEOUT = 16
 EXPORTS = ("fmb_version", "fmb_last_error", "fmb_sizeof", "fmb_launch_count", "fmb_nl_build", "fmb_nl_compact", "fmb_nl_compact_static",
            "fmb_nl_needs_rebuild",
            "fmb_forces", "fmb_edge_features", "fmb_forward", "fmb_backward", "fmb_gemm", "fmb_langevin_first_half",
-           "fmb_langevin_second_half", "fmb_commit_forces", "fmb_profile_enable", "fmb_profile_read")
+           "fmb_langevin_second_half", "fmb_langevin_device_noise", "fmb_commit_forces", "fmb_profile_enable", "fmb_profile_read")
 
 
 class Fmb200Error(RuntimeError):
@@ -76,6 +76,7 @@ class WorkStruct(ctypes.Structure):
         ("h", c_void_p), ("d_h", c_void_p), ("d_basis", c_void_p), ("d_msg", c_void_p), ("d_mid", c_void_p),
         ("d_x", c_void_p), ("node_energy", c_void_p), ("atom_virial", c_void_p), ("force_acc", c_void_p),
         ("partial", c_void_p), ("energy", c_void_p), ("forces", c_void_p), ("stress", c_void_p), ("status", c_void_p),
+        ("n_energy_atoms", c_int32), ("n_inner_atoms", c_int32),
     ]
 
 
@@ -123,6 +124,7 @@ def load() -> ctypes.CDLL:
     lib.fmb_gemm.argtypes = [P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P]
     lib.fmb_langevin_first_half.argtypes = [POINTER(LangevinStruct), P]
     lib.fmb_langevin_second_half.argtypes = [POINTER(LangevinStruct), P]
+    lib.fmb_langevin_device_noise.argtypes = [P, c_int, ctypes.c_ulonglong, P, P]
     lib.fmb_commit_forces.argtypes = [POINTER(WorkStruct), P, P, P, P]
     lib.fmb_profile_enable.argtypes = [c_int]
     lib.fmb_profile_read.argtypes = [POINTER(c_float), POINTER(c_int), c_int]

@@ -80,7 +80,9 @@ struct Ctx {
     const fmb_nl_t* nl;
     const fmb_work_t* w;
     cudaStream_t stream;
-    int n;
+    int n;               // atoms of the list
+    int n0;              // atoms that get first-layer rows (owned + inner halo; = n without domain decomposition)
+    int n1;              // owned atoms: last-layer rows and energy
     int hidden_dim;      // components of h after layer 0
     long long count_cap; // entries of the edge buffers
     int n_chunks;
@@ -129,7 +131,7 @@ struct LinearBatch {
 };
 
 // `twin`: base of the weight array's tensor-core twin (or null); the block's twin starts at twice its float offset
-void block_linear(LinearBatch& batch, const Ctx& c, const float* in, long long in_atom, long long in_off, int k,
+void block_linear(LinearBatch& batch, const Ctx& c, int rows, const float* in, long long in_atom, long long in_off, int k,
                   const float* base, const float* twin, long long w_off, float* out, long long out_atom,
                   long long out_off, int n_out, int l, int accumulate, const int32_t* batch_species = nullptr,
                   int select = -1) {
@@ -145,7 +147,7 @@ void block_linear(LinearBatch& batch, const Ctx& c, const float* in, long long i
     g.error_word = c.w->status;
     g.c = out + out_off;
     g.c_nm = nm; g.c_bs = out_atom; g.c_rs = n_out;
-    g.m = c.n * nm; g.n = n_out; g.k = k;
+    g.m = rows * nm; g.n = n_out; g.k = k;
     g.accumulate = accumulate;
     g.batch_species = batch_species;
     g.select = select;
@@ -178,9 +180,10 @@ int forward_layer(const Ctx& c, int layer) {
     const int in_dim = dim_of(L.l_in_max), out_dim = dim_of(L.l_out_max);
     float* h_out = h_of(c, layer);
     const float* x = nullptr;
+    const int rows = layer == 0 ? c.n0 : c.n1;     // atoms that get this layer's outputs
     LinearBatch lb;
     if (layer == 0) {
-        FMB_TRY(fill_from_species(c.n, out_dim * kC, c.w->species, L.sc_species, h_out, c.stream));
+        FMB_TRY(fill_from_species(rows, out_dim * kC, c.w->species, L.sc_species, h_out, c.stream));
         x = L.x_species;
     } else {
         const float* h_in = h_of(c, layer - 1);
@@ -188,11 +191,11 @@ int forward_layer(const Ctx& c, int layer) {
         // species-dependent skip: one row-masked GEMM per present species and irrep, each row written exactly once
         for (int l = 0; l <= L.skip_lmax; ++l)
             for (int z = 0; z < c.m->n_species; ++z)
-                block_linear(lb, c, h_in, (long long)h_in_dim * kC, (long long)l * l * kC, kC, L.w_skip, L.tc[3],
+                block_linear(lb, c, rows, h_in, (long long)h_in_dim * kC, (long long)l * l * kC, kC, L.w_skip, L.tc[3],
                              ((long long)l * c.m->n_species + z) * kC * kC, h_out, (long long)out_dim * kC,
                              (long long)l * l * kC, kC, l, 0, c.w->species, z);
         for (int l = 0; l <= L.l_in_max; ++l)
-            block_linear(lb, c, h_in, (long long)h_in_dim * kC, (long long)l * l * kC, kC, L.w_up, L.tc[1],
+            block_linear(lb, c, c.n0, h_in, (long long)h_in_dim * kC, (long long)l * l * kC, kC, L.w_up, L.tc[1],
                          (long long)l * kC * kC, c.w->x, (long long)in_dim * kC, (long long)l * l * kC, kC, l, 0);
         FMB_TRY(run_linears(c, lb));
         x = c.w->x;
@@ -201,7 +204,7 @@ int forward_layer(const Ctx& c, int layer) {
         const long long e0 = (long long)k * c.chunk;
         FMB_TRY(radial_weights(c, layer, e0, false));
         TpArgs t{};
-        t.lin = L.l_in_max; t.species_x = layer == 0; t.n_atoms = c.n;
+        t.lin = L.l_in_max; t.species_x = layer == 0; t.n_atoms = c.n; t.n_rows = rows;
         t.chunk_e0 = e0; t.chunk_edges = c.chunk;
         t.count = (const long long*)c.nl->count; t.row_ptr = c.nl->edge_row_ptr; t.senders = c.nl->edge_index;
         t.species = c.w->species; t.x = x; t.edge_sh = c.w->edge_sh; t.tp_w = c.w->tp_w; t.mid = c.w->mid;
@@ -210,16 +213,16 @@ int forward_layer(const Ctx& c, int layer) {
     }
     float* msg = msg_of(c, layer);
     for (int l = 0; l <= 3; ++l)
-        block_linear(lb, c, c.w->mid, (long long)ml.mid_dim * kC, (long long)ml.base[l] * kC, ml.segs[l] * kC, L.w_lin,
+        block_linear(lb, c, rows, c.w->mid, (long long)ml.mid_dim * kC, (long long)ml.base[l] * kC, ml.segs[l] * kC, L.w_lin,
                      L.tc[5], lin_weight_offset(ml, l), msg, (long long)kNSH * kC, (long long)l * l * kC, kC, l, 0);
     FMB_TRY(run_linears(c, lb));
     {
         StageScope scope(c.stream, kStSymFwd);
-        FMB_TRY(symcon_forward(c.n, L.n_sc_terms, out_dim, L.sc_terms, L.sc_coef, c.w->species, msg, c.w->basis,
+        FMB_TRY(symcon_forward(rows, L.n_sc_terms, out_dim, L.sc_terms, L.sc_coef, c.w->species, msg, c.w->basis,
                                c.stream));
     }
     for (int l = 0; l <= L.l_out_max; ++l)
-        block_linear(lb, c, c.w->basis, (long long)out_dim * kC, (long long)l * l * kC, kC, L.w_prod, L.tc[7],
+        block_linear(lb, c, rows, c.w->basis, (long long)out_dim * kC, (long long)l * l * kC, kC, L.w_prod, L.tc[7],
                      (long long)l * kC * kC, h_out, (long long)out_dim * kC, (long long)l * l * kC, kC, l, 1);
     FMB_TRY(run_linears(c, lb));
     return FMB_OK;
@@ -231,25 +234,26 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
     const fmb_layer_t& L = c.m->layer[layer];
     const MidLayout ml = mid_layout(L.l_in_max);
     const int in_dim = dim_of(L.l_in_max), out_dim = dim_of(L.l_out_max);
+    const int rows = layer == 0 ? c.n0 : c.n1;     // atoms whose outputs of this layer carry a gradient
     LinearBatch lb;
     for (int l = 0; l <= L.l_out_max; ++l)
-        block_linear(lb, c, d_h_out, (long long)out_dim * kC, (long long)l * l * kC, kC, L.w_prod_t, L.tc[8],
+        block_linear(lb, c, rows, d_h_out, (long long)out_dim * kC, (long long)l * l * kC, kC, L.w_prod_t, L.tc[8],
                      (long long)l * kC * kC, c.w->d_basis, (long long)out_dim * kC, (long long)l * l * kC, kC, l, 0);
     if (layer > 0) {
         for (int l = 0; l <= L.skip_lmax; ++l)
             for (int z = 0; z < c.m->n_species; ++z)
-                block_linear(lb, c, d_h_out, (long long)out_dim * kC, (long long)l * l * kC, kC, L.w_skip_t, L.tc[4],
+                block_linear(lb, c, rows, d_h_out, (long long)out_dim * kC, (long long)l * l * kC, kC, L.w_skip_t, L.tc[4],
                              ((long long)l * c.m->n_species + z) * kC * kC, d_h_in, (long long)c.hidden_dim * kC,
                              (long long)l * l * kC, kC, l, 1, c.w->species, z);
     }
     FMB_TRY(run_linears(c, lb));
     {
         StageScope scope(c.stream, kStSymBwd);
-        FMB_TRY(symcon_backward(c.n, L.n_sc_terms, out_dim, L.sc_terms, L.sc_coef, c.w->species, msg_of(c, layer),
+        FMB_TRY(symcon_backward(rows, L.n_sc_terms, out_dim, L.sc_terms, L.sc_coef, c.w->species, msg_of(c, layer),
                                 c.w->d_basis, c.w->d_msg, c.stream));
     }
     for (int l = 0; l <= 3; ++l)
-        block_linear(lb, c, c.w->d_msg, (long long)kNSH * kC, (long long)l * l * kC, kC, L.w_lin_t, L.tc[6],
+        block_linear(lb, c, rows, c.w->d_msg, (long long)kNSH * kC, (long long)l * l * kC, kC, L.w_lin_t, L.tc[6],
                      lin_weight_offset(ml, l), c.w->d_mid, (long long)ml.mid_dim * kC, (long long)ml.base[l] * kC,
                      ml.segs[l] * kC, l, 0);
     FMB_TRY(run_linears(c, lb));
@@ -258,6 +262,8 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
         FMB_TRY(radial_weights(c, layer, e0, true));
         TpArgs t{};
         t.lin = L.l_in_max; t.species_x = layer == 0; t.n_atoms = c.n;
+        // every atom that sends into a row with a gradient gets a force; first-layer senders are all atoms
+        t.n_rows = layer == 0 ? c.n : c.n0; t.n_valid = rows; t.fresh_from = layer == 0 ? c.n0 : 0;
         t.chunk_e0 = e0; t.chunk_edges = c.chunk; t.tangent_offset = c.chunk * L.n_paths * kC;
         t.count = (const long long*)c.nl->count; t.row_ptr = c.nl->edge_row_ptr; t.senders = c.nl->edge_index;
         t.species = c.w->species; t.x = layer == 0 ? L.x_species : c.w->x;
@@ -269,7 +275,7 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
     }
     if (layer > 0) {
         for (int l = 0; l <= L.l_in_max; ++l)
-            block_linear(lb, c, c.w->d_x, (long long)in_dim * kC, (long long)l * l * kC, kC, L.w_up_t, L.tc[2],
+            block_linear(lb, c, c.n0, c.w->d_x, (long long)in_dim * kC, (long long)l * l * kC, kC, L.w_up_t, L.tc[2],
                          (long long)l * kC * kC, d_h_in, (long long)c.hidden_dim * kC, (long long)l * l * kC, kC, l, 1);
         FMB_TRY(run_linears(c, lb));
     }
@@ -286,6 +292,9 @@ int make_ctx(Ctx& c, const fmb_model_t* m, const fmb_nl_t* nl, const fmb_work_t*
     FMB_REQUIRE(w->chunk_edges > 0, "forces: chunk_edges must be positive");
     c.m = m; c.nl = nl; c.w = w; c.stream = stream;
     c.n = w->n_atoms;
+    c.n1 = w->n_energy_atoms > 0 ? w->n_energy_atoms : c.n;
+    c.n0 = w->n_inner_atoms > 0 ? w->n_inner_atoms : c.n;
+    FMB_REQUIRE(c.n1 <= c.n0 && c.n0 <= c.n, "forces: owned <= inner <= all atoms");
     c.hidden_dim = dim_of(m->hidden_lmax);
     c.count_cap = nl->capacity;
     c.chunk = std::min<long long>(w->chunk_edges, nl->capacity);
@@ -319,7 +328,7 @@ extern "C" FMB_API int fmb_forward(const fmb_model_t* model, const fmb_nl_t* nl,
     FMB_TRY(forward_layer(c, 1));
     // readout; the gradient of the last layer's scalars is parked in `basis` (free after the forward pass)
     StageScope scope(c.stream, kStReadout);
-    FMB_TRY(readout(model, c.n, h_of(c, 0), h_of(c, 1), work->node_energy, work->d_h, work->basis, c.stream));
+    FMB_TRY(readout(model, c.n0, c.n1, h_of(c, 0), h_of(c, 1), work->node_energy, work->d_h, work->basis, c.stream));
     return FMB_OK;
 }
 
@@ -329,7 +338,7 @@ extern "C" FMB_API int fmb_backward(const fmb_model_t* model, const fmb_nl_t* nl
     FMB_TRY(backward_layer(c, 1, work->basis, work->d_h, 1));
     FMB_TRY(backward_layer(c, 0, work->d_h, nullptr, 0));
     StageScope scope(c.stream, kStReadout);
-    FMB_TRY(reduce_outputs(model, work, cell_volume(nl), c.stream));
+    FMB_TRY(reduce_outputs(model, work, c.n1, cell_volume(nl), c.stream));
     return FMB_OK;
 }
 

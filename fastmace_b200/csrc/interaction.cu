@@ -55,7 +55,7 @@ __device__ __forceinline__ void load_sh(const float* __restrict__ edge_sh, long 
 // ---------------------------------------------------------------------------------------------- forward
 template <int LIN, bool SPECIES_X>
 __global__ void __launch_bounds__(kC)
-k_tp_forward(int n_atoms, long long chunk_e0, long long chunk_edges, const long long* __restrict__ count_ptr,
+k_tp_forward(int n_atoms, int n_rows, long long chunk_e0, long long chunk_edges, const long long* __restrict__ count_ptr,
              const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ senders,
              const int32_t* __restrict__ species, const float* __restrict__ x, const float* __restrict__ edge_sh,
              const float* __restrict__ tp_w, float* __restrict__ mid) {
@@ -65,7 +65,7 @@ k_tp_forward(int n_atoms, long long chunk_e0, long long chunk_edges, const long 
     if (e0 >= e1 && !(e0 == 0 && count == 0)) return;
     const int c = threadIdx.x;
     const int first = (e0 == 0) ? 0 : chunk_first_row(row_ptr, n_atoms, e0);
-    for (int i = first + blockIdx.x; i < n_atoms; i += gridDim.x) {
+    for (int i = first + blockIdx.x; i < n_rows; i += gridDim.x) {
         const long long rb = row_ptr[i], re = row_ptr[i + 1];
         if (rb >= e1 && e1 < count) break;   // rows of later chunks (the last chunk also zeroes trailing empty rows)
         float acc[MID];
@@ -154,7 +154,7 @@ __device__ __forceinline__ void edge_vector_gradient(const float* g, float dr, f
 
 template <int LIN, bool SPECIES_X, bool NEED_DX>
 __global__ void __launch_bounds__(kC)
-k_tp_backward(int n_atoms, long long chunk_e0, long long chunk_edges, long long tangent_offset,
+k_tp_backward(int n_atoms, int n_rows, int n_valid, int fresh_from, long long chunk_e0, long long chunk_edges, long long tangent_offset,
               const long long* __restrict__ count_ptr, const int32_t* __restrict__ row_ptr,
               const int32_t* __restrict__ senders, const int32_t* __restrict__ species, const float* __restrict__ x,
               const float* __restrict__ edge_sh, const float* __restrict__ edge_vec, const float* __restrict__ tp_w,
@@ -167,13 +167,13 @@ k_tp_backward(int n_atoms, long long chunk_e0, long long chunk_edges, long long 
     const int c = threadIdx.x, warp = c >> 5, lane = c & 31;
     if (e0 >= e1 && !(e0 == 0 && count == 0)) return;
     const int first = (e0 == 0) ? 0 : chunk_first_row(row_ptr, n_atoms, e0);
-    for (int a = first + blockIdx.x; a < n_atoms; a += gridDim.x) {
+    for (int a = first + blockIdx.x; a < n_rows; a += gridDim.x) {
         const long long rb = row_ptr[a], re = row_ptr[a + 1];
         if (rb >= e1 && e1 < count) break;
         const bool continued = rb < e0;     // this row started in an earlier chunk: accumulate onto its partial sums
         float g_a[MID], x_a[IN], dx[IN];
 #pragma unroll
-        for (int k = 0; k < MID; ++k) g_a[k] = __ldg(d_mid + ((long long)a * MID + k) * kC + c);
+        for (int k = 0; k < MID; ++k) g_a[k] = a < n_valid ? __ldg(d_mid + ((long long)a * MID + k) * kC + c) : 0.0f;
         if (SPECIES_X) {
             x_a[0] = __ldg(x + (long long)species[a] * kC + c);
         } else {
@@ -213,7 +213,9 @@ k_tp_backward(int n_atoms, long long chunk_e0, long long chunk_edges, long long 
                 {
                     float g_j[MID];
 #pragma unroll
-                    for (int q = 0; q < MID; ++q) g_j[q] = __ldg(d_mid + ((long long)j * MID + q) * kC + c);
+                    // rows at or beyond n_valid carry no gradient (atoms whose energy another domain owns)
+                    for (int q = 0; q < MID; ++q)
+                        g_j[q] = j < n_valid ? __ldg(d_mid + ((long long)j * MID + q) * kC + c) : 0.0f;
                     TpBackward<LIN, true, NEED_DX>::run(x_a, Y, w, wp, g_j, dY, dr, dx);
                 }
                 warp_reduce16(dY);
@@ -250,7 +252,7 @@ k_tp_backward(int n_atoms, long long chunk_e0, long long chunk_edges, long long 
                 for (int q = 0; q < 6; ++q) vir[q] += __shfl_xor_sync(0xffffffffu, vir[q], o);
             }
             if (lane == 0) {
-                const bool fresh = first_layer_of_pass && !continued;
+                const bool fresh = (first_layer_of_pass || a >= fresh_from) && !continued;
 #pragma unroll
                 for (int q = 0; q < 3; ++q)
                     force_acc[3 * a + q] = (fresh ? 0.0f : force_acc[3 * a + q]) + fsum[q];
@@ -285,11 +287,12 @@ int persistent_grid(const void* kernel, int n_atoms) {
 }  // namespace
 
 int tp_forward_launch(const TpArgs& t, cudaStream_t stream) {
+    if (t.n_rows <= 0) return FMB_OK;
 #define FMB_FWD(LIN_, SP_)                                                                                             \
     {                                                                                                                  \
         auto kernel = k_tp_forward<LIN_, SP_>;                                                                         \
-        const int grid = persistent_grid((const void*)kernel, t.n_atoms);                                                           \
-        kernel<<<grid, kC, 0, stream>>>(t.n_atoms, t.chunk_e0, t.chunk_edges, t.count, t.row_ptr, t.senders,           \
+        const int grid = persistent_grid((const void*)kernel, t.n_rows);                                                           \
+        kernel<<<grid, kC, 0, stream>>>(t.n_atoms, t.n_rows, t.chunk_e0, t.chunk_edges, t.count, t.row_ptr, t.senders, \
                                         t.species, t.x, t.edge_sh, t.tp_w, t.mid);                                     \
     }
     if (t.species_x) {
@@ -310,11 +313,13 @@ int tp_forward_launch(const TpArgs& t, cudaStream_t stream) {
 }
 
 int tp_backward_launch(const TpArgs& t, cudaStream_t stream) {
+    if (t.n_rows <= 0) return FMB_OK;
 #define FMB_BWD(LIN_, SP_, DX_)                                                                                        \
     {                                                                                                                  \
         auto kernel = k_tp_backward<LIN_, SP_, DX_>;                                                                   \
-        const int grid = persistent_grid((const void*)kernel, t.n_atoms);                                                           \
-        kernel<<<grid, kC, 0, stream>>>(t.n_atoms, t.chunk_e0, t.chunk_edges, t.tangent_offset, t.count, t.row_ptr,    \
+        const int grid = persistent_grid((const void*)kernel, t.n_rows);                                                           \
+        kernel<<<grid, kC, 0, stream>>>(t.n_atoms, t.n_rows, t.n_valid, t.fresh_from, t.chunk_e0, t.chunk_edges,       \
+                                        t.tangent_offset, t.count, t.row_ptr,                                         \
                                         t.senders, t.species, t.x, t.edge_sh, t.edge_vec, t.tp_w, t.d_mid, t.d_x,      \
                                         t.force_acc, t.atom_virial, t.first_layer_of_pass);                            \
     }

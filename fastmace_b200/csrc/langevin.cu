@@ -110,11 +110,70 @@ k_second_half(fmb_langevin_t lv) {
     }
 }
 
+// Counter-based normal deviates (Philox4x32-10 + Box-Muller in float64): one (seed, step, atom) triple always yields
+// the same six numbers, so every rank of a domain-decomposed run draws identical noise without communication and
+// without the host generator, whose draw of 6 N normals per step is the bottleneck beyond ~10^5 atoms.
+__device__ __forceinline__ void philox_round(uint32_t (&c)[4], uint32_t k0, uint32_t k1) {
+    const uint64_t p0 = (uint64_t)0xD2511F53u * c[0], p1 = (uint64_t)0xCD9E8D57u * c[2];
+    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c[1] ^ k0, n2 = (uint32_t)(p0 >> 32) ^ c[3] ^ k1;
+    c[0] = n0; c[1] = (uint32_t)p1; c[2] = n2; c[3] = (uint32_t)p0;
+}
+
+__device__ __forceinline__ void philox(uint32_t (&c)[4], uint32_t k0, uint32_t k1) {
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        philox_round(c, k0, k1);
+        k0 += 0x9E3779B9u;
+        k1 += 0xBB67AE85u;
+    }
+}
+
+__device__ __forceinline__ void box_muller(uint32_t a, uint32_t b, uint32_t c, uint32_t d, double& z0, double& z1) {
+    const double u1 = ((double)(((uint64_t)(a >> 5) << 26) | (uint64_t)(b >> 6)) + 0.5) * (1.0 / 9007199254740992.0);
+    const double u2 = ((double)(((uint64_t)(c >> 5) << 26) | (uint64_t)(d >> 6)) + 0.5) * (1.0 / 9007199254740992.0);
+    const double r = sqrt(-2.0 * log(u1));
+    double sn, cs;
+    sincospi(2.0 * u2, &sn, &cs);
+    z0 = r * cs;
+    z1 = r * sn;
+}
+
+__global__ void __launch_bounds__(256)
+k_device_noise(int n, unsigned long long seed, const int32_t* __restrict__ step, double* __restrict__ row) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+    double z[8];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        uint32_t c[4] = {(uint32_t)i, (uint32_t)*step, (uint32_t)h, 0x6d616365u};
+        philox(c, k0, k1);
+        uint32_t e[4] = {(uint32_t)i, (uint32_t)*step, (uint32_t)(h + 2), 0x6d616365u};
+        philox(e, k0, k1);
+        box_muller(c[0], c[1], c[2], c[3], z[4 * h + 0], z[4 * h + 1]);
+        box_muller(e[0], e[1], e[2], e[3], z[4 * h + 2], z[4 * h + 3]);
+    }
+    // xi then eta, [2][n][3]
+#pragma unroll
+    for (int a = 0; a < 3; ++a) {
+        row[3 * i + a] = z[a];
+        row[3 * (long long)n + 3 * i + a] = z[4 + a];
+    }
+}
+
 }  // namespace
 
 }  // namespace fmb
 
 using namespace fmb;
+
+extern "C" FMB_API int fmb_langevin_device_noise(double* noise_row, int n_atoms, unsigned long long seed,
+                                                 const int32_t* step_counter, fmb_stream_t stream_) {
+    FMB_REQUIRE(noise_row && step_counter && n_atoms > 0, "fmb_langevin_device_noise: bad argument");
+    k_device_noise<<<ceil_div(n_atoms, 256), 256, 0, (cudaStream_t)stream_>>>(n_atoms, seed, step_counter, noise_row);
+    FMB_LAUNCH_CHECK();
+    return FMB_OK;
+}
 
 extern "C" FMB_API int fmb_langevin_first_half(const fmb_langevin_t* lv, fmb_stream_t stream_) {
     FMB_REQUIRE(lv && lv->n_atoms > 1, "fmb_langevin_first_half: bad argument");

@@ -64,13 +64,20 @@ __global__ void k_fill_from_species(int n_atoms, int row, const int32_t* __restr
 // One warp per atom. Non-last layers: e += h[a][0][:] . w, gradient w. Last layer: 128 -> 16 -> SiLU -> 1 with its
 // gradient. The energy scale is folded in here. mode bit 0: add to node_energy instead of overwriting.
 __global__ void __launch_bounds__(128)
-k_readout(int n_atoms, int dim_first, int dim_last, int mlp_hidden, float scale, float shift, float silu_norm,
+k_readout(int n_atoms, int n_energy, int dim_first, int dim_last, int mlp_hidden, float scale, float shift, float silu_norm,
           const float* __restrict__ h_first, const float* __restrict__ h_last, const float* __restrict__ w_first,
           const float* __restrict__ w_last0, const float* __restrict__ w_last1, float* __restrict__ node_energy,
           float* __restrict__ d_h_first, float* __restrict__ d_h_last) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int a = blockIdx.x * 4 + warp;
     if (a >= n_atoms) return;
+    if (a >= n_energy) {
+        // an atom whose energy belongs to another domain: it contributes no energy and seeds no gradient
+        float* df = d_h_first + (long long)a * dim_first * kC;
+        for (int k = lane; k < dim_first * kC; k += 32) df[k] = 0.0f;
+        if (lane == 0) node_energy[a] = 0.0f;
+        return;
+    }
     // first readout (linear) and the gradient it leaves on h_first's scalars; other components start at zero
     float e = 0.0f;
     const float* hf = h_first + (long long)a * dim_first * kC;
@@ -124,7 +131,7 @@ struct E0Table {
 
 // partial[b][0] = sum of node energies (+E0) of block b's atoms, partial[b][1..6] = virial components; float64.
 __global__ void __launch_bounds__(256)
-k_reduce_partial(int n_atoms, const float* __restrict__ node_energy, const int32_t* __restrict__ species,
+k_reduce_partial(int n_atoms, int n_energy, const float* __restrict__ node_energy, const int32_t* __restrict__ species,
                  E0Table e0, const float* __restrict__ atom_virial,
                  double* __restrict__ partial) {
     __shared__ double sh[8][7];
@@ -132,7 +139,7 @@ k_reduce_partial(int n_atoms, const float* __restrict__ node_energy, const int32
     const int per_block = (n_atoms + gridDim.x - 1) / gridDim.x;
     const int begin = blockIdx.x * per_block, end = min(n_atoms, begin + per_block);
     for (int a = begin + threadIdx.x; a < end; a += blockDim.x) {
-        acc[0] += (double)node_energy[a] + e0.v[species[a]];
+        if (a < n_energy) acc[0] += (double)node_energy[a] + e0.v[species[a]];
         if (atom_virial) {
 #pragma unroll
             for (int q = 0; q < 6; ++q) acc[1 + q] += (double)atom_virial[6 * a + q];
@@ -226,22 +233,22 @@ int fill_from_species(int n_atoms, int row, const int32_t* species, const float*
     return FMB_OK;
 }
 
-int readout(const fmb_model_t* m, int n_atoms, const float* h_first, const float* h_last, float* node_energy,
-            float* d_h_first, float* d_h_last, cudaStream_t stream) {
+int readout(const fmb_model_t* m, int n_atoms, int n_energy, const float* h_first, const float* h_last,
+            float* node_energy, float* d_h_first, float* d_h_last, cudaStream_t stream) {
     const int dim_first = (m->layer[0].l_out_max + 1) * (m->layer[0].l_out_max + 1);
     const int dim_last = 1;
     const float* w_last = m->layer[m->n_layers - 1].w_readout;
-    k_readout<<<ceil_div(n_atoms, 4), 128, 0, stream>>>(n_atoms, dim_first, dim_last, m->mlp_hidden, m->scale, m->shift,
+    k_readout<<<ceil_div(n_atoms, 4), 128, 0, stream>>>(n_atoms, n_energy, dim_first, dim_last, m->mlp_hidden, m->scale, m->shift,
                                                         m->silu_norm, h_first, h_last, m->layer[0].w_readout, w_last,
                                                         w_last + kC * 16, node_energy, d_h_first, d_h_last);
     FMB_LAUNCH_CHECK();
     return FMB_OK;
 }
 
-int reduce_outputs(const fmb_model_t* m, const fmb_work_t* w, double volume, cudaStream_t stream) {
+int reduce_outputs(const fmb_model_t* m, const fmb_work_t* w, int n_energy, double volume, cudaStream_t stream) {
     E0Table e0;
     for (int k = 0; k < FMB_MAX_SPECIES; ++k) e0.v[k] = m->e0[k];
-    k_reduce_partial<<<kReduceBlocks, 256, 0, stream>>>(w->n_atoms, w->node_energy, w->species, e0,
+    k_reduce_partial<<<kReduceBlocks, 256, 0, stream>>>(w->n_atoms, n_energy, w->node_energy, w->species, e0,
                                                         w->compute_stress ? w->atom_virial : nullptr, w->partial);
     FMB_LAUNCH_CHECK();
     k_reduce_final<<<1, 32, 0, stream>>>(kReduceBlocks, w->partial, 1.0 / volume, w->compute_stress, w->energy, w->stress,

@@ -11,7 +11,10 @@ int edge_features(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t
 struct TpArgs {
     int lin;
     bool species_x;
-    int n_atoms;
+    int n_atoms;           // atoms of the list (rows of row_ptr)
+    int n_rows;            // receivers this launch computes: [0, n_rows)
+    int n_valid;           // backward: atoms [0, n_valid) have a message gradient, the others read as zero
+    int fresh_from;        // backward: atoms at or beyond this start their force / virial sums from zero
     long long chunk_e0, chunk_edges, tangent_offset;
     const long long* count;
     const int32_t* row_ptr;
@@ -36,9 +39,9 @@ int symcon_forward(int n_atoms, int n_terms, int out_dim, const int32_t* terms, 
 int symcon_backward(int n_atoms, int n_terms, int out_dim, const int32_t* terms, const float* coef,
                     const int32_t* species, const float* msg, const float* d_basis, float* d_msg, cudaStream_t stream);
 int fill_from_species(int n_atoms, int row, const int32_t* species, const float* table, float* out, cudaStream_t stream);
-int readout(const fmb_model_t* m, int n_atoms, const float* h_first, const float* h_last, float* node_energy,
+int readout(const fmb_model_t* m, int n_atoms, int n_energy, const float* h_first, const float* h_last, float* node_energy,
             float* d_h_first, float* d_h_last, cudaStream_t stream);
-int reduce_outputs(const fmb_model_t* m, const fmb_work_t* w, double volume, cudaStream_t stream);
+int reduce_outputs(const fmb_model_t* m, const fmb_work_t* w, int n_energy, double volume, cudaStream_t stream);
 int commit_forces(const fmb_work_t* w, double* f64, double* e64, double* s64, cudaStream_t stream);
 
 }  // namespace fmb

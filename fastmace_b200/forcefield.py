@@ -37,7 +37,7 @@ class ForceOutput(NamedTuple):
 class B200ForceField:
     def __init__(self, spec: MaceSpec, weights, numbers, cell, *, compute_stress: bool = False, device="cuda",
                  neighbours: NeighbourConfig | None = None, chunk_edges: int = DEFAULT_CHUNK_EDGES,
-                 positions=None):
+                 positions=None, packed: PackedModel | None = None, n_owned: int = 0, n_inner: int = 0):
         if not torch.cuda.is_available():
             raise _lib.Fmb200Error("B200ForceField needs a CUDA device: there is no CPU path")
         self.lib = _lib.load()
@@ -49,7 +49,12 @@ class B200ForceField:
         self.numbers = np.asarray(numbers, dtype=np.int64)
         self.natoms = len(self.numbers)
         self.cell = np.asarray(cell, dtype=np.float64).reshape(3, 3)
-        self.packed = PackedModel(spec, weights, sorted(set(int(z) for z in self.numbers)), self._device)
+        # ``packed``: a model already packed for a superset of these species (domain decomposition re-creates the
+        # local force field at every re-partition and reuses one packed model); ``n_owned`` / ``n_inner``: the atoms
+        # are ordered owned | inner halo | outer halo (0 = every atom is owned)
+        self.packed = packed if packed is not None else \
+            PackedModel(spec, weights, sorted(set(int(z) for z in self.numbers)), self._device)
+        self.n_owned, self.n_inner = int(n_owned), int(n_inner)
         self.species = self.packed.species_index(self.numbers)
         self.neighbours = CellListNeighbours(self.cell, spec.r_cut, self._device, torch.float32, neighbours)
         self.chunk_edges = int(chunk_edges)
@@ -129,6 +134,7 @@ class B200ForceField:
             setattr(w, name, tensor.data_ptr())
         w.energy, w.forces, w.stress = self.energy.data_ptr(), self.forces.data_ptr(), self.stress.data_ptr()
         w.status = self.status.data_ptr()
+        w.n_energy_atoms, w.n_inner_atoms = self.n_owned, self.n_inner
         self.work = w
 
     # ------------------------------------------------------------------ protocol methods

@@ -45,7 +45,10 @@ def noise_steps(limit: int, numbers: int) -> int:
 
 class Langevin:
     def __init__(self, state: SimulationState, config: IntegratorConfig | None = None, *, temperature_K: float = 0.0,
-                 force_buffer: torch.Tensor | None = None):
+                 force_buffer: torch.Tensor | None = None, noise: str = "host", device_seed: int = 0):
+        """``noise="host"``: the reference's NumPy stream, uploaded in batches. ``noise="device"``: counter-based
+        normals generated on the GPU per step (``fmb_langevin_device_noise``): not the reference's numbers, but
+        identical on every rank of a domain-decomposed run and free of the host draw that limits large systems."""
         self.lib = _lib.load()
         config = config or IntegratorConfig()
         if config.ensemble != "nvt":
@@ -53,7 +56,10 @@ class Langevin:
         self.config = config
         self.dt = config.timestep_fs * FS
         self.natoms = state.natoms
-        self.noise_batch = noise_steps(config.noise_batch, 6 * self.natoms)
+        if noise not in ("host", "device"):
+            raise ValueError("noise is 'host' or 'device'")
+        self.noise_mode, self.device_seed = noise, int(device_seed)
+        self.noise_batch = 1 if noise == "device" else noise_steps(config.noise_batch, 6 * self.natoms)
         dev = state.positions.device
         f64 = dict(dtype=torch.float64, device=dev)
         dt, fr = self.dt, config.friction
@@ -75,8 +81,10 @@ class Langevin:
         shape = (self.noise_batch, 2, self.natoms, 3)
         state.rng.batch = torch.zeros(shape, **f64)
         state.rng.cursor = self.noise_batch        # used up: the first step refills
-        self._staging = [torch.empty(shape, dtype=torch.float64).pin_memory() if dev.type == "cuda"
-                         else torch.empty(shape, dtype=torch.float64) for _ in range(2)]
+        self.zero_cursor = torch.zeros((), dtype=torch.int32, device=dev)
+        self._staging = [] if noise == "device" else \
+            [torch.empty(shape, dtype=torch.float64).pin_memory() if dev.type == "cuda"
+             else torch.empty(shape, dtype=torch.float64) for _ in range(2)]
         self._staging_events = [torch.cuda.Event() if dev.type == "cuda" else None for _ in range(2)]
         self._next = 0
         self._ahead: threading.Thread | None = None
@@ -92,7 +100,9 @@ class Langevin:
         s.c3_unit, s.c4_unit, s.c5_unit = self.c3_unit.data_ptr(), self.c4_unit.data_ptr(), self.c5_unit.data_ptr()
         s.sqrt_kT = self.sqrt_kT.data_ptr()
         s.noise = state.rng.batch.data_ptr()
-        s.noise_cursor = self.cursor_dev.data_ptr()
+        # device noise: the batch holds the current step only (row 0) and the counter the second half advances is
+        # the step index the generator is keyed with
+        s.noise_cursor = (self.zero_cursor if noise == "device" else self.cursor_dev).data_ptr()
         s.noise_cursor_rw = self.cursor_dev.data_ptr()
         s.x_old, s.rnd_pos, s.rnd_vel = self.x_old.data_ptr(), self.rnd_pos.data_ptr(), self.rnd_vel.data_ptr()
         s.partial = self.partial.data_ptr()
@@ -137,6 +147,8 @@ class Langevin:
 
     def prepare_step(self, state: SimulationState) -> None:
         """Refill the noise batch when it is used up (host; between replays) and advance the host cursor."""
+        if self.noise_mode == "device":
+            return
         if state.rng.cursor == self.noise_batch:
             self.refill(state)
         state.rng.cursor += 1
@@ -151,6 +163,10 @@ class Langevin:
 
     # ------------------------------------------------------------------ stages (graph-capturable)
     def first_half(self, state: SimulationState) -> None:
+        if self.noise_mode == "device":
+            _lib.check(self.lib.fmb_langevin_device_noise(state.rng.batch.data_ptr(), self.natoms, self.device_seed,
+                                                          self.cursor_dev.data_ptr(), _lib.current_stream()),
+                       "fmb_langevin_device_noise")
         _lib.check(self.lib.fmb_langevin_first_half(ctypes.byref(self.struct), _lib.current_stream()),
                    "fmb_langevin_first_half")
 

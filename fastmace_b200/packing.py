@@ -185,8 +185,13 @@ class PackedModel:
 
     def species_index(self, numbers) -> torch.Tensor:
         """[N] int32 index of each atom's species among the present ones."""
-        lookup = {z: k for k, z in enumerate(self.species_z)}
-        return torch.tensor([lookup[int(z)] for z in numbers], dtype=torch.int32, device=self.device)
+        table = np.full(128, -1, dtype=np.int32)
+        for k, z in enumerate(self.species_z):
+            table[z] = k
+        index = table[np.asarray(numbers, dtype=np.int64)]
+        if (index < 0).any():
+            raise ValueError("an atom's species is not among the species the model was packed for")
+        return torch.as_tensor(index, dtype=torch.int32, device=self.device)
 
     def pointer(self):
         return ctypes.byref(self.struct)

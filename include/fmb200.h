@@ -190,6 +190,12 @@ typedef struct {
     float* forces;                    /* [n_atoms][3] */
     float* stress;                    /* [9] */
     uint32_t* status;                 /* [1] */
+    /* Domain decomposition (0 = every atom): the atoms are ordered owned | inner halo | outer halo. Atoms
+     * [0, n_energy_atoms) are owned: only they contribute energy and get the last layer's rows; atoms
+     * [0, n_inner_atoms) get the first layer's rows (they are senders of owned receivers); the rest only act as
+     * species-only senders of the first layer. Forces come out for every atom (partial sums for halo atoms). */
+    int32_t n_energy_atoms;
+    int32_t n_inner_atoms;
 } fmb_work_t;
 
 /* MACEForceField.__call__ (fastmace/model/forces.py:1127-1136,1220-1240): energy (float64), forces and stress of the
@@ -247,6 +253,12 @@ typedef struct {
 
 FMB_API int fmb_langevin_first_half(const fmb_langevin_t* lv, fmb_stream_t stream);
 FMB_API int fmb_langevin_second_half(const fmb_langevin_t* lv, fmb_stream_t stream);
+/* No counterpart in the reference (its noise is NumPy's, drawn on the host: langevin.py:224-231). Fills one noise
+ * row [2][n_atoms][3] (xi, then eta) with standard normals from Philox4x32-10 keyed by `seed` and indexed by
+ * (*step_counter, atom): identical on every GPU that passes the same seed and step, for domain-decomposed runs and for
+ * sizes where the host draw of 6 N normals per step would limit the step. */
+FMB_API int fmb_langevin_device_noise(double* noise_row, int n_atoms, unsigned long long seed,
+                                      const int32_t* step_counter, fmb_stream_t stream);
 /* state.forces/energy/stress <- ForceOutput (fastmace/engine/graph.py:1125-1131): fp32 -> float64 copies. */
 FMB_API int fmb_commit_forces(const fmb_work_t* work, double* forces64, double* energy64, double* stress64,
                       fmb_stream_t stream);

@@ -183,13 +183,14 @@ def readout(spec, weights, layer, h):
 
 
 def evaluate(spec: MaceSpec, weights, positions, cell, atomic_numbers, sender, receiver, unit_shifts,
-             dtype=torch.float64, compute_stress=True, keep=None):
+             dtype=torch.float64, compute_stress=True, keep=None, n_energy=None):
     """Energy (float64 scalar), forces [N, 3], stress [3, 3] (ASE sign, dE/d(strain) / |det cell|).
 
     ``positions`` [N, 3] and ``cell`` [3, 3] float64; ``sender``/``receiver`` int64 [E]; ``unit_shifts`` [E, 3]
     integer-valued; ``atomic_numbers`` [N]. ``dtype`` is the model precision: edge vectors are formed in float64 and
     cast (the reference's large-box path, ``fastmace/model/forces.py:176-186``), per-atom energies are summed in
-    float64. ``keep``: optional dict that receives intermediates for kernel-level tests.
+    float64. ``keep``: optional dict that receives intermediates for kernel-level tests. ``n_energy``: only the first
+    ``n_energy`` atoms contribute energy (the owned atoms of one domain; the others are halo atoms).
     """
     weights = {k: v.to(dtype) for k, v in weights.items()}
     positions = torch.as_tensor(positions, dtype=torch.float64).clone().requires_grad_(True)
@@ -222,6 +223,8 @@ def evaluate(spec: MaceSpec, weights, positions, cell, atomic_numbers, sender, r
         node_energy = node_energy + readout(spec, weights, t, h)
     node_energy = spec.scale * node_energy + spec.shift
     e0 = torch.tensor(e0_table(spec))[species]
+    if n_energy is not None:
+        e0, node_energy = e0[:n_energy], node_energy[:n_energy]
     energy = e0.sum() + node_energy.to(torch.float64).sum()
     if keep is not None:
         keep["node_energy"] = node_energy

@@ -39,6 +39,13 @@ WORKLOADS = {
     "small_nacl_216_langevin": dict(model="small", seed=0, repeat=(3, 3, 3), sigma=0.05, temperature=300.0),
 }
 DEFAULT_WORKLOAD = "medium_nacl_1944_langevin"
+# the spatially decomposed configuration (884,736-atom NaCl, 48 x 48 x 48 cells): the default at --gpus > 1
+DOMAIN_WORKLOAD = "medium_nacl_884736_langevin"
+DOMAIN_WORKLOADS = {
+    DOMAIN_WORKLOAD: dict(model="medium", seed=1, repeat=(48, 48, 48), sigma=0.05, temperature=300.0, max_steps=200),
+    "medium_nacl_110592_langevin": dict(model="medium", seed=1, repeat=(24, 24, 24), sigma=0.05, temperature=300.0,
+                                        max_steps=200),
+}
 
 
 def peaks():
@@ -178,15 +185,136 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def run_domain(args, world, rank, local_rank, device):
+    """Domain-decomposed MD (one brick per rank, replicated state, one force all-reduce per step), timed through the
+    public API: ``B200Engine.step`` in checked mode over a ``DomainForceField``."""
+    import dataclasses
+
+    import torch.distributed as dist
+
+    from fastmace_b200 import _lib
+    from fastmace_b200.domain import DomainForceField
+    from fastmace_b200.engine import B200Engine
+    from fastmace_b200.langevin import IntegratorConfig, Langevin
+    from fastmace_b200.model import SPECS, init_weights
+    from fastmace_b200.state import SimulationState
+    from fastmace_b200.structures import nacl
+
+    w = DOMAIN_WORKLOADS[args.workload]
+    lib = _lib.load()
+    spec = dataclasses.replace(SPECS[w["model"]], avg_num_neighbors=32.0)
+    weights = init_weights(spec, w["seed"])
+    structure = nacl(w["repeat"], w["sigma"], w["seed"]).with_velocities(w["temperature"], w["seed"] + 100)
+    group = dist.group.WORLD if world > 1 else None
+    ff = DomainForceField(spec, weights, structure.numbers, structure.cell, rank=rank, n_ranks=world, device=device,
+                          group=group, compute_stress=True)
+    state = SimulationState.from_structure(structure, ff.device, seed=w["seed"], compute_stress=True)
+    integrator = Langevin(state, IntegratorConfig(timestep_fs=1.0), temperature_K=w["temperature"], noise="device",
+                          device_seed=w["seed"])
+    engine = B200Engine(ff, integrator, state, mode="checked")
+    initial_energy = engine.potential_energy()
+    steps = min(args.steps, w["max_steps"])
+    warmup = min(max(3, args.warmup), 10)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def reduce_max(ms):
+        if world > 1:
+            t = torch.tensor([ms], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return ms
+
+    for _ in range(warmup):
+        engine.step()
+    engine.flush()
+    launches0 = lib.fmb_launch_count()
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        engine.step()
+    stop.record()
+    stop.synchronize()
+    barrier()
+    clocks = sampler.stop()
+    total_ms = reduce_max(start.elapsed_time(stop))
+    launches = int(lib.fmb_launch_count() - launches0)
+    engine.flush()
+    # end to end: the same steps with the step's energy read back to the host every step
+    e2e_steps = min(steps, 50)
+    pinned = torch.zeros(e2e_steps, dtype=torch.float64).pin_memory()
+    barrier()
+    t0 = time.perf_counter()
+    for k in range(e2e_steps):
+        engine.step()
+        pinned[k:k + 1].copy_(state.energy, non_blocking=True)
+    engine.flush()
+    barrier()
+    e2e_ms = reduce_max((time.perf_counter() - t0) * 1e3)
+    assert bool(torch.isfinite(pinned).all()), "non-finite energies"
+    n_atoms = structure.natoms
+    # stage timing of this rank's local force call
+    lib.fmb_profile_enable(1)
+    x_loc = ff._local_positions(state.positions)
+    for _ in range(2):
+        ff.local_ff(x_loc)
+    _lib.profile_read()
+    calls = 3
+    for _ in range(calls):
+        ff.local_ff(x_loc)
+    stages = _lib.profile_read()
+    lib.fmb_profile_enable(0)
+    stage_ms = {k: v[0] / calls for k, v in stages.items()}
+    n_edges = int(ff.edge_count.item())
+    algo = stage_bytes(spec, ff.local.n_local, n_edges)
+    top = max((k for k in stage_ms if k in algo), key=lambda k: stage_ms[k])
+    pk = peaks()
+    achieved = algo[top] / (stage_ms[top] * 1e-3) / 1e9
+    info = ff.info()
+    line = dict(metric="md_atom_steps_per_s", value=n_atoms * steps / (total_ms * 1e-3), unit="atom-steps/s",
+                n_gpus=world, steps=steps, warmup=warmup, ms_per_step=total_ms / steps,
+                us_per_step=1e3 * total_ms / steps, higher_is_better=True, scaling="strong", vs_baseline=None,
+                dtype="f32", data="synthetic",
+                config=dict(workload=args.workload, atoms=n_atoms, model=w["model"],
+                            integrator="langevin_nvt_1fs_0.01perfs_device_noise",
+                            parallelism=f"bricks{'x'.join(map(str, info['bricks']))}",
+                            local_atoms_rank0=info["local_atoms"], owned_atoms_rank0=info["owned_atoms"],
+                            local_edges_rank0=n_edges, initial_energy_eV=initial_energy, neighbour_rebuilds=info["neighbour_rebuilds"],
+                            collective="one all-reduce of forces [N,3] fp32 + 10 float64 scalars per step",
+                            l2="per-step working set far exceeds the 126 MB L2; no flush"),
+                clocks=clocks,
+                e2e=dict(value=n_atoms * e2e_steps / (e2e_ms * 1e-3), unit="atom-steps/s", h2d_bytes_per_step=0,
+                         d2h_bytes_per_step=8 + 4, ms_per_step=e2e_ms / e2e_steps, steps=e2e_steps,
+                         note="state and noise live on the device; per step the host reads the rebuild flag and the energy"),
+                gpu_launches=launches, launches_per_step=launches / steps,
+                roofline=dict(bound="hbm", kernel=top, achieved=achieved, peak=pk["hbm_gbs"], unit="GB/s",
+                              frac=achieved / pk["hbm_gbs"], traffic=None, peak_source=pk["source"],
+                              algorithmic_bytes=algo[top], stage_ms={k: round(v, 4) for k, v in stage_ms.items()},
+                              note="rank 0's local force call"))
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=1000)
     parser.add_argument("--warmup", type=int, default=100)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    parser.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + sorted(DOMAIN_WORKLOADS))
     parser.add_argument("--no-cpu-baseline", action="store_true")
     args = parser.parse_args()
+    if args.workload is None:
+        args.workload = DOMAIN_WORKLOAD if int(os.environ.get("WORLD_SIZE", "1")) > 1 else DEFAULT_WORKLOAD
     if args.impl == "reference":
         run_reference(args)
         return
@@ -204,6 +332,9 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
     lib = _lib.load()
+    if args.workload in DOMAIN_WORKLOADS:
+        run_domain(args, world, rank, local_rank, device)
+        return
 
     spec, weights, structure, ff, state, integrator, engine = build_problem(args.workload, device)
     n_atoms = structure.natoms

@@ -97,7 +97,16 @@ const float* hidden_of(const Ctx& c, int layer, int tangent) {
     return c.w->edge_hidden + ((long long)(2 * layer + tangent) * c.count_cap) * kRadial;
 }
 
-int radial_weights(const Ctx& c, int layer, long long e0, bool with_tangent) {
+// limits[0] = edges whose receiver gets first-layer rows, limits[1] = edges whose receiver is owned (the list is
+// receiver-sorted, so both are prefixes); without domain decomposition both equal the edge count
+__global__ void k_edge_limits(const int32_t* __restrict__ row_ptr, int n0, int n1, long long* __restrict__ limits) {
+    limits[0] = row_ptr[n0];
+    limits[1] = row_ptr[n1];
+}
+
+long long* edge_limits(const Ctx& c) { return reinterpret_cast<long long*>(c.w->partial + 4096); }
+
+int radial_weights(const Ctx& c, int layer, long long e0, bool with_tangent, const long long* limit) {
     const fmb_layer_t& L = c.m->layer[layer];
     const long long rows = std::min<long long>(c.chunk, c.count_cap - e0);
     StageScope scope(c.stream, kStRadial);
@@ -118,7 +127,7 @@ int radial_weights(const Ctx& c, int layer, long long e0, bool with_tangent) {
         g.m = (int)rows;
         g.n = L.n_paths * kC;
         g.k = kRadial;
-        g.m_limit = (const long long*)c.nl->count;
+        g.m_limit = limit;
         g.m_limit_offset = e0;
     }
     return gemm_batch(list, count, c.stream);
@@ -202,7 +211,7 @@ int forward_layer(const Ctx& c, int layer) {
     }
     for (int k = 0; k < c.n_chunks; ++k) {
         const long long e0 = (long long)k * c.chunk;
-        FMB_TRY(radial_weights(c, layer, e0, false));
+        FMB_TRY(radial_weights(c, layer, e0, false, edge_limits(c) + (layer == 0 ? 0 : 1)));
         TpArgs t{};
         t.lin = L.l_in_max; t.species_x = layer == 0; t.n_atoms = c.n; t.n_rows = rows;
         t.chunk_e0 = e0; t.chunk_edges = c.chunk;
@@ -259,7 +268,7 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
     FMB_TRY(run_linears(c, lb));
     for (int k = 0; k < c.n_chunks; ++k) {
         const long long e0 = (long long)k * c.chunk;
-        FMB_TRY(radial_weights(c, layer, e0, true));
+        FMB_TRY(radial_weights(c, layer, e0, true, layer == 0 ? (const long long*)c.nl->count : edge_limits(c)));
         TpArgs t{};
         t.lin = L.l_in_max; t.species_x = layer == 0; t.n_atoms = c.n;
         // every atom that sends into a row with a gradient gets a force; first-layer senders are all atoms
@@ -324,6 +333,8 @@ extern "C" FMB_API int fmb_edge_features(const fmb_model_t* model, const fmb_nl_
 extern "C" FMB_API int fmb_forward(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, fmb_stream_t stream) {
     Ctx c;
     FMB_TRY(make_ctx(c, model, nl, work, (cudaStream_t)stream));
+    k_edge_limits<<<1, 1, 0, c.stream>>>(nl->edge_row_ptr, c.n0, c.n1, edge_limits(c));
+    FMB_LAUNCH_CHECK();
     FMB_TRY(forward_layer(c, 0));
     FMB_TRY(forward_layer(c, 1));
     // readout; the gradient of the last layer's scalars is parked in `basis` (free after the forward pass)
@@ -335,6 +346,8 @@ extern "C" FMB_API int fmb_forward(const fmb_model_t* model, const fmb_nl_t* nl,
 extern "C" FMB_API int fmb_backward(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, fmb_stream_t stream) {
     Ctx c;
     FMB_TRY(make_ctx(c, model, nl, work, (cudaStream_t)stream));
+    k_edge_limits<<<1, 1, 0, c.stream>>>(nl->edge_row_ptr, c.n0, c.n1, edge_limits(c));
+    FMB_LAUNCH_CHECK();
     FMB_TRY(backward_layer(c, 1, work->basis, work->d_h, 1));
     FMB_TRY(backward_layer(c, 0, work->d_h, nullptr, 0));
     StageScope scope(c.stream, kStReadout);

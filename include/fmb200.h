@@ -184,7 +184,7 @@ typedef struct {
     float* node_energy;               /* [n_atoms] */
     float* atom_virial;               /* [n_atoms][6] */
     float* force_acc;                 /* [n_atoms][3] */
-    double* partial;                  /* [>= 1024 * 8] block partial sums */
+    double* partial;                  /* [>= 1024 * 8] block partial sums; [4096..4097] hold two int64 edge limits */
     /* outputs */
     double* energy;                   /* [1] */
     float* forces;                    /* [n_atoms][3] */

@@ -89,3 +89,41 @@ def test_device_noise_is_reproducible_and_normal():
     assert abs(v.mean().item()) < 5e-3 and abs(v.std().item() - 1.0) < 5e-3
     assert abs((v ** 4).mean().item() - 3.0) < 0.05        # kurtosis of a normal
     assert abs(torch.corrcoef(torch.stack([a[0, :, 0], a[1, :, 0]]))[0, 1].item()) < 0.01
+
+
+def _nccl_worker(rank, world, port, ret):
+    import os
+    import torch.distributed as dist
+    from fastmace_b200.domain import DomainForceField
+    from fastmace_b200.forcefield import B200ForceField
+    from fastmace_b200.model import MEDIUM, init_weights
+    from fastmace_b200.structures import nacl
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    spec, weights = MEDIUM, init_weights(MEDIUM, 1)
+    s = nacl((3, 3, 3), 0.05, 1)
+    ff = DomainForceField(spec, weights, s.numbers, s.cell, rank=rank, n_ranks=world, device=f"cuda:{rank}",
+                          group=dist.group.WORLD)
+    e, f, st = ff.evaluate(s, stress=True)
+    if rank == 0:
+        e0, f0, s0 = B200ForceField(spec, weights, s.numbers, s.cell, compute_stress=True,
+                                    device="cuda:0").evaluate(s, stress=True)
+        ret["energy"] = abs(e - e0) / max(1.0, abs(e0))
+        ret["forces"] = float(np.abs(f - f0).max() / np.abs(f0).max())
+        ret["stress"] = float(np.abs(st - s0).max() / np.abs(s0).max())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_ranks_over_nccl():
+    """One process per GPU, forces summed by the NCCL all-reduce, against the undecomposed call."""
+    import socket
+    import torch.multiprocessing as mp
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
+    ret = mp.Manager().dict()
+    mp.spawn(_nccl_worker, args=(2, port, ret), nprocs=2, join=True)
+    assert ret["energy"] <= 1e-6 and ret["forces"] <= 2e-5 and ret["stress"] <= 2e-5

@@ -209,6 +209,26 @@ int forward_layer(const Ctx& c, int layer) {
         FMB_TRY(run_linears(c, lb));
         x = c.w->x;
     }
+    float* msg = msg_of(c, layer);
+    const bool reassociated = layer == 0 && L.first[0] != nullptr;
+    if (reassociated) {
+        // outer products per receiver and sender species, then one GEMM per output irrep straight to the message
+        const int nz = c.m->n_species;
+        {
+            FirstArgs f{};
+            f.n_rows = rows; f.n_species = nz; f.count = (const long long*)c.nl->count;
+            f.row_ptr = c.nl->edge_row_ptr; f.senders = c.nl->edge_index; f.species = c.w->species;
+            f.edge_sh = c.w->edge_sh; f.hidden = hidden_of(c, 0, 0); f.s = c.w->mid;
+            StageScope scope(c.stream, kStTpFwd0);
+            FMB_TRY(first_accumulate_launch(f, c.stream));
+        }
+        const long long s_atom = (long long)kNSH * nz * kRadial;
+        for (int l = 0; l <= 3; ++l)
+            block_linear(lb, c, rows, c.w->mid, s_atom, (long long)l * l * nz * kRadial, nz * kRadial, L.first[0],
+                         L.first[2], (long long)l * nz * kRadial * kC, msg, (long long)kNSH * kC,
+                         (long long)l * l * kC, kC, l, 0);
+        FMB_TRY(run_linears(c, lb));
+    } else {
     for (int k = 0; k < c.n_chunks; ++k) {
         const long long e0 = (long long)k * c.chunk;
         FMB_TRY(radial_weights(c, layer, e0, false, edge_limits(c) + (layer == 0 ? 0 : 1)));
@@ -220,11 +240,11 @@ int forward_layer(const Ctx& c, int layer) {
         StageScope scope(c.stream, layer == 0 ? kStTpFwd0 : kStTpFwd1);
         FMB_TRY(tp_forward_launch(t, c.stream));
     }
-    float* msg = msg_of(c, layer);
     for (int l = 0; l <= 3; ++l)
         block_linear(lb, c, rows, c.w->mid, (long long)ml.mid_dim * kC, (long long)ml.base[l] * kC, ml.segs[l] * kC, L.w_lin,
                      L.tc[5], lin_weight_offset(ml, l), msg, (long long)kNSH * kC, (long long)l * l * kC, kC, l, 0);
     FMB_TRY(run_linears(c, lb));
+    }
     {
         StageScope scope(c.stream, kStSymFwd);
         FMB_TRY(symcon_forward(rows, L.n_sc_terms, out_dim, L.sc_terms, L.sc_coef, c.w->species, msg, c.w->basis,
@@ -260,6 +280,25 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
         StageScope scope(c.stream, kStSymBwd);
         FMB_TRY(symcon_backward(rows, L.n_sc_terms, out_dim, L.sc_terms, L.sc_coef, c.w->species, msg_of(c, layer),
                                 c.w->d_basis, c.w->d_msg, c.stream));
+    }
+    if (layer == 0 && L.first[0] != nullptr) {
+        // reassociated first layer: gradient of the outer-product sums, then the per-edge kernel
+        const int nz = c.m->n_species;
+        const long long s_atom = (long long)kNSH * nz * kRadial;
+        for (int l = 0; l <= 3; ++l)
+            block_linear(lb, c, rows, c.w->d_msg, (long long)kNSH * kC, (long long)l * l * kC, kC, L.first[1], L.first[3],
+                         (long long)l * nz * kRadial * kC, c.w->d_mid, s_atom, (long long)l * l * nz * kRadial,
+                         nz * kRadial, l, 0);
+        FMB_TRY(run_linears(c, lb));
+        FirstArgs f{};
+        f.n_rows = c.n; f.n_valid = rows; f.fresh_from = c.n0; f.n_species = nz;
+        f.count = (const long long*)c.nl->count; f.row_ptr = c.nl->edge_row_ptr; f.senders = c.nl->edge_index;
+        f.species = c.w->species; f.edge_sh = c.w->edge_sh; f.edge_vec = c.w->edge_vec;
+        f.hidden = hidden_of(c, 0, 0); f.hidden_tangent = hidden_of(c, 0, 1); f.d_s = c.w->d_mid;
+        f.force_acc = c.w->force_acc; f.atom_virial = c.w->atom_virial; f.first_layer_of_pass = first_layer_of_pass;
+        StageScope scope(c.stream, kStTpBwd0);
+        FMB_TRY(first_backward_launch(f, c.stream));
+        return FMB_OK;
     }
     for (int l = 0; l <= 3; ++l)
         block_linear(lb, c, rows, c.w->d_msg, (long long)kNSH * kC, (long long)l * l * kC, kC, L.w_lin_t, L.tc[6],

@@ -271,6 +271,149 @@ k_tp_backward(int n_atoms, int n_rows, int n_valid, int fresh_from, long long ch
     }
 }
 
+// ---------------------------------------------------------------------------------------------- first layer
+// The first layer's senders are species-only rows, so its message factorises (exact algebra, the reference's
+// "reassociation", fastmace/rewrites/mh1/modules.py:146-160): per receiver i and sender species z
+//     S[i, lm, z, k] = sum_{e -> i, species(sender e) = z} Y[e, lm] * hidden[e, k]          (16 x 64 per species)
+// and the message is S times a per-l matrix that folds the last radial layer, the sender row and the message linear.
+// No [E, P*C] weights, no tensor product per edge.
+constexpr int kFirstZ = FMB_MAX_SPECIES;
+
+// CTA per receiver, thread = (k = tid & 63, half = tid >> 6 -> harmonics 8 * half .. 8 * half + 7); the tile is
+// accumulated in shared memory at [z][lm][k], every thread owning its own cells.
+__global__ void __launch_bounds__(kC)
+k_first_accumulate(int n_rows, int n_species, const long long* __restrict__ count_ptr,
+                   const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ senders,
+                   const int32_t* __restrict__ species, const float* __restrict__ edge_sh,
+                   const float* __restrict__ hidden, float* __restrict__ s_out) {
+    extern __shared__ float tile[];                       // [n_species][16][64]
+    const int k = threadIdx.x & 63, half = threadIdx.x >> 6;
+    for (int i = blockIdx.x; i < n_rows; i += gridDim.x) {
+        for (int q = threadIdx.x; q < n_species * kNSH * kRadial; q += kC) tile[q] = 0.0f;
+        __syncthreads();
+        const long long rb = row_ptr[i], re = row_ptr[i + 1];
+        for (long long e = rb; e < re; ++e) {
+            const int z = species[senders[e]];
+            const float h = __ldg(hidden + e * kRadial + k);
+            const float4* yp = reinterpret_cast<const float4*>(edge_sh + 16 * e + 8 * half);
+            const float4 y0 = __ldg(yp), y1 = __ldg(yp + 1);
+            float* cell = tile + ((z * kNSH + 8 * half) * kRadial) + k;
+            cell[0 * kRadial] = fmaf(y0.x, h, cell[0 * kRadial]);
+            cell[1 * kRadial] = fmaf(y0.y, h, cell[1 * kRadial]);
+            cell[2 * kRadial] = fmaf(y0.z, h, cell[2 * kRadial]);
+            cell[3 * kRadial] = fmaf(y0.w, h, cell[3 * kRadial]);
+            cell[4 * kRadial] = fmaf(y1.x, h, cell[4 * kRadial]);
+            cell[5 * kRadial] = fmaf(y1.y, h, cell[5 * kRadial]);
+            cell[6 * kRadial] = fmaf(y1.z, h, cell[6 * kRadial]);
+            cell[7 * kRadial] = fmaf(y1.w, h, cell[7 * kRadial]);
+        }
+        __syncthreads();
+        // global layout [i][lm][z][k]: the K = n_species * 64 values of one (atom, harmonic) row are contiguous
+        float* out = s_out + (long long)i * kNSH * n_species * kRadial;
+        for (int q = threadIdx.x; q < n_species * kNSH * kRadial; q += kC) {
+            const int kk = q & 63, z = (q >> 6) % n_species, lm = q / (64 * n_species);
+            out[q] = tile[(z * kNSH + lm) * kRadial + kk];
+        }
+        __syncthreads();
+    }
+}
+
+// Backward of the same: CTA per atom a; for each edge j -> a of its row both the edge (gradient block of a, species
+// of j) and its mirror a -> j (gradient block of j, species of a, harmonics with (-1)^l) contribute
+//   dE/dY[lm] = sum_k C[lm, k] hidden[k],   dE/dr = sum_k hidden'[k] sum_lm C[lm, k] Y[lm],   C = G_a[., z_j] + (-1)^l G_j[., z_a]
+// and the force on a is minus the sum over the row of the edge-vector gradient, as in k_tp_backward.
+__global__ void __launch_bounds__(kC)
+k_first_backward(int n_rows, int n_valid, int fresh_from, int n_species, const long long* __restrict__ count_ptr,
+                 const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ senders,
+                 const int32_t* __restrict__ species, const float* __restrict__ edge_sh,
+                 const float* __restrict__ edge_vec, const float* __restrict__ hidden,
+                 const float* __restrict__ hidden_tangent, const float* __restrict__ d_s,
+                 float* __restrict__ force_acc, float* __restrict__ atom_virial, int first_layer_of_pass) {
+    __shared__ float red[kEdgeBatch][4][kRed + 1];
+    const int c = threadIdx.x, k = c & 63, half = c >> 6, warp = c >> 5, lane = c & 31;
+    const long long row_floats = (long long)kNSH * n_species * kRadial;
+    for (int a = blockIdx.x; a < n_rows; a += gridDim.x) {
+        const long long rb = row_ptr[a], re = row_ptr[a + 1];
+        const int za = species[a];
+        float fsum[3] = {0.f, 0.f, 0.f}, vir[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (long long batch = rb; batch < re; batch += kEdgeBatch) {
+            const int nb = (int)min((long long)kEdgeBatch, re - batch);
+            for (int b = 0; b < nb; ++b) {
+                const long long e = batch + b;
+                const int j = senders[e];
+                const int zj = species[j];
+                const float h = __ldg(hidden + e * kRadial + k), hp = __ldg(hidden_tangent + e * kRadial + k);
+                const float4* yp = reinterpret_cast<const float4*>(edge_sh + 16 * e + 8 * half);
+                const float4 y0 = __ldg(yp), y1 = __ldg(yp + 1);
+                const float Y[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
+                float part[9];
+                float dh = 0.0f;
+#pragma unroll
+                for (int m = 0; m < 8; ++m) {
+                    const int lm = 8 * half + m;
+                    // (-1)^l of harmonic lm: l = 0 (lm 0), 1 (1..3), 2 (4..8), 3 (9..15)
+                    const float sign = (lm >= 1 && lm <= 3) || lm >= 9 ? -1.0f : 1.0f;
+                    const long long cell = ((long long)lm * n_species) * kRadial + k;
+                    const float ga = a < n_valid ? __ldg(d_s + a * row_floats + cell + (long long)zj * kRadial) : 0.0f;
+                    const float gj = j < n_valid ? __ldg(d_s + j * row_floats + cell + (long long)za * kRadial) : 0.0f;
+                    const float cc = ga + sign * gj;
+                    part[m] = cc * h;
+                    dh = fmaf(cc, Y[m], dh);
+                }
+                part[8] = dh * hp;
+                // reduce the 9 partial sums over the warp, then over the warps through shared memory
+#pragma unroll
+                for (int m = 0; m < 9; ++m) part[m] = warp_sum(part[m]);
+                if (lane == 0) {
+#pragma unroll
+                    for (int m = 0; m < 8; ++m) red[b][warp][m] = part[m];
+                    red[b][warp][16] = part[8];
+                }
+            }
+            __syncthreads();
+            if (c < nb) {
+                const long long e = batch + c;
+                float g[16];
+                // warps 0, 1 hold harmonics 0..7 (half 0), warps 2, 3 harmonics 8..15
+#pragma unroll
+                for (int m = 0; m < 8; ++m) {
+                    g[m] = red[c][0][m] + red[c][1][m];
+                    g[8 + m] = red[c][2][m] + red[c][3][m];
+                }
+                const float drt = red[c][0][16] + red[c][1][16] + red[c][2][16] + red[c][3][16];
+                const float4 uv = __ldg(reinterpret_cast<const float4*>(edge_vec) + e);
+                float q3[3];
+                edge_vector_gradient(g, drt, uv.x, uv.y, uv.z, uv.w, q3);
+                fsum[0] += q3[0]; fsum[1] += q3[1]; fsum[2] += q3[2];
+                const float vx = uv.x * uv.w, vy = uv.y * uv.w, vz = uv.z * uv.w;
+                vir[0] += vx * q3[0]; vir[1] += vy * q3[1]; vir[2] += vz * q3[2];
+                vir[3] += 0.5f * (vy * q3[2] + vz * q3[1]);
+                vir[4] += 0.5f * (vx * q3[2] + vz * q3[0]);
+                vir[5] += 0.5f * (vx * q3[1] + vy * q3[0]);
+            }
+            __syncthreads();
+        }
+        if (warp == 0) {
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) {
+#pragma unroll
+                for (int q = 0; q < 3; ++q) fsum[q] += __shfl_xor_sync(0xffffffffu, fsum[q], o);
+#pragma unroll
+                for (int q = 0; q < 6; ++q) vir[q] += __shfl_xor_sync(0xffffffffu, vir[q], o);
+            }
+            if (lane == 0) {
+                const bool fresh = first_layer_of_pass || a >= fresh_from;
+#pragma unroll
+                for (int q = 0; q < 3; ++q)
+                    force_acc[3 * a + q] = (fresh ? 0.0f : force_acc[3 * a + q]) + fsum[q];
+#pragma unroll
+                for (int q = 0; q < 6; ++q)
+                    atom_virial[6 * a + q] = (fresh ? 0.0f : atom_virial[6 * a + q]) + 0.5f * vir[q];
+            }
+        }
+    }
+}
+
 int persistent_grid(const void* kernel, int n_atoms) {
     static std::map<const void*, int> cache;
     auto it = cache.find(kernel);
@@ -336,6 +479,31 @@ int tp_backward_launch(const TpArgs& t, cudaStream_t stream) {
         FMB_REQUIRE(false, "tp_backward: unsupported node l_max");
     }
 #undef FMB_BWD
+    FMB_LAUNCH_CHECK();
+    return FMB_OK;
+}
+
+}  // namespace fmb
+
+namespace fmb {
+
+int first_accumulate_launch(const FirstArgs& f, cudaStream_t stream) {
+    if (f.n_rows <= 0) return FMB_OK;
+    FMB_REQUIRE(f.n_species >= 1 && f.n_species <= kFirstZ, "first layer: too many species");
+    const size_t smem = (size_t)f.n_species * kNSH * kRadial * sizeof(float);
+    const int grid = persistent_grid((const void*)k_first_accumulate, f.n_rows);
+    k_first_accumulate<<<grid, kC, smem, stream>>>(f.n_rows, f.n_species, f.count, f.row_ptr, f.senders, f.species,
+                                                   f.edge_sh, f.hidden, f.s);
+    FMB_LAUNCH_CHECK();
+    return FMB_OK;
+}
+
+int first_backward_launch(const FirstArgs& f, cudaStream_t stream) {
+    if (f.n_rows <= 0) return FMB_OK;
+    const int grid = persistent_grid((const void*)k_first_backward, f.n_rows);
+    k_first_backward<<<grid, kC, 0, stream>>>(f.n_rows, f.n_valid, f.fresh_from, f.n_species, f.count, f.row_ptr,
+                                              f.senders, f.species, f.edge_sh, f.edge_vec, f.hidden, f.hidden_tangent,
+                                              f.d_s, f.force_acc, f.atom_virial, f.first_layer_of_pass);
     FMB_LAUNCH_CHECK();
     return FMB_OK;
 }

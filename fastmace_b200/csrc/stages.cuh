@@ -34,6 +34,26 @@ struct TpArgs {
 int tp_forward_launch(const TpArgs& t, cudaStream_t stream);
 int tp_backward_launch(const TpArgs& t, cudaStream_t stream);
 
+// first layer in reassociated form (outer products per receiver and sender species)
+struct FirstArgs {
+    int n_rows, n_valid, fresh_from, n_species;
+    const long long* count;
+    const int32_t* row_ptr;
+    const int32_t* senders;
+    const int32_t* species;
+    const float* edge_sh;
+    const float* edge_vec;
+    const float* hidden;           // [edges][64] last hidden radial layer of the first interaction
+    const float* hidden_tangent;   // its derivative with respect to the edge length
+    float* s;                      // forward output [n][16][n_species][64]
+    const float* d_s;              // backward input, same layout
+    float* force_acc;
+    float* atom_virial;
+    int first_layer_of_pass;
+};
+int first_accumulate_launch(const FirstArgs& f, cudaStream_t stream);
+int first_backward_launch(const FirstArgs& f, cudaStream_t stream);
+
 int symcon_forward(int n_atoms, int n_terms, int out_dim, const int32_t* terms, const float* coef,
                    const int32_t* species, const float* msg, float* basis, cudaStream_t stream);
 int symcon_backward(int n_atoms, int n_terms, int out_dim, const int32_t* terms, const float* coef,

@@ -105,6 +105,8 @@ class B200ForceField:
         max_paths = max(len(spec.paths(t)) for t in range(spec.num_interactions))
         max_mid = max(self.packed.struct.layer[t].mid_dim for t in range(spec.num_interactions))
         hid = (spec.hidden_lmax + 1) ** 2
+        # the reassociated first layer keeps its per-species outer-product sums [16][n_species][64] in `mid` / `d_mid`
+        mid_floats = max(max_mid * c, 16 * len(self.packed.species_z) * 64)
         f32 = dict(dtype=torch.float32, device=dev)
         buf = {
             "edge_vec": torch.zeros(cap, 4, **f32),
@@ -112,14 +114,14 @@ class B200ForceField:
             "edge_hidden": torch.zeros(spec.num_interactions, 2, cap, 64, **f32),
             "tp_w": torch.zeros(2 * chunk, max_paths * c, **f32),
             "x": torch.zeros(n, hid, c, **f32),
-            "mid": torch.zeros(n, max_mid, c, **f32),
+            "mid": torch.zeros(n, mid_floats, **f32),
             "msg": torch.zeros(spec.num_interactions, n, 16, c, **f32),
             "basis": torch.zeros(n, hid, c, **f32),
             "h": torch.zeros(n * (hid + 1), c, **f32),
             "d_h": torch.zeros(n, hid, c, **f32),
             "d_basis": torch.zeros(n, hid, c, **f32),
             "d_msg": torch.zeros(n, 16, c, **f32),
-            "d_mid": torch.zeros(n, max_mid, c, **f32),
+            "d_mid": torch.zeros(n, mid_floats, **f32),
             "d_x": torch.zeros(n, hid, c, **f32),
             "node_energy": torch.zeros(n, **f32),
             "atom_virial": torch.zeros(n, 6, **f32),

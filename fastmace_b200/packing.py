@@ -130,6 +130,19 @@ class PackedModel:
                     sc[k, 0] = h0[k] @ skip[:, e, :] / math.sqrt(c * n_el)
                 layer.x_species = self._put("l0.x_species", x_species)
                 layer.sc_species = self._put("l0.sc_species", sc)
+                # reassociated first layer: message[i, (l, m), :] = sum_z S[i, (l, m), z, :] @ first_l[z], with
+                # S[i, lm, z, k] = sum_{e -> i, species(sender) = z} hidden[e, k] * Y[e, lm]  (exact algebra)
+                w4 = (w["l0.rad.3"] / math.sqrt(widths[3])).to(torch.float32).to(torch.float64)
+                blocks = []
+                for l_out in range(spec.sh_lmax + 1):
+                    (p0,) = so3.paths_into(paths, l_out)
+                    lin_l = w[f"l0.lin.{p0}"] / math.sqrt(c) / spec.avg_num_neighbors
+                    per_z = [(w4[:, p0 * c:(p0 + 1) * c] * x_species[z][None, :]) @ lin_l for z in range(len(idx))]
+                    blocks.append(torch.cat(per_z, dim=0).to(torch.float32))           # [nz * 64, C]
+                layer.first[0] = self._put("l0.first", torch.cat([b.reshape(-1) for b in blocks]))
+                layer.first[1] = self._put("l0.first_t", torch.cat([b.t().contiguous().reshape(-1) for b in blocks]))
+                layer.first[2] = self._twin("l0.first", blocks)
+                layer.first[3] = self._twin("l0.first_t", [b.t().contiguous() for b in blocks])
             else:
                 up = torch.stack([w[f"l{t}.up.{l}"] / math.sqrt(c) for l in range(spec.l_in_max(t) + 1)])
                 layer.w_up = self._put(f"l{t}.w_up", up)

@@ -141,6 +141,12 @@ typedef struct {
      * w_prod, w_prod_t: for every [K][N] block at float offset o of the array, the twin holds at offset 2 o the
      * transposed block [N][K] rounded to tf32 (hi) followed by the tf32 remainder (lo). Null = SIMT GEMM. */
     const float* tc[9];
+    /* First layer only (senders are species-only rows, so the edge side reduces to 64 x 16 outer products per
+     * receiver and sender species, fastmace/rewrites/mh1/modules.py:146-160): per output irrep l the matrix
+     * [n_species * 64][C] = last radial layer x sender species row x message linear, l blocks concatenated; its
+     * transpose [C][n_species * 64] per l; and the tensor-core twins of both. Null = evaluate the first layer like the
+     * others. */
+    const float* first[4];
 } fmb_layer_t;
 
 typedef struct {

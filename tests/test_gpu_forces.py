@@ -95,7 +95,7 @@ def test_stage_intermediates_against_oracle():
     # the scattered message of the last layer is still in `mid` ... overwritten by the backward? no: d_mid is separate
     paths = spec.paths(1)
     slots, _ = message_slots(paths)
-    mid = ff.buf["mid"].cpu().numpy()
+    mid = ff.buf["mid"].cpu().numpy().reshape(n, -1)[:, :so3.mid_dim(paths) * c].reshape(n, -1, c)
     ref = keep["l1.mid"].numpy()
     perm = np.zeros(so3.mid_dim(paths), dtype=np.int64)
     for p, path in enumerate(paths):

@@ -330,11 +330,15 @@ k_first_backward(int n_rows, int n_valid, int fresh_from, int n_species, const l
                  const float* __restrict__ hidden_tangent, const float* __restrict__ d_s,
                  float* __restrict__ force_acc, float* __restrict__ atom_virial, int first_layer_of_pass) {
     __shared__ float red[kEdgeBatch][4][kRed + 1];
+    extern __shared__ float own[];                        // this atom's gradient block [16][n_species][64]
     const int c = threadIdx.x, k = c & 63, half = c >> 6, warp = c >> 5, lane = c & 31;
     const long long row_floats = (long long)kNSH * n_species * kRadial;
     for (int a = blockIdx.x; a < n_rows; a += gridDim.x) {
         const long long rb = row_ptr[a], re = row_ptr[a + 1];
         const int za = species[a];
+        __syncthreads();
+        for (int q = c; q < (int)row_floats; q += kC) own[q] = a < n_valid ? __ldg(d_s + a * row_floats + q) : 0.0f;
+        __syncthreads();
         float fsum[3] = {0.f, 0.f, 0.f}, vir[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         for (long long batch = rb; batch < re; batch += kEdgeBatch) {
             const int nb = (int)min((long long)kEdgeBatch, re - batch);
@@ -354,21 +358,30 @@ k_first_backward(int n_rows, int n_valid, int fresh_from, int n_species, const l
                     // (-1)^l of harmonic lm: l = 0 (lm 0), 1 (1..3), 2 (4..8), 3 (9..15)
                     const float sign = (lm >= 1 && lm <= 3) || lm >= 9 ? -1.0f : 1.0f;
                     const long long cell = ((long long)lm * n_species) * kRadial + k;
-                    const float ga = a < n_valid ? __ldg(d_s + a * row_floats + cell + (long long)zj * kRadial) : 0.0f;
+                    const float ga = own[cell + zj * kRadial];
                     const float gj = j < n_valid ? __ldg(d_s + j * row_floats + cell + (long long)za * kRadial) : 0.0f;
                     const float cc = ga + sign * gj;
                     part[m] = cc * h;
                     dh = fmaf(cc, Y[m], dh);
                 }
                 part[8] = dh * hp;
-                // reduce the 9 partial sums over the warp, then over the warps through shared memory
+                // reduce over the warp: the 8 harmonic sums with a transpose-reduce (lane l ends with value l >> 2),
+                // the radial one with a plain butterfly; the warps meet in shared memory
 #pragma unroll
-                for (int m = 0; m < 9; ++m) part[m] = warp_sum(part[m]);
-                if (lane == 0) {
+                for (int halfw = 4, bit = 16; halfw >= 1; halfw >>= 1, bit >>= 1) {
+                    const bool upper = (lane & bit) != 0;
 #pragma unroll
-                    for (int m = 0; m < 8; ++m) red[b][warp][m] = part[m];
-                    red[b][warp][16] = part[8];
+                    for (int m = 0; m < halfw; ++m) {
+                        const float keep = upper ? part[m + halfw] : part[m];
+                        const float send = upper ? part[m] : part[m + halfw];
+                        part[m] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
+                    }
                 }
+                part[0] += __shfl_xor_sync(0xffffffffu, part[0], 2);
+                part[0] += __shfl_xor_sync(0xffffffffu, part[0], 1);
+                part[8] = warp_sum(part[8]);
+                if ((lane & 3) == 0) red[b][warp][lane >> 2] = part[0];
+                if (lane == 0) red[b][warp][16] = part[8];
             }
             __syncthreads();
             if (c < nb) {
@@ -501,7 +514,8 @@ int first_accumulate_launch(const FirstArgs& f, cudaStream_t stream) {
 int first_backward_launch(const FirstArgs& f, cudaStream_t stream) {
     if (f.n_rows <= 0) return FMB_OK;
     const int grid = persistent_grid((const void*)k_first_backward, f.n_rows);
-    k_first_backward<<<grid, kC, 0, stream>>>(f.n_rows, f.n_valid, f.fresh_from, f.n_species, f.count, f.row_ptr,
+    const size_t smem = (size_t)kNSH * f.n_species * kRadial * sizeof(float);
+    k_first_backward<<<grid, kC, smem, stream>>>(f.n_rows, f.n_valid, f.fresh_from, f.n_species, f.count, f.row_ptr,
                                               f.senders, f.species, f.edge_sh, f.edge_vec, f.hidden, f.hidden_tangent,
                                               f.d_s, f.force_acc, f.atom_virial, f.first_layer_of_pass);
     FMB_LAUNCH_CHECK();

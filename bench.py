@@ -37,6 +37,12 @@ WORKLOADS = {
     # name: (model, structure builder args, temperature, avg_num_neighbors)
     "medium_nacl_1944_langevin": dict(model="medium", seed=1, repeat=(9, 9, 3), sigma=0.05, temperature=300.0),
     "small_nacl_216_langevin": dict(model="small", seed=0, repeat=(3, 3, 3), sigma=0.05, temperature=300.0),
+    # 13,824-site random 5-species FCC alloy (primitive cell 24^3), large model, 1,000 K
+    "large_alloy_13824_langevin": dict(model="large", seed=2, builder="fcc_alloy", repeat=(24, 24, 24), sigma=0.1,
+                                       temperature=1000.0, avg_num_neighbors=54.0),
+    # 110,592-atom amorphous Si-O box at 2.2 g/cm^3 (about 59 neighbours per atom at 6 A), medium model
+    "medium_sio2_110592_langevin": dict(model="medium", seed=1, builder="silica", temperature=300.0,
+                                        avg_num_neighbors=60.0),
 }
 DEFAULT_WORKLOAD = "medium_nacl_1944_langevin"
 # the spatially decomposed configuration (884,736-atom NaCl, 48 x 48 x 48 cells): the default at --gpus > 1
@@ -113,12 +119,19 @@ def build_problem(workload: str, device):
     from fastmace_b200.langevin import IntegratorConfig, Langevin
     from fastmace_b200.model import SPECS, init_weights
     from fastmace_b200.state import SimulationState
-    from fastmace_b200.structures import nacl
+    from fastmace_b200.structures import fcc_alloy, nacl, silica
 
     w = WORKLOADS[workload]
-    spec = dataclasses.replace(SPECS[w["model"]], avg_num_neighbors=32.0)
+    spec = dataclasses.replace(SPECS[w["model"]], avg_num_neighbors=w.get("avg_num_neighbors", 32.0))
     weights = init_weights(spec, w["seed"])
-    structure = nacl(w["repeat"], w["sigma"], w["seed"]).with_velocities(w["temperature"], w["seed"] + 100)
+    builder = w.get("builder", "nacl")
+    if builder == "nacl":
+        structure = nacl(w["repeat"], w["sigma"], w["seed"])
+    elif builder == "fcc_alloy":
+        structure = fcc_alloy(w["repeat"], w["sigma"], w["seed"])
+    else:
+        structure = silica(seed=w["seed"])
+    structure = structure.with_velocities(w["temperature"], w["seed"] + 100)
     ff = B200ForceField(spec, weights, structure.numbers, structure.cell, compute_stress=True, device=device)
     state = SimulationState.from_structure(structure, ff.device, seed=w["seed"], compute_stress=True)
     integrator = Langevin(state, IntegratorConfig(timestep_fs=1.0), temperature_K=w["temperature"])

@@ -81,46 +81,31 @@ def fcc_alloy(repeat=(24, 24, 24), sigma: float = 0.1, seed: int = 2, a: float =
 
 
 def silica(n_si: int = 36864, density: float = 2.2, seed: int = 1, min_distance: float = 1.4) -> Structure:
-    """Amorphous Si-O box: n_si Si + 2 n_si O placed uniformly at random in a cubic periodic cell at ``density``
-    g/cm^3, rejecting any position closer than ``min_distance`` (minimum image) to an accepted one."""
+    """Amorphous Si-O box: n_si Si + 2 n_si O placed one after the other uniformly at random in a cubic periodic cell
+    at ``density`` g/cm^3; a trial position closer than ``min_distance`` (minimum image) to an accepted one is
+    rejected. Trials are drawn in batches; inside a batch they are accepted in order, so the result is that of the
+    sequential procedure."""
+    from scipy.spatial import cKDTree
+
     n = 3 * n_si
     mass_g = (n_si * ATOMIC_MASSES[14] + 2 * n_si * ATOMIC_MASSES[8]) * _AMU * 1e3
     length = (mass_g / density) ** (1.0 / 3.0) * 1e8  # cm -> Å
     rng = np.random.default_rng(seed)
-    nb = max(1, int(length // min_distance))
-    width = length / nb
-    bins: dict[tuple, list] = {}
-    out = np.empty((n, 3))
-    count = 0
-    d2 = min_distance * min_distance
-    while count < n:
-        trial = rng.uniform(0.0, length, size=(4096, 3))
-        for p in trial:
-            b = tuple((p // width).astype(int) % nb)
-            ok = True
-            for dx in (-1, 0, 1):
-                for dy in (-1, 0, 1):
-                    for dz in (-1, 0, 1):
-                        for q in bins.get(((b[0] + dx) % nb, (b[1] + dy) % nb, (b[2] + dz) % nb), ()):
-                            d = p - q
-                            d -= length * np.round(d / length)
-                            if d @ d < d2:
-                                ok = False
-                                break
-                        if not ok:
-                            break
-                    if not ok:
-                        break
-                if not ok:
-                    break
-            if ok:
-                bins.setdefault(b, []).append(p)
-                out[count] = p
-                count += 1
-                if count == n:
-                    break
+    accepted = np.empty((0, 3))
+    while len(accepted) < n:
+        trial = rng.uniform(0.0, length, size=(min(8192, 2 * (n - len(accepted)) + 64), 3))
+        ok = np.ones(len(trial), dtype=bool)
+        if len(accepted):
+            dist, _ = cKDTree(accepted, boxsize=length).query(trial, k=1, distance_upper_bound=min_distance)
+            ok &= ~np.isfinite(dist)
+        pairs = cKDTree(trial, boxsize=length).query_pairs(min_distance, output_type="ndarray")
+        for i, j in pairs[np.lexsort((pairs[:, 0], pairs[:, 1]))] if len(pairs) else ():
+            # j > i: the later trial is rejected if the earlier one stands
+            if ok[i] and ok[j]:
+                ok[j] = False
+        accepted = np.concatenate([accepted, trial[ok]])[:n]
     numbers = np.where(rng.permutation(n) < n_si, 14, 8).astype(np.int64)
-    return Structure(out, length * np.eye(3), numbers)
+    return Structure(accepted, length * np.eye(3), numbers)
 
 
 __all__ = ["Structure", "nacl", "fcc_alloy", "silica", "FS", "KB", "ATOMIC_MASSES"]

@@ -13,6 +13,7 @@ are simply never read), and forces come from analytic backward kernels, not auto
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import NamedTuple
 
 import numpy as np
@@ -57,7 +58,8 @@ class B200ForceField:
         self.n_owned, self.n_inner = int(n_owned), int(n_inner)
         self.species = self.packed.species_index(self.numbers)
         self.neighbours = CellListNeighbours(self.cell, spec.r_cut, self._device, torch.float32, neighbours)
-        self.chunk_edges = int(chunk_edges)
+        # FMB_CHUNK_EDGES overrides the chunk size (a tuning knob: small chunks keep the per-edge weights in L2)
+        self.chunk_edges = int(os.environ.get("FMB_CHUNK_EDGES", chunk_edges))
         self.num_edges = 0
         self.calls = 0
         self.data = {}

@@ -227,12 +227,91 @@ def _write(path: str, text: str) -> None:
             handle.write(text)
 
 
+# --------------------------------------------------------------------------------------------- path-major bodies
+PATHS_OUT = os.path.join(HERE, "csrc", "generated", "tp_paths_generated.cuh")
+
+
+def _emit_paths(lin: int) -> str:
+    """One ``TpPath<LIN, P>`` per path: shape constants and the forward / adjoint of that path alone, for the kernels
+    that take the radial weights of one path at a time from tensor memory."""
+    paths = so3.tp_paths(lin)
+    slots, blocks = message_slots(paths)
+    out = [f"// ---- node l_max = {lin}"]
+    seen_in: set[int] = set()
+    for p, path in enumerate(paths):
+        l_in, l_edge, l_out = path["l_in"], path["l_edge"], path["l_out"]
+        n_in, n_e, n_o = 2 * l_in + 1, 2 * l_edge + 1, 2 * l_out + 1
+        base, n_seg = blocks[l_out]
+        seg = slots[(p, 0)] - base
+        first_for_in = l_in not in seen_in
+        seen_in.add(l_in)
+        sign = -1.0 if l_edge % 2 else 1.0
+        out += [f"template <> struct TpPath<{lin}, {p}> {{  // {l_in} x {l_edge} -> {l_out}",
+                f"    static constexpr int kNin = {n_in}, kNe = {n_e}, kNo = {n_o};",
+                f"    static constexpr int kInOff = {path['in_off']}, kEdgeOff = {path['edge_off']};",
+                f"    static constexpr int kSlotBase = {base + seg}, kSlotStride = {n_seg};",
+                f"    static constexpr bool kFirstForIn = {'true' if first_for_in else 'false'};",
+                f"    static __device__ __forceinline__ void forward(const float (&x)[{n_in}], const float (&Y)[{n_e}], "
+                f"float w, float (&acc)[{n_o}]) {{"]
+        by_out: dict[int, list] = {}
+        by_edge: dict[int, list] = {}
+        by_in: dict[int, list] = {}
+        for mi, me, mo, c in path["terms"]:
+            by_out.setdefault(mo, []).append((mi, me, c))
+            by_edge.setdefault(me, []).append((mi, mo, c))
+            by_in.setdefault(mi, []).append((me, mo, c))
+        for mo, terms in sorted(by_out.items()):
+            expr = " + ".join(f"{_lit(c)} * x[{mi}] * Y[{me}]" for mi, me, c in terms)
+            out.append(f"        acc[{mo}] = fmaf(w, {expr}, acc[{mo}]);")
+        out += ["    }",
+                "    // edge as stored (sender features xj, receiver gradient ga) plus its mirror (own features xa, the",
+                "    // sender's gradient gj, harmonics with (-1)^l): part[0 .. kNe) = dE/dY of this path, part[kNe] = dE/dr",
+                f"    static __device__ __forceinline__ void backward(const float (&xj)[{n_in}], const float (&ga)[{n_o}], "
+                f"const float (&xa)[{n_in}], const float (&gj)[{n_o}], const float (&Y)[{n_e}], float w, float wp, "
+                f"float (&part)[{n_e + 1}], float (&dx)[{n_in}]) {{",
+                f"        constexpr float sg = {_lit(sign)};",
+                "        float dw = 0.0f;"]
+        for me in range(n_e):
+            terms = by_edge.get(me, [])
+            if not terms:
+                out.append(f"        part[{me}] = 0.0f;")
+                continue
+            e1 = " + ".join(f"{_lit(c)} * xj[{mi}] * ga[{mo}]" for mi, mo, c in terms)
+            e2 = " + ".join(f"{_lit(c)} * xa[{mi}] * gj[{mo}]" for mi, mo, c in terms)
+            out.append(f"        {{ const float s = ({e1}) + sg * ({e2}); dw = fmaf(s, Y[{me}], dw); part[{me}] = w * s; }}")
+        out.append(f"        part[{n_e}] = wp * dw;")
+        for mi in range(n_in):
+            terms = by_in.get(mi, [])
+            if not terms:
+                continue
+            expr = " + ".join(f"{_lit(c)} * Y[{me}] * gj[{mo}]" for me, mo, c in terms)
+            out.append(f"        dx[{mi}] = fmaf(w * sg, {expr}, dx[{mi}]);")
+        out += ["    }", "};"]
+    out.append(f"#define FMB_FOR_EACH_PATH_{lin}(X) " + " ".join(f"X({p})" for p in range(len(paths))))
+    out.append("")
+    return "\n".join(out)
+
+
+def render_paths() -> str:
+    head = ["// GENERATED by fastmace_b200/codegen.py from fastmace_b200/so3.py -- do not edit.",
+            "// The channelwise tensor product one path at a time (same coefficients and message layout as",
+            "// tp_generated.cuh): message component of output m is kSlotBase + m * kSlotStride.",
+            "#pragma once",
+            "",
+            "namespace fmb {",
+            "",
+            "template <int LIN, int P> struct TpPath;",
+            ""]
+    return "\n".join(head + [_emit_paths(lin) for lin in (1, 2)] + ["}  // namespace fmb", ""])
+
+
 _tp_main = main
 
 
 def main() -> str:  # noqa: F811  (both generated headers)
     out = _tp_main()
     _write(SYMCON_OUT, render_symcon())
+    _write(PATHS_OUT, render_paths())
     return out
 
 

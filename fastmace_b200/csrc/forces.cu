@@ -9,6 +9,8 @@
 #include "gemm.cuh"
 #include "stages.cuh"
 
+#include <cstdlib>
+
 #include <cmath>
 #include <vector>
 
@@ -229,7 +231,21 @@ int forward_layer(const Ctx& c, int layer) {
                          (long long)l * l * kC, kC, l, 0);
         FMB_TRY(run_linears(c, lb));
     } else {
-    for (int k = 0; k < c.n_chunks; ++k) {
+    bool fused = false;
+    if (layer > 0 && L.rad_img && tensor_cores_enabled()) {
+        // last radial layer inside the tensor-product kernel: no per-edge weight matrix, one launch for all rows
+        FusedArgs f{};
+        f.lin = L.l_in_max; f.n_rows = rows; f.row_ptr = c.nl->edge_row_ptr; f.senders = c.nl->edge_index;
+        f.x = x; f.edge_sh = c.w->edge_sh; f.hidden = hidden_of(c, layer, 0); f.image = L.rad_img; f.mid = c.w->mid;
+        f.error_word = c.w->status;
+        StageScope scope(c.stream, kStTpFwd1);
+        const int rc = tp_fused_forward(f, c.stream);
+        if (rc != FMB_ERR_UNSUPPORTED) {
+            if (rc) return rc;
+            fused = true;
+        }
+    }
+    for (int k = 0; k < c.n_chunks && !fused; ++k) {
         const long long e0 = (long long)k * c.chunk;
         FMB_TRY(radial_weights(c, layer, e0, false, edge_limits(c) + (layer == 0 ? 0 : 1)));
         TpArgs t{};
@@ -305,7 +321,28 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
                      lin_weight_offset(ml, l), c.w->d_mid, (long long)ml.mid_dim * kC, (long long)ml.base[l] * kC,
                      ml.segs[l] * kC, l, 0);
     FMB_TRY(run_linears(c, lb));
-    for (int k = 0; k < c.n_chunks; ++k) {
+    bool fused = false;
+    // The fused adjoint executes more instructions per edge than the edge-major kernel (one reduction over channels per
+    // path) and measures slower on the 1,944-atom cell; FMB_FUSED_ADJOINT=1 selects it (it needs no weight buffer).
+    static const bool fused_adjoint = [] {
+        const char* env = std::getenv("FMB_FUSED_ADJOINT");
+        return env && env[0] == '1';
+    }();
+    if (fused_adjoint && layer > 0 && L.rad_img && tensor_cores_enabled()) {
+        FusedArgs f{};
+        f.lin = L.l_in_max; f.n_rows = c.n0; f.n_valid = rows; f.fresh_from = 0; f.first_layer_of_pass = first_layer_of_pass;
+        f.row_ptr = c.nl->edge_row_ptr; f.senders = c.nl->edge_index; f.x = c.w->x; f.edge_sh = c.w->edge_sh;
+        f.edge_vec = c.w->edge_vec; f.hidden = hidden_of(c, layer, 0); f.hidden_tangent = hidden_of(c, layer, 1);
+        f.image = L.rad_img; f.d_mid = c.w->d_mid; f.d_x = c.w->d_x; f.force_acc = c.w->force_acc;
+        f.atom_virial = c.w->atom_virial; f.error_word = c.w->status;
+        StageScope scope(c.stream, kStTpBwd1);
+        const int rc = tp_fused_backward(f, c.stream);
+        if (rc != FMB_ERR_UNSUPPORTED) {
+            if (rc) return rc;
+            fused = true;
+        }
+    }
+    for (int k = 0; k < c.n_chunks && !fused; ++k) {
         const long long e0 = (long long)k * c.chunk;
         FMB_TRY(radial_weights(c, layer, e0, true, layer == 0 ? (const long long*)c.nl->count : edge_limits(c)));
         TpArgs t{};
@@ -317,7 +354,7 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
         t.species = c.w->species; t.x = layer == 0 ? L.x_species : c.w->x;
         t.edge_sh = c.w->edge_sh; t.edge_vec = c.w->edge_vec; t.tp_w = c.w->tp_w;
         t.d_mid = c.w->d_mid; t.d_x = c.w->d_x; t.force_acc = c.w->force_acc; t.atom_virial = c.w->atom_virial;
-        t.first_layer_of_pass = first_layer_of_pass;
+        t.first_layer_of_pass = first_layer_of_pass; t.error_word = c.w->status;
         StageScope scope(c.stream, layer == 0 ? kStTpBwd0 : kStTpBwd1);
         FMB_TRY(tp_backward_launch(t, c.stream));
     }

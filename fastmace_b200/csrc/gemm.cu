@@ -119,6 +119,8 @@ static int gemm_mode() {
     return mode;
 }
 
+bool tensor_cores_enabled() { return gemm_mode() == 1; }
+
 int gemm_batch(const GemmArgs* list, int count, cudaStream_t stream) {
     int done = 0;
     while (done < count) {

@@ -40,5 +40,7 @@ int gemm_tc_batch(const GemmArgs* list, int count, cudaStream_t stream);
 int gemm_batch(const GemmArgs* list, int count, cudaStream_t stream);
 // picks gemm_tc when it applies and FMB_GEMM selects it, else gemm_simt
 int gemm(const GemmArgs& args, cudaStream_t stream);
+// false when FMB_GEMM=simt keeps every contraction on the FP32 pipes (A/B tests)
+bool tensor_cores_enabled();
 
 }  // namespace fmb

@@ -30,9 +30,37 @@ struct TpArgs {
     float* force_acc;
     float* atom_virial;
     int first_layer_of_pass;
+    uint32_t* error_word;  // device status word for bounded-wait failures of the staged kernels
 };
 int tp_forward_launch(const TpArgs& t, cudaStream_t stream);
 int tp_backward_launch(const TpArgs& t, cudaStream_t stream);
+
+// Tensor product of an interaction after the first with the last radial layer fused in (tp_fused.cu): no per-edge
+// weight matrix; one launch covers all rows.
+struct FusedArgs {
+    int lin;
+    int n_rows;            // receivers [0, n_rows)
+    int n_valid;           // adjoint: atoms [0, n_valid) have a message gradient, the others read as zero
+    int fresh_from;        // adjoint: atoms at or beyond this start their force / virial sums from zero
+    int first_layer_of_pass;
+    const int32_t* row_ptr;
+    const int32_t* senders;
+    const float* x;                // [atoms][(lin + 1)^2][C]
+    const float* edge_sh;
+    const float* edge_vec;
+    const float* hidden;           // [edges][64] last hidden radial layer of this interaction
+    const float* hidden_tangent;   // its derivative with respect to the edge length (adjoint)
+    const float* image;            // fmb_layer_t.rad_img
+    float* mid;                    // forward output
+    const float* d_mid;            // adjoint input
+    float* d_x;
+    float* force_acc;
+    float* atom_virial;
+    uint32_t* error_word;
+};
+// FMB_ERR_UNSUPPORTED when the fused kernels do not apply (no weight image, lin outside 1..2)
+int tp_fused_forward(const FusedArgs& f, cudaStream_t stream);
+int tp_fused_backward(const FusedArgs& f, cudaStream_t stream);
 
 // first layer in reassociated form (outer products per receiver and sender species)
 struct FirstArgs {

@@ -44,6 +44,29 @@ def tensor_core_twin(blocks) -> torch.Tensor:
     return torch.cat(out)
 
 
+def radial_image(w4: torch.Tensor, channels: int = 128) -> torch.Tensor:
+    """The last radial layer [64][paths * channels] (fp32, already scaled) as the fused tensor-product kernels stream it:
+    per path p, K half h and part (0 = tf32 remainder, 1 = tf32 value) one 16 KB tile [128 channels][32 features] of the
+    transposed block in the K-major operand layout with 128-byte swizzle (8-row groups of 1024 bytes, the 16-byte
+    chunk index XORed with row mod 8), at float offset ((p * 2 + h) * 2 + part) * 4096."""
+    k, n = w4.shape
+    assert k == 64 and channels == 128 and n % channels == 0
+    bt = w4.to(torch.float32).t().contiguous()                      # [paths * 128][64]
+    hi = tf32_round(bt)
+    lo = tf32_round(bt - hi)
+    row = torch.arange(128).view(128, 1)
+    kk = torch.arange(32).view(1, 32)
+    offset = (row >> 3) * 256 + (row & 7) * 32 + ((((kk >> 2) & 7) ^ (row & 7)) << 2) + (kk & 3)   # float index in a tile
+    offset = offset.reshape(-1)
+    n_paths = n // channels
+    image = torch.zeros(n_paths, 2, 2, 4096, dtype=torch.float32)
+    for p in range(n_paths):
+        for h in range(2):
+            for part, source in enumerate((lo, hi)):
+                image[p, h, part, offset] = source[p * 128:(p + 1) * 128, h * 32:(h + 1) * 32].reshape(-1)
+    return image.reshape(-1)
+
+
 def contraction_terms(spec: MaceSpec, weights, layer: int, species_z):
     """(terms int32 [T, 4], coef float64 [n_species, T, C]) of one layer's symmetric contraction, sorted by output."""
     c = spec.channels
@@ -122,6 +145,8 @@ class PackedModel:
             for i in range(4):
                 layer.rad_w[i] = self._put(f"l{t}.rad.{i}", w[f"l{t}.rad.{i}"] / math.sqrt(widths[i]))
             layer.tc[0] = self._twin(f"l{t}.rad.3", [self.tensors[f"l{t}.rad.3"]])
+            if t > 0 and c == 128:
+                layer.rad_img = self._put(f"l{t}.rad.img", radial_image(self.tensors[f"l{t}.rad.3"].cpu(), c))
             if t == 0:
                 x_species = h0 @ (w["l0.up.0"] / math.sqrt(c))
                 sc = torch.zeros(len(idx), spec.out_dim(0), c, dtype=torch.float64)
@@ -210,4 +235,4 @@ class PackedModel:
         return ctypes.byref(self.struct)
 
 
-__all__ = ["PackedModel", "contraction_terms", "tensor_core_twin", "tf32_round"]
+__all__ = ["PackedModel", "contraction_terms", "radial_image", "tensor_core_twin", "tf32_round"]

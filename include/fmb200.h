@@ -147,6 +147,11 @@ typedef struct {
      * transpose [C][n_species * 64] per l; and the tensor-core twins of both. Null = evaluate the first layer like the
      * others. */
     const float* first[4];
+    /* Last radial layer as the fused tensor-product kernels stream it into shared memory: for path p, K half h (32 of
+     * the 64 hidden features) and part (0 = tf32 remainder, 1 = tf32 value) a 16 KB tile [128 channels][32] of
+     * W4^T in the K-major 128-byte-swizzled operand layout, at float offset ((p * 2 + h) * 2 + part) * 4096.
+     * Null = materialise the per-edge weights with a GEMM. */
+    const float* rad_img;
 } fmb_layer_t;
 
 typedef struct {

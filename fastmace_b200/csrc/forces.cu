@@ -91,6 +91,15 @@ struct Ctx {
     long long chunk;
 };
 
+// When the whole edge list is one chunk, the last interaction's radial weights written by the forward pass are still
+// in tp_w when its adjoint runs (the reassociated first layer never touches tp_w), so the adjoint only adds their d/dr.
+// The forward pass then takes the unfused route (GEMM + tensor-product kernel) so that the weights exist; with more
+// than one chunk the fused kernel runs instead and the adjoint recomputes both per chunk.
+bool keeps_forward_weights(const Ctx& c, int layer) {
+    return c.n_chunks == 1 && layer > 0 && layer == c.m->n_layers - 1 && c.m->layer[0].first[0] != nullptr &&
+           c.n0 == c.n && c.n1 == c.n;
+}
+
 float* h_of(const Ctx& c, int layer) {
     return layer == 0 ? c.w->h : c.w->h + (long long)c.n * c.hidden_dim * kC;
 }
@@ -108,14 +117,15 @@ __global__ void k_edge_limits(const int32_t* __restrict__ row_ptr, int n0, int n
 
 long long* edge_limits(const Ctx& c) { return reinterpret_cast<long long*>(c.w->partial + 4096); }
 
-int radial_weights(const Ctx& c, int layer, long long e0, bool with_tangent, const long long* limit) {
+// first .. last: 0 = values, 1 = their d/dr (second half of tp_w)
+int radial_weights(const Ctx& c, int layer, long long e0, int first, int last, const long long* limit) {
     const fmb_layer_t& L = c.m->layer[layer];
     const long long rows = std::min<long long>(c.chunk, c.count_cap - e0);
     StageScope scope(c.stream, kStRadial);
     GemmArgs list[2];
-    const int count = with_tangent ? 2 : 1;
-    for (int tangent = 0; tangent < count; ++tangent) {
-        GemmArgs& g = list[tangent];
+    const int count = last - first + 1;
+    for (int tangent = first; tangent <= last; ++tangent) {
+        GemmArgs& g = list[tangent - first];
         g.a = hidden_of(c, layer, tangent) + e0 * kRadial;
         g.a_bs = kRadial;
         g.b = L.rad_w[3];
@@ -232,7 +242,7 @@ int forward_layer(const Ctx& c, int layer) {
         FMB_TRY(run_linears(c, lb));
     } else {
     bool fused = false;
-    if (layer > 0 && L.rad_img && tensor_cores_enabled()) {
+    if (layer > 0 && L.rad_img && tensor_cores_enabled() && !keeps_forward_weights(c, layer)) {
         // last radial layer inside the tensor-product kernel: no per-edge weight matrix, one launch for all rows
         FusedArgs f{};
         f.lin = L.l_in_max; f.n_rows = rows; f.row_ptr = c.nl->edge_row_ptr; f.senders = c.nl->edge_index;
@@ -247,7 +257,7 @@ int forward_layer(const Ctx& c, int layer) {
     }
     for (int k = 0; k < c.n_chunks && !fused; ++k) {
         const long long e0 = (long long)k * c.chunk;
-        FMB_TRY(radial_weights(c, layer, e0, false, edge_limits(c) + (layer == 0 ? 0 : 1)));
+        FMB_TRY(radial_weights(c, layer, e0, 0, 0, edge_limits(c) + (layer == 0 ? 0 : 1)));
         TpArgs t{};
         t.lin = L.l_in_max; t.species_x = layer == 0; t.n_atoms = c.n; t.n_rows = rows;
         t.chunk_e0 = e0; t.chunk_edges = c.chunk;
@@ -344,7 +354,8 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
     }
     for (int k = 0; k < c.n_chunks && !fused; ++k) {
         const long long e0 = (long long)k * c.chunk;
-        FMB_TRY(radial_weights(c, layer, e0, true, layer == 0 ? (const long long*)c.nl->count : edge_limits(c)));
+        FMB_TRY(radial_weights(c, layer, e0, keeps_forward_weights(c, layer) ? 1 : 0, 1,
+                               layer == 0 ? (const long long*)c.nl->count : edge_limits(c)));
         TpArgs t{};
         t.lin = L.l_in_max; t.species_x = layer == 0; t.n_atoms = c.n;
         // every atom that sends into a row with a gradient gets a force; first-layer senders are all atoms

@@ -122,6 +122,18 @@ int radial_weights(const Ctx& c, int layer, long long e0, int first, int last, c
     const fmb_layer_t& L = c.m->layer[layer];
     const long long rows = std::min<long long>(c.chunk, c.count_cap - e0);
     StageScope scope(c.stream, kStRadial);
+    if (L.rad_img && tensor_cores_enabled()) {
+        // the fused kernels' tensor-core pipeline as a plain producer (one launch per matrix)
+        bool done = true;
+        for (int tangent = first; tangent <= last && done; ++tangent) {
+            const int rc = radial_weights_tc(hidden_of(c, layer, tangent) + e0 * kRadial, L.rad_img,
+                                             c.w->tp_w + (long long)tangent * c.chunk * L.n_paths * kC, (int)rows, L.n_paths,
+                                             limit, e0, c.w->status, c.stream);
+            if (rc == FMB_ERR_UNSUPPORTED) done = false;
+            else if (rc) return rc;
+        }
+        if (done) return FMB_OK;
+    }
     GemmArgs list[2];
     const int count = last - first + 1;
     for (int tangent = first; tangent <= last; ++tangent) {

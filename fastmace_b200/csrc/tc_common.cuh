@@ -90,10 +90,10 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 // others return at once, so the kernel runs to its end (with meaningless results and the error word raised) instead of
 // spinning.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort, unsigned limit) {
-    if (*abort) return false;
-    for (unsigned spin = 0; spin < limit; ++spin) {
+    if (mbar_try(bar, parity)) return true;                 // the common case costs one instruction
+    for (unsigned spin = 1; spin < limit; ++spin) {
         if (mbar_try(bar, parity)) return true;
-        if ((spin & 255u) == 255u && *abort) return false;
+        if ((spin & 63u) == 63u && *abort) return false;
     }
     *abort = 1;
     return false;

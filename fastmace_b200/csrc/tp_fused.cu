@@ -92,6 +92,80 @@ __device__ __forceinline__ void warp_reduce_t(float (&v)[NP]) {
     for (int rest = 16 >> log2_of(NP); rest >= 1; rest >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], rest);
 }
 
+// State of the thread that feeds the tensor cores: it keeps the ring of weight pieces full (bulk copies, look-ahead
+// of NST pieces across paths, rounds and work items: the sequence of pieces is periodic) and issues the MMAs of one
+// path at a time. Counters wrap by comparison, there is no division on this thread's critical path.
+template <int TN, int NST>
+struct Feeder {
+    uint32_t bar0, ring0, tmem_base, idesc;
+    uint64_t desc_bh, desc_bl;
+    const float* image;
+    volatile int* abort_flag;
+    uint32_t pieces;                  // 4 * paths: pieces of one pass over the weight image
+    uint32_t total;                   // pieces this CTA consumes in all
+    uint32_t step = 0, load = 0;      // pieces consumed / requested
+    uint32_t st = 0, ph = 0;          // stage and parity of the next piece to consume
+    uint32_t lst = 0, lph = 1;        // stage to refill and the parity its `empty` barrier has to show
+    uint32_t piece = 0;               // next piece to request
+    uint32_t gpath = 0, ground = 0;
+
+    __device__ __forceinline__ uint32_t bar(int slot) const { return bar0 + 8u * (uint32_t)slot; }
+
+    __device__ __forceinline__ void top_up() {
+        while (load < total && load - step < (uint32_t)NST) {
+            mbar_wait(bar(kBarEmpty) + 8u * lst, lph, abort_flag, kSpin);
+            const uint32_t full = bar(kBarFull) + 8u * lst;
+            mbar_expect_tx(full, kStageBytes);
+            bulk_load(ring0 + lst * kStageBytes, image + (size_t)piece * (kStageBytes / 4), kStageBytes, full);
+            ++load;
+            if (++piece == pieces) piece = 0;
+            if (++lst == (uint32_t)NST) { lst = 0; lph ^= 1u; }
+        }
+    }
+
+    // waits until the consumers have staged the N-side operand of the next round
+    __device__ __forceinline__ void begin_round() {
+        top_up();
+        mbar_wait(bar(kBarB), ground & 1u, abort_flag, kSpin);
+        fence_after_sync();
+        ++ground;
+    }
+
+    // the 24 MMAs of one path (3xTF32: weights_lo x hidden_hi, weights_hi x hidden_lo, weights_hi x hidden_hi, per K
+    // half) into accumulator gpath & 1
+    __device__ __forceinline__ void path() {
+        const uint32_t buf = gpath & 1u;
+        mbar_wait(bar(kBarTEmpty + buf), ((gpath >> 1) & 1u) ^ 1u, abort_flag, kSpin);
+        fence_after_sync();
+        const uint32_t d = tmem_base + buf * TN;
+#pragma unroll
+        for (int s4 = 0; s4 < 4; ++s4) {
+            top_up();
+            mbar_wait(bar(kBarFull) + 8u * st, ph, abort_flag, kSpin);
+            fence_after_sync();
+            const uint64_t adesc = make_desc(ring0 + st * kStageBytes);
+            const int kh = s4 >> 1;
+            if ((s4 & 1) == 0) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    mma_tf32(d, adesc + (uint64_t)(2 * k), desc_bh + k_step<TN>(4 * kh + k), idesc, (s4 == 0 && k == 0) ? 0 : 1);
+            } else {
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    mma_tf32(d, adesc + (uint64_t)(2 * k), desc_bl + k_step<TN>(4 * kh + k), idesc, 1);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    mma_tf32(d, adesc + (uint64_t)(2 * k), desc_bh + k_step<TN>(4 * kh + k), idesc, 1);
+            }
+            mma_commit(bar(kBarEmpty) + 8u * st);
+            ++step;
+            if (++st == (uint32_t)NST) { st = 0; ph ^= 1u; }
+        }
+        mma_commit(bar(kBarTFull + buf));
+        ++gpath;
+    }
+};
+
 // sender rows of EB edge columns for one path: the path's input components of x (and, for the adjoint, the path's
 // components of the senders' message gradient; rows at or beyond n_valid read as zero)
 template <typename TP, int IN, int EB>
@@ -191,64 +265,19 @@ k_tp_fused(const __grid_constant__ FusedArgs a) {
     if (warp == 8) {
         // ------------------------------------------------------------------ tensor-core warp (one thread)
         if (lane == 0) {
+            Feeder<TN, NST> feed;
+            feed.bar0 = bar0; feed.ring0 = smem_u32(ring); feed.tmem_base = tmem_base; feed.idesc = make_idesc<TN>();
+            feed.desc_bh = make_desc(smem_u32(b_hi)); feed.desc_bl = make_desc(smem_u32(b_lo));
+            feed.image = a.image; feed.abort_flag = abort_flag; feed.pieces = 4u * P;
             uint32_t total = 0;
             for (int item = blockIdx.x; item < n_items; item += gridDim.x)
                 total += (uint32_t)item_rows(row_ptr, a.n_rows, item).rounds * (4u * P);
-            uint32_t step = 0, load = 0, gpath = 0, ground = 0;
-            const uint32_t idesc = make_idesc<TN>();
-            const uint64_t desc_bh = make_desc(smem_u32(b_hi)), desc_bl = make_desc(smem_u32(b_lo));
-            const uint32_t ring0 = smem_u32(ring);
-            const float* __restrict__ image = a.image;
-            auto top_up = [&]() {
-                while (load < total && load < step + NST) {
-                    const uint32_t st = load % NST;
-                    { FMB_T0(); mbar_wait(bar(kBarEmpty + st), ((load / NST) & 1u) ^ 1u, abort_flag, kSpin); FMB_T1(0); }
-                    mbar_expect_tx(bar(kBarFull + st), kStageBytes);
-                    bulk_load(ring0 + st * kStageBytes, image + (size_t)(load % (4u * P)) * (kStageBytes / 4), kStageBytes,
-                              bar(kBarFull + st));
-                    ++load;
-                }
-            };
+            feed.total = total;
             for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
                 const int rounds = item_rows(row_ptr, a.n_rows, item).rounds;
                 for (int r = 0; r < rounds; ++r) {
-                    top_up();
-                    { FMB_T0(); mbar_wait(bar(kBarB), ground & 1u, abort_flag, kSpin); FMB_T1(1); }
-                    fence_after_sync();
-                    for (int p = 0; p < P; ++p) {
-                        const uint32_t buf = gpath & 1u;
-                        { FMB_T0(); mbar_wait(bar(kBarTEmpty + buf), ((gpath >> 1) & 1u) ^ 1u, abort_flag, kSpin); FMB_T1(2); }
-                        fence_after_sync();
-                        const uint32_t d = tmem_base + buf * TN;
-#pragma unroll
-                        for (int s4 = 0; s4 < 4; ++s4) {
-                            top_up();
-                            const uint32_t st = step % NST;
-                            { FMB_T0(); mbar_wait(bar(kBarFull + st), (step / NST) & 1u, abort_flag, kSpin); FMB_T1(3); }
-                            fence_after_sync();
-                            const uint64_t adesc = make_desc(ring0 + st * kStageBytes);
-                            const int kh = s4 >> 1;
-                            if ((s4 & 1) == 0) {
-                                // lo part of the weights x hi part of the hidden features
-#pragma unroll
-                                for (int k = 0; k < 4; ++k)
-                                    mma_tf32(d, adesc + (uint64_t)(2 * k), desc_bh + k_step<TN>(4 * kh + k), idesc,
-                                             (s4 == 0 && k == 0) ? 0 : 1);
-                            } else {
-#pragma unroll
-                                for (int k = 0; k < 4; ++k)
-                                    mma_tf32(d, adesc + (uint64_t)(2 * k), desc_bl + k_step<TN>(4 * kh + k), idesc, 1);
-#pragma unroll
-                                for (int k = 0; k < 4; ++k)
-                                    mma_tf32(d, adesc + (uint64_t)(2 * k), desc_bh + k_step<TN>(4 * kh + k), idesc, 1);
-                            }
-                            mma_commit(bar(kBarEmpty + st));
-                            ++step;
-                        }
-                        mma_commit(bar(kBarTFull + buf));
-                        ++gpath;
-                    }
-                    ++ground;
+                    feed.begin_round();
+                    for (int p = 0; p < P; ++p) feed.path();
                 }
             }
         }
@@ -501,6 +530,140 @@ k_tp_fused(const __grid_constant__ FusedArgs a) {
     }
 }
 
+// ------------------------------------------------------------------------------------------------ weights only
+// The same tensor-core pipeline used as a plain producer of the per-edge radial weights W[e][path * 128 + channel]
+// (or of their d/dr, from the tangent features) for the edge-major kernels: tiles of 256 consecutive edges, the
+// consumers only move accumulator columns to global memory -- lane = channel, so a warp writes 128 contiguous bytes of
+// one edge row per store (a path-major layout [path][edge][128], contiguous per tile, measured slower both for this
+// kernel and for its readers). The hidden features of a tile are split and staged once for all paths, the accumulator of
+// path p is stored while the tensor cores work on path p + 1. HBM-write bound: 4 * paths * 128 bytes per edge.
+struct WeightArgs {
+    const float* hidden;          // [edges][64]
+    const float* image;           // fmb_layer_t.rad_img
+    float* out;                   // [edges][n_paths * 128]
+    const long long* limit;       // device scalar: rows at or beyond *limit - limit_offset are skipped
+    long long limit_offset;
+    int rows;                     // host bound on the rows of this launch
+    int n_paths;
+    uint32_t* error_word;
+};
+
+constexpr int kWeightStages = 4;
+constexpr int kWeightTile = 256;
+constexpr int kWeightRing = 2 * kWeightTile * 256;                    // after the hi and lo N-side operands
+constexpr int kWeightBars = kWeightRing + kWeightStages * kStageBytes;
+constexpr int kWeightBytes = kWeightBars + 256 + 16 + 1024;
+
+__global__ void __launch_bounds__(kFusedThreads, 1)
+k_radial_weights(const __grid_constant__ WeightArgs a) {
+    constexpr int TN = kWeightTile, NST = kWeightStages;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t* b_hi = smem;
+    uint8_t* b_lo = smem + TN * 256;
+    uint8_t* ring = smem + kWeightRing;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kWeightBars);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kWeightBars + 256);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kWeightBars + 260);
+    const uint32_t bar0 = smem_u32(bars);
+    auto bar = [&](int slot) { return bar0 + 8u * (uint32_t)slot; };
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int s = 0; s < NST; ++s) {
+            mbar_init(bar(kBarFull + s), 1);
+            mbar_init(bar(kBarEmpty + s), 1);
+        }
+        mbar_init(bar(kBarTFull), 1);
+        mbar_init(bar(kBarTFull + 1), 1);
+        mbar_init(bar(kBarTEmpty), 8);
+        mbar_init(bar(kBarTEmpty + 1), 8);
+        mbar_init(bar(kBarB), 8);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 8) tmem_alloc(smem_u32(tmem_slot), 2 * TN);
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    long long rows = a.rows;
+    if (a.limit) rows = min(rows, max(*a.limit - a.limit_offset, 0LL));
+    const int n_tiles = (int)((rows + TN - 1) / TN);
+    const int P = a.n_paths;
+
+    if (warp == 8) {
+        if (lane == 0) {
+            Feeder<TN, NST> feed;
+            feed.bar0 = bar0; feed.ring0 = smem_u32(ring); feed.tmem_base = tmem_base; feed.idesc = make_idesc<TN>();
+            feed.desc_bh = make_desc(smem_u32(b_hi)); feed.desc_bl = make_desc(smem_u32(b_lo));
+            feed.image = a.image; feed.abort_flag = abort_flag; feed.pieces = 4u * P;
+            uint32_t total = 0;
+            for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) total += 4u * P;
+            feed.total = total;
+            for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+                feed.begin_round();
+                for (int p = 0; p < P; ++p) feed.path();
+            }
+        }
+    } else {
+        const int wg = tid >> 7, c = tid & 127, quadrant = warp & 3;
+        const uint32_t lane_base = (uint32_t)(quadrant * 32) << 16;
+        const int ld_row = warp * 8 + (lane & 7), ld_q = lane >> 3;
+        const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        const long long ld = (long long)P * kC;
+        uint32_t gpath = 0;
+        for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+            const long long e0 = (long long)t * TN;
+#pragma unroll
+            for (int sweep = 0; sweep < TN / 64; ++sweep) {
+                const int row = ld_row + 64 * sweep;
+                const bool ok = e0 + row < rows;
+                const float* src = a.hidden + (e0 + row) * kRadial;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float4 v = ok ? __ldg(reinterpret_cast<const float4*>(src) + ld_q + 4 * j) : zero4;
+                    const float4 hi = make_float4(tf32_rna(v.x), tf32_rna(v.y), tf32_rna(v.z), tf32_rna(v.w));
+                    const float4 lo = make_float4(tf32_rna(v.x - hi.x), tf32_rna(v.y - hi.y), tf32_rna(v.z - hi.z),
+                                                  tf32_rna(v.w - hi.w));
+                    const uint32_t off = tile_offset<TN>(row, (ld_q + 4 * j) * 4);
+                    *reinterpret_cast<float4*>(b_hi + off) = hi;
+                    *reinterpret_cast<float4*>(b_lo + off) = lo;
+                }
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(kBarB));
+            const long long eg = e0 + 128 * wg;                        // first edge of this group's 128 columns
+            const int live = (int)min(128LL, max(rows - eg, 0LL));
+            for (int p = 0; p < P; ++p) {
+                const uint32_t buf = gpath & 1u;
+                const uint32_t t0 = tmem_base + lane_base + buf * TN + 128u * (uint32_t)wg;
+                mbar_wait(bar(kBarTFull + buf), (gpath >> 1) & 1u, abort_flag, kSpin);
+                fence_after_sync();
+                float* dst = a.out + eg * ld + (long long)p * kC + c;
+                for (int sb = 0; sb < live; sb += 16) {
+                    float w[16];
+                    tmem_load<16>(t0 + sb, w);
+#pragma unroll
+                    for (int q = 0; q < 16; ++q)
+                        if (sb + q < live) dst[(long long)(sb + q) * ld] = w[q];
+                }
+                fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(kBarTEmpty + buf));
+                ++gpath;
+            }
+        }
+    }
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 8) {
+        __syncwarp();
+        if (lane == 0 && *abort_flag && a.error_word) atomicOr(a.error_word, FMB_STATUS_TENSOR_TIMEOUT);
+        tmem_free(tmem_base, 2 * TN);
+    }
+}
+
 template <int LIN, bool BWD>
 int launch_fused(const FusedArgs& f, cudaStream_t stream) {
     static int sms = 0;
@@ -520,6 +683,25 @@ int launch_fused(const FusedArgs& f, cudaStream_t stream) {
 }
 
 }  // namespace
+
+int radial_weights_tc(const float* hidden, const float* image, float* out, int rows, int n_paths, const long long* limit,
+                      long long limit_offset, uint32_t* error_word, cudaStream_t stream) {
+    if (!image || n_paths < 1) return FMB_ERR_UNSUPPORTED;
+    if (rows <= 0) return FMB_OK;
+    static int sms = 0;
+    if (sms == 0) {
+        FMB_CUDA_CHECK(cudaFuncSetAttribute(k_radial_weights, cudaFuncAttributeMaxDynamicSharedMemorySize, kWeightBytes));
+        int dev = 0, count = 148;
+        FMB_CUDA_CHECK(cudaGetDevice(&dev));
+        FMB_CUDA_CHECK(cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev));
+        sms = count;
+    }
+    WeightArgs a{hidden, image, out, limit, limit_offset, rows, n_paths, error_word};
+    const int tiles = (rows + kWeightTile - 1) / kWeightTile;
+    k_radial_weights<<<tiles < sms ? tiles : sms, kFusedThreads, kWeightBytes, stream>>>(a);
+    FMB_LAUNCH_CHECK();
+    return FMB_OK;
+}
 
 int tp_fused_forward(const FusedArgs& f, cudaStream_t stream) {
     if (!f.image || f.lin < 1 || f.lin > 2) return FMB_ERR_UNSUPPORTED;

@@ -8,6 +8,7 @@
 // e3nn's FullyConnectedNet scaling (:148-150). The envelope multiplies the 8 Bessel inputs of a bias-free network, so
 // an edge at or beyond the cutoff yields exactly zero weights (fastmace/model/capabilities.py:369-394).
 
+#include "gemm.cuh"
 #include "stages.cuh"
 
 namespace fmb {
@@ -206,6 +207,203 @@ k_edge_features(EdgeParams p, const double* __restrict__ x, const int32_t* __res
     }
 }
 
+// ------------------------------------------------------------------------------------------------ tensor-core MLP
+// The same kernel with the three hidden layers on the warp-level tensor-core path (mma.sync m16n8k8, 3xTF32: value
+// and remainder parts of both operands, A_lo B_hi + A_hi B_lo + A_hi B_hi in fp32 accumulators). The layers are 64 wide:
+// a tcgen05 tile (M = 128, one issuing thread, TMEM round trips between the layers for the SiLU) would spend its time
+// on fixed costs, while here every warp owns 32 edges end to end -- activations private to the warp in shared memory
+// (only __syncwarp between layers), accumulators and the SiLU in registers. Shared-memory strides are chosen so that
+// the fragment loads are conflict-free (68 = 4 mod 32 for the A side, 72 = 8 mod 32 for the B side).
+constexpr int kLda = 68, kLdb = 72;
+constexpr int kActFloats = 32 * kLda;                       // one warp's activations (values or tangents)
+constexpr int kMmaSmemFloats = 2 * 64 * kLdb + 4 * 2 * kActFloats;
+
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return r;
+}
+
+__device__ __forceinline__ void mma_16x8x8(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// One layer for this warp's 32 edges: cv / ct [m tile][n tile][4] = act (values / tangents) [32][K] x W [K][64].
+template <int K>
+__device__ __forceinline__ void layer_mma(const float* __restrict__ av, const float* __restrict__ at,
+                                          const float* __restrict__ wh, const float* __restrict__ wl,
+                                          float (&cv)[2][8][4], float (&ct)[2][8][4]) {
+    const int lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { cv[mt][nt][i] = 0.0f; ct[mt][nt][i] = 0.0f; }
+#pragma unroll 1
+    for (int k0 = 0; k0 < K; k0 += 8) {
+        uint32_t vh[2][4], vl[2][4], th[2][4], tl[2][4];
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int off = (gid + 8 * (i & 1) + 16 * mt) * kLda + k0 + tig + 4 * (i >> 1);
+                const float v = av[off], t = at[off];
+                vh[mt][i] = to_tf32(v); vl[mt][i] = to_tf32(v - __uint_as_float(vh[mt][i]));
+                th[mt][i] = to_tf32(t); tl[mt][i] = to_tf32(t - __uint_as_float(th[mt][i]));
+            }
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            const int o0 = (k0 + tig) * kLdb + nt * 8 + gid, o1 = o0 + 4 * kLdb;
+            const uint32_t bh0 = __float_as_uint(wh[o0]), bh1 = __float_as_uint(wh[o1]);
+            const uint32_t bl0 = __float_as_uint(wl[o0]), bl1 = __float_as_uint(wl[o1]);
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+                mma_16x8x8(cv[mt][nt], vl[mt], bh0, bh1);
+                mma_16x8x8(cv[mt][nt], vh[mt], bl0, bl1);
+                mma_16x8x8(cv[mt][nt], vh[mt], bh0, bh1);
+                mma_16x8x8(ct[mt][nt], tl[mt], bh0, bh1);
+                mma_16x8x8(ct[mt][nt], th[mt], bl0, bl1);
+                mma_16x8x8(ct[mt][nt], th[mt], bh0, bh1);
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kThreads, 2)
+k_edge_features_mma(EdgeParams p, const double* __restrict__ x, const int32_t* __restrict__ edge_index,
+                    const float* __restrict__ unit_shifts, const long long* __restrict__ count_ptr,
+                    float* __restrict__ edge_vec, float* __restrict__ edge_sh, float* __restrict__ edge_hidden) {
+    extern __shared__ __align__(16) float smem[];
+    float* wh = smem;                          // [64][kLdb] tf32 values of the layer's weights
+    float* wl = smem + 64 * kLdb;              // their tf32 remainders
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, tig = lane & 3;
+    float* av = smem + 2 * 64 * kLdb + warp * 2 * kActFloats;   // this warp's activations [32][kLda]
+    float* at = av + kActFloats;                                // and their d/dr
+    const long long count = *count_ptr;
+    const long long e0 = (long long)blockIdx.x * kEdgesPerBlock;
+    if (e0 >= count) return;
+    const long long e = e0 + tid;
+    const bool live = e < count;
+    float ef[8], def[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { ef[k] = 0.0f; def[k] = 0.0f; }
+    if (live) {
+        const int s = edge_index[e], r = edge_index[p.capacity + e];
+        const double u0 = unit_shifts[3 * e], u1 = unit_shifts[3 * e + 1], u2 = unit_shifts[3 * e + 2];
+        double v[3];
+#pragma unroll
+        for (int a = 0; a < 3; ++a) {
+            const double shift = u0 * p.cell[a] + u1 * p.cell[3 + a] + u2 * p.cell[6 + a];
+            v[a] = (x[3 * r + a] - x[3 * s + a]) + shift;
+        }
+        const float vx = (float)v[0], vy = (float)v[1], vz = (float)v[2];
+        const float len = sqrtf(vx * vx + vy * vy + vz * vz);
+        const float inv = 1.0f / fmaxf(len, 1e-12f);
+        const float ux = vx * inv, uy = vy * inv, uz = vz * inv;
+        reinterpret_cast<float4*>(edge_vec)[e] = make_float4(ux, uy, uz, len);
+        float Y[16];
+        sh16(ux, uy, uz, Y);
+        float4* ysh = reinterpret_cast<float4*>(edge_sh + 16 * e);
+        ysh[0] = make_float4(Y[0], Y[1], Y[2], Y[3]);
+        ysh[1] = make_float4(Y[4], Y[5], Y[6], Y[7]);
+        ysh[2] = make_float4(Y[8], Y[9], Y[10], Y[11]);
+        ysh[3] = make_float4(Y[12], Y[13], Y[14], Y[15]);
+        if (len < p.r_cut) {
+            const float rc = p.r_cut;
+            const float xr = len / rc;
+            const float x2 = xr * xr, x4 = x2 * x2, x5 = x4 * xr;
+            const float env = 1.0f - 21.0f * x5 + 35.0f * x5 * xr - 15.0f * x5 * x2;
+            const float denv = (-105.0f * x4 + 210.0f * x5 - 105.0f * x5 * xr) / rc;
+            const float pref = sqrtf(2.0f / rc);
+            const float inv_r = 1.0f / len;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float wk = (float)(k + 1) * 3.14159265358979323846f / rc;
+                float sn, cs;
+                sincosf(wk * len, &sn, &cs);
+                const float bes = pref * sn * inv_r;
+                const float dbes = pref * (wk * cs * inv_r - sn * inv_r * inv_r);
+                ef[k] = bes * env;
+                def[k] = dbes * env + bes * denv;
+            }
+        }
+    }
+    float cv[2][8][4], ct[2][8][4];
+    for (int layer = 0; layer < p.n_layers; ++layer) {
+        for (int hidden = 0; hidden < 3; ++hidden) {
+            const int kk = hidden == 0 ? 8 : 64;
+            __syncthreads();                        // every warp is done with the previous weights
+            const float* __restrict__ wsrc = p.rad_w[layer][hidden];
+            for (int q = tid; q < kk * 64; q += kThreads) {
+                const float w = __ldg(wsrc + q);
+                const float hi = __uint_as_float(to_tf32(w));
+                const int dst = (q >> 6) * kLdb + (q & 63);
+                wh[dst] = hi;
+                wl[dst] = __uint_as_float(to_tf32(w - hi));
+            }
+            if (hidden == 0) {
+                // this thread's edge is row `lane` of its warp's tile
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    av[lane * kLda + k] = ef[k];
+                    at[lane * kLda + k] = def[k];
+                }
+            }
+            __syncthreads();
+            if (hidden == 0) layer_mma<8>(av, at, wh, wl, cv, ct);
+            else layer_mma<64>(av, at, wh, wl, cv, ct);
+            // normalised SiLU and its derivative on the accumulator fragments
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float a = cv[mt][nt][i];
+                        const float sig = 1.0f / (1.0f + expf(-a));
+                        cv[mt][nt][i] = p.silu_norm * a * sig;
+                        ct[mt][nt][i] = p.silu_norm * sig * (1.0f + a * (1.0f - sig)) * ct[mt][nt][i];
+                    }
+            if (hidden < 2) {
+                __syncwarp();                       // all lanes have read this layer's inputs
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const int off = (gid + 8 * h + 16 * mt) * kLda + nt * 8 + 2 * tig;
+                            *reinterpret_cast<float2*>(av + off) = make_float2(cv[mt][nt][2 * h], cv[mt][nt][2 * h + 1]);
+                            *reinterpret_cast<float2*>(at + off) = make_float2(ct[mt][nt][2 * h], ct[mt][nt][2 * h + 1]);
+                        }
+                __syncwarp();
+            }
+        }
+        // the third hidden layer goes to global memory: [layer][0 value / 1 tangent][edge][64]
+        float* hv = edge_hidden + ((long long)(2 * layer) * p.capacity) * 64;
+        float* ht = edge_hidden + ((long long)(2 * layer + 1) * p.capacity) * 64;
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const long long ee = e0 + warp * 32 + gid + 8 * h + 16 * mt;
+                if (ee < count) {
+#pragma unroll
+                    for (int nt = 0; nt < 8; ++nt) {
+                        *reinterpret_cast<float2*>(hv + ee * 64 + nt * 8 + 2 * tig) =
+                            make_float2(cv[mt][nt][2 * h], cv[mt][nt][2 * h + 1]);
+                        *reinterpret_cast<float2*>(ht + ee * 64 + nt * 8 + 2 * tig) =
+                            make_float2(ct[mt][nt][2 * h], ct[mt][nt][2 * h + 1]);
+                    }
+                }
+            }
+    }
+}
+
 }  // namespace
 
 int edge_features(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, const double* positions,
@@ -225,6 +423,20 @@ int edge_features(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t
         configured = true;
     }
     const int blocks = ceil_div(nl->capacity, kEdgesPerBlock);
+    if (tensor_cores_enabled()) {
+        const size_t smem_mma = (size_t)kMmaSmemFloats * sizeof(float);
+        static bool configured_mma = false;
+        if (!configured_mma) {
+            FMB_CUDA_CHECK(cudaFuncSetAttribute(k_edge_features_mma, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                (int)smem_mma));
+            configured_mma = true;
+        }
+        k_edge_features_mma<<<blocks, kThreads, smem_mma, stream>>>(p, positions, nl->edge_index, nl->unit_shifts,
+                                                                    (const long long*)nl->count, work->edge_vec,
+                                                                    work->edge_sh, work->edge_hidden);
+        FMB_LAUNCH_CHECK();
+        return FMB_OK;
+    }
     k_edge_features<<<blocks, kThreads, smem, stream>>>(p, positions, nl->edge_index, nl->unit_shifts,
                                                         (const long long*)nl->count, work->edge_vec, work->edge_sh,
                                                         work->edge_hidden);

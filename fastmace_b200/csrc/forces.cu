@@ -163,9 +163,10 @@ struct LinearBatch {
     int count = 0;
 };
 
-// `twin`: base of the weight array's tensor-core twin (or null); the block's twin starts at twice its float offset
+// `twin`, `img`: bases of the weight array's tensor-core twin and image (or null); the block's part starts at twice its
+// float offset in both
 void block_linear(LinearBatch& batch, const Ctx& c, int rows, const float* in, long long in_atom, long long in_off, int k,
-                  const float* base, const float* twin, long long w_off, float* out, long long out_atom,
+                  const float* base, const float* twin, const float* img, long long w_off, float* out, long long out_atom,
                   long long out_off, int n_out, int l, int accumulate, const int32_t* batch_species = nullptr,
                   int select = -1) {
     GemmArgs& g = batch.list[batch.count++];
@@ -177,6 +178,7 @@ void block_linear(LinearBatch& batch, const Ctx& c, int rows, const float* in, l
         g.bt_hi = twin + 2 * w_off;
         g.bt_lo = g.bt_hi + (long long)k * n_out;
     }
+    if (img) g.b_img = img + 2 * w_off;
     g.error_word = c.w->status;
     g.c = out + out_off;
     g.c_nm = nm; g.c_bs = out_atom; g.c_rs = n_out;
@@ -224,11 +226,11 @@ int forward_layer(const Ctx& c, int layer) {
         // species-dependent skip: one row-masked GEMM per present species and irrep, each row written exactly once
         for (int l = 0; l <= L.skip_lmax; ++l)
             for (int z = 0; z < c.m->n_species; ++z)
-                block_linear(lb, c, rows, h_in, (long long)h_in_dim * kC, (long long)l * l * kC, kC, L.w_skip, L.tc[3],
+                block_linear(lb, c, rows, h_in, (long long)h_in_dim * kC, (long long)l * l * kC, kC, L.w_skip, L.tc[3], L.tc_img[3],
                              ((long long)l * c.m->n_species + z) * kC * kC, h_out, (long long)out_dim * kC,
                              (long long)l * l * kC, kC, l, 0, c.w->species, z);
         for (int l = 0; l <= L.l_in_max; ++l)
-            block_linear(lb, c, c.n0, h_in, (long long)h_in_dim * kC, (long long)l * l * kC, kC, L.w_up, L.tc[1],
+            block_linear(lb, c, c.n0, h_in, (long long)h_in_dim * kC, (long long)l * l * kC, kC, L.w_up, L.tc[1], L.tc_img[1],
                          (long long)l * kC * kC, c.w->x, (long long)in_dim * kC, (long long)l * l * kC, kC, l, 0);
         FMB_TRY(run_linears(c, lb));
         x = c.w->x;
@@ -249,7 +251,7 @@ int forward_layer(const Ctx& c, int layer) {
         const long long s_atom = (long long)kNSH * nz * kRadial;
         for (int l = 0; l <= 3; ++l)
             block_linear(lb, c, rows, c.w->mid, s_atom, (long long)l * l * nz * kRadial, nz * kRadial, L.first[0],
-                         L.first[2], (long long)l * nz * kRadial * kC, msg, (long long)kNSH * kC,
+                         L.first[2], L.first_img[0], (long long)l * nz * kRadial * kC, msg, (long long)kNSH * kC,
                          (long long)l * l * kC, kC, l, 0);
         FMB_TRY(run_linears(c, lb));
     } else {
@@ -280,7 +282,7 @@ int forward_layer(const Ctx& c, int layer) {
     }
     for (int l = 0; l <= 3; ++l)
         block_linear(lb, c, rows, c.w->mid, (long long)ml.mid_dim * kC, (long long)ml.base[l] * kC, ml.segs[l] * kC, L.w_lin,
-                     L.tc[5], lin_weight_offset(ml, l), msg, (long long)kNSH * kC, (long long)l * l * kC, kC, l, 0);
+                     L.tc[5], L.tc_img[5], lin_weight_offset(ml, l), msg, (long long)kNSH * kC, (long long)l * l * kC, kC, l, 0);
     FMB_TRY(run_linears(c, lb));
     }
     {
@@ -289,7 +291,7 @@ int forward_layer(const Ctx& c, int layer) {
                                c.stream));
     }
     for (int l = 0; l <= L.l_out_max; ++l)
-        block_linear(lb, c, rows, c.w->basis, (long long)out_dim * kC, (long long)l * l * kC, kC, L.w_prod, L.tc[7],
+        block_linear(lb, c, rows, c.w->basis, (long long)out_dim * kC, (long long)l * l * kC, kC, L.w_prod, L.tc[7], L.tc_img[7],
                      (long long)l * kC * kC, h_out, (long long)out_dim * kC, (long long)l * l * kC, kC, l, 1);
     FMB_TRY(run_linears(c, lb));
     return FMB_OK;
@@ -304,12 +306,12 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
     const int rows = layer == 0 ? c.n0 : c.n1;     // atoms whose outputs of this layer carry a gradient
     LinearBatch lb;
     for (int l = 0; l <= L.l_out_max; ++l)
-        block_linear(lb, c, rows, d_h_out, (long long)out_dim * kC, (long long)l * l * kC, kC, L.w_prod_t, L.tc[8],
+        block_linear(lb, c, rows, d_h_out, (long long)out_dim * kC, (long long)l * l * kC, kC, L.w_prod_t, L.tc[8], L.tc_img[8],
                      (long long)l * kC * kC, c.w->d_basis, (long long)out_dim * kC, (long long)l * l * kC, kC, l, 0);
     if (layer > 0) {
         for (int l = 0; l <= L.skip_lmax; ++l)
             for (int z = 0; z < c.m->n_species; ++z)
-                block_linear(lb, c, rows, d_h_out, (long long)out_dim * kC, (long long)l * l * kC, kC, L.w_skip_t, L.tc[4],
+                block_linear(lb, c, rows, d_h_out, (long long)out_dim * kC, (long long)l * l * kC, kC, L.w_skip_t, L.tc[4], L.tc_img[4],
                              ((long long)l * c.m->n_species + z) * kC * kC, d_h_in, (long long)c.hidden_dim * kC,
                              (long long)l * l * kC, kC, l, 1, c.w->species, z);
     }
@@ -324,7 +326,7 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
         const int nz = c.m->n_species;
         const long long s_atom = (long long)kNSH * nz * kRadial;
         for (int l = 0; l <= 3; ++l)
-            block_linear(lb, c, rows, c.w->d_msg, (long long)kNSH * kC, (long long)l * l * kC, kC, L.first[1], L.first[3],
+            block_linear(lb, c, rows, c.w->d_msg, (long long)kNSH * kC, (long long)l * l * kC, kC, L.first[1], L.first[3], L.first_img[1],
                          (long long)l * nz * kRadial * kC, c.w->d_mid, s_atom, (long long)l * l * nz * kRadial,
                          nz * kRadial, l, 0);
         FMB_TRY(run_linears(c, lb));
@@ -339,7 +341,7 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
         return FMB_OK;
     }
     for (int l = 0; l <= 3; ++l)
-        block_linear(lb, c, rows, c.w->d_msg, (long long)kNSH * kC, (long long)l * l * kC, kC, L.w_lin_t, L.tc[6],
+        block_linear(lb, c, rows, c.w->d_msg, (long long)kNSH * kC, (long long)l * l * kC, kC, L.w_lin_t, L.tc[6], L.tc_img[6],
                      lin_weight_offset(ml, l), c.w->d_mid, (long long)ml.mid_dim * kC, (long long)ml.base[l] * kC,
                      ml.segs[l] * kC, l, 0);
     FMB_TRY(run_linears(c, lb));
@@ -383,7 +385,7 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
     }
     if (layer > 0) {
         for (int l = 0; l <= L.l_in_max; ++l)
-            block_linear(lb, c, c.n0, c.w->d_x, (long long)in_dim * kC, (long long)l * l * kC, kC, L.w_up_t, L.tc[2],
+            block_linear(lb, c, c.n0, c.w->d_x, (long long)in_dim * kC, (long long)l * l * kC, kC, L.w_up_t, L.tc[2], L.tc_img[2],
                          (long long)l * kC * kC, d_h_in, (long long)c.hidden_dim * kC, (long long)l * l * kC, kC, l, 1);
         FMB_TRY(run_linears(c, lb));
     }

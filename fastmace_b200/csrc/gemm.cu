@@ -126,7 +126,10 @@ int gemm_batch(const GemmArgs* list, int count, cudaStream_t stream) {
     while (done < count) {
         const int take = count - done < 8 ? count - done : 8;
         int rc = FMB_ERR_UNSUPPORTED;
-        if (gemm_mode() == 1) rc = gemm_tc_batch(list + done, take, stream);
+        if (gemm_mode() == 1) {
+            rc = gemm_ws_batch(list + done, take, stream);
+            if (rc == FMB_ERR_UNSUPPORTED) rc = gemm_tc_batch(list + done, take, stream);
+        }
         if (rc == FMB_ERR_UNSUPPORTED) {
             for (int q = 0; q < take; ++q) {
                 rc = gemm_simt(list[done + q], stream);

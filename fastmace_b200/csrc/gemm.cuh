@@ -14,6 +14,8 @@ struct GemmArgs {
     // optional tensor-core operands: B transposed ([n][k], K contiguous) and split into tf32 hi / lo parts
     const float* bt_hi = nullptr;
     const float* bt_lo = nullptr;
+    // optional: the same parts packed per (128 columns, 32 K) piece in the shared-memory operand layout (gemm_ws.cu)
+    const float* b_img = nullptr;
     uint32_t* error_word = nullptr;   // device status word for bounded-wait failures
     float* c = nullptr;
     int m = 0, n = 0, k = 0;
@@ -36,6 +38,8 @@ int gemm_simt(const GemmArgs& args, cudaStream_t stream);
 int gemm_tc(const GemmArgs& args, cudaStream_t stream);
 // several GEMMs (at most 8) in one launch of the tensor-core kernel; FMB_ERR_UNSUPPORTED if any does not qualify
 int gemm_tc_batch(const GemmArgs* list, int count, cudaStream_t stream);
+// warp-specialised tensor-core kernel (weights by bulk copy from b_img); FMB_ERR_UNSUPPORTED if any does not qualify
+int gemm_ws_batch(const GemmArgs* list, int count, cudaStream_t stream);
 // the same through whichever kernel applies (one launch when the tensor-core kernel takes them all)
 int gemm_batch(const GemmArgs* list, int count, cudaStream_t stream);
 // picks gemm_tc when it applies and FMB_GEMM selects it, else gemm_simt

@@ -204,6 +204,15 @@ k_gemm_tc(const __grid_constant__ Batch batch) {
     const float* __restrict__ bt_hi = pr.bt_hi;
     const float* __restrict__ bt_lo = pr.bt_lo;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef FMB_GEMM_PROFILE
+    long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const long long t_begin = clock64();
+#define GP0() const long long gp__ = clock64()
+#define GP1(slot) prof[slot] += clock64() - gp__
+#else
+#define GP0()
+#define GP1(slot)
+#endif
 
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -356,6 +365,9 @@ k_gemm_tc(const __grid_constant__ Batch batch) {
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     };
 
+#ifdef FMB_GEMM_PROFILE
+    prof[6] = clock64() - t_begin;      // set-up: alloc, barrier, descriptors
+#endif
     if (SWAP) {
         stage_weights_128();
     } else if (a_resident) {
@@ -370,15 +382,27 @@ k_gemm_tc(const __grid_constant__ Batch batch) {
     for (int nt = nt_begin; nt < nt_end && !failed; ++nt) {
         for (int kc = 0; kc < k_chunks; ++kc) {
             if (in_flight) {
+                GP0();
                 if (!mbar_wait(bar, phase)) failed = true;
                 phase ^= 1;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                GP1(0);
             }
-            if (!SWAP && !a_resident) store_a();
-            store_b();
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            if (__syncthreads_or(failed ? 1 : 0)) { failed = true; break; }
+            {
+                GP0();
+                if (!SWAP && !a_resident) store_a();
+                store_b();
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                GP1(1);
+            }
+            {
+                GP0();
+                const int any = __syncthreads_or(failed ? 1 : 0);
+                GP1(2);
+                if (any) { failed = true; break; }
+            }
             if (tid == 0) {
+                GP0();
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_d = tmem_base + (uint32_t)((nt & 1) * TN);
 #pragma unroll
@@ -393,6 +417,7 @@ k_gemm_tc(const __grid_constant__ Batch batch) {
                 }
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                              :: "r"(bar) : "memory");
+                GP1(3);
             }
             in_flight = true;
             // fetch the next item's operands while the tensor cores run
@@ -415,7 +440,16 @@ k_gemm_tc(const __grid_constant__ Batch batch) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     }
     if (__syncthreads_or(failed ? 1 : 0)) failed = true;
-    if (!failed && pending_tile >= 0) epilogue(pending_tile);
+    {
+        GP0();
+        if (!failed && pending_tile >= 0) epilogue(pending_tile);
+        GP1(5);
+    }
+#ifdef FMB_GEMM_PROFILE
+    if (blockIdx.x == 0 && (tid == 0 || tid == 64))
+        printf("gemm<%d,%d> tid %d total %lld | setup %lld wait %lld store %lld sync %lld issue %lld epilogue %lld\n", (int)SWAP, TN,
+               tid, clock64() - t_begin, prof[6], prof[0], prof[1], prof[2], prof[3], prof[5]);
+#endif
     if (failed && tid == 0 && batch.error_word) atomicOr(batch.error_word, FMB_STATUS_TENSOR_TIMEOUT);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();

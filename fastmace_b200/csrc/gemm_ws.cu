@@ -1,0 +1,271 @@
+// Warp-specialised tcgen05 / TMEM GEMM (3xTF32) for the per-irrep linears, the species skip and the first-layer
+// fold: C[r, :] (+)= A[r, :] * W with strided rows (GemmArgs), N a multiple of 128, K a multiple of 32.
+//
+// The first tensor-core GEMM of this library (gemm_tc.cu) stages both operands through registers with all threads and
+// then issues its MMAs, so every K chunk pays a global-memory round trip in series (measured: 6,000 of the 7,500
+// cycles a 64-wide chunk takes are spent waiting for the loads). Here the roles are split:
+//   * the weights never pass through registers: their tf32 value / remainder parts are packed at load time into the
+//     K-major 128-byte-swizzled operand layout, 32 KB per (128 columns, 32 K) piece, and one thread brings the pieces
+//     in with bulk copies that complete on an mbarrier;
+//   * four loader warps hold the activation rows of the next K chunk in registers while they split and store the
+//     current one (two shared-memory stages), so the loads of chunk k + 1 are in flight during chunk k;
+//   * the same thread that issues the bulk copies issues the MMAs (M = 128 rows, N = 128, K = 8 each; 12 per chunk)
+//     and commits them to the stage's `empty` barrier; after the last chunk it commits to the accumulator barrier and
+//     the loader warps turn into the epilogue (lane = row; strided rows, accumulate, species mask).
+// One CTA computes one 128 x 128 tile of C; up to eight problems share a launch. Waits are bounded (tc::mbar_wait).
+
+#include "gemm.cuh"
+#include "tc_common.cuh"
+
+#include <algorithm>
+
+namespace fmb {
+
+namespace {
+
+using namespace tc;
+
+constexpr int kWsThreads = 160;          // 4 loader / epilogue warps + the control warp
+constexpr int kWsStages = 2;
+constexpr int kWsTK = 32;                // K elements per stage
+constexpr int kWsPiece = 128 * kWsTK * 4;        // 16 KB: one of the value / remainder parts of an operand stage
+constexpr int kWsStageBytes = 4 * kWsPiece;      // A value, A remainder, W value, W remainder
+constexpr int kWsBytes = kWsStages * kWsStageBytes + 256 + 1024;
+constexpr unsigned kWsSpin = 1u << 20;
+constexpr int kWsMaxProblems = 8;
+
+struct WsRowMap {
+    int nm;
+    long long bs, rs;
+    __device__ __forceinline__ long long operator()(int r) const {
+        return nm == 1 ? (long long)r * bs : (long long)(r / nm) * bs + (long long)(r % nm) * rs;
+    }
+};
+
+struct WsProblem {
+    const float* a;
+    const float* img;            // weight image: piece (n tile, k chunk) at float offset (nt * (k / 32) + kc) * 8192
+    float* c;
+    int m, n, k;
+    WsRowMap amap, cmap;
+    int accumulate;
+    const long long* m_limit;
+    long long m_limit_offset;
+    const int32_t* batch_species;
+    int select;
+    int tile_begin;              // first CTA of this problem
+};
+
+struct WsBatch {
+    WsProblem p[kWsMaxProblems];
+    int count;
+    uint32_t* error_word;
+};
+
+// the loader thread's share (4 rows x 2 float4) of K chunk kc
+__device__ __forceinline__ void ws_fetch(const float* const (&src)[4], const bool (&ok)[4], int kc, int ld_q,
+                                         float4 (&out)[4][2]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+            out[i][j] = ok[i] ? __ldg(reinterpret_cast<const float4*>(src[i] + kc * kWsTK) + ld_q + 4 * j)
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
+// barrier slots: b_full[2], a_full[2], empty[2], acc
+constexpr int kWsBFull = 0, kWsAFull = 2, kWsEmpty = 4, kWsAcc = 6;
+
+__global__ void __launch_bounds__(kWsThreads, 1)
+k_gemm_ws(const __grid_constant__ WsBatch batch) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kWsStages * kWsStageBytes);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const uint32_t bar0 = smem_u32(bars);
+    auto bar = [&](int slot) { return bar0 + 8u * (uint32_t)slot; };
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    int which = 0;
+#pragma unroll
+    for (int q = 1; q < kWsMaxProblems; ++q)
+        if (q < batch.count && (int)blockIdx.x >= batch.p[q].tile_begin) which = q;
+    // every field the loops use is copied to registers (the record is selected with a run-time index)
+    const WsProblem& pr = batch.p[which];
+    const float* __restrict__ a = pr.a;
+    const float* __restrict__ img = pr.img;
+    float* const c_out = pr.c;
+    const WsRowMap amap = pr.amap, cmap = pr.cmap;
+    const int accumulate = pr.accumulate, select = pr.select, k = pr.k;
+    const int32_t* const batch_species = pr.batch_species;
+    int m = pr.m;
+    if (pr.m_limit) {
+        const long long lim = *pr.m_limit - pr.m_limit_offset;
+        if (lim < m) m = lim < 0 ? 0 : (int)lim;
+    }
+    const int n_tiles = pr.n >> 7;
+    const int local = blockIdx.x - pr.tile_begin;
+    const int row0 = (local / n_tiles) * 128, nt = local % n_tiles;
+    if (row0 >= m) return;
+    const int chunks = k / kWsTK;
+
+    if (tid == 0) {
+        for (int s = 0; s < kWsStages; ++s) {
+            mbar_init(bar(kWsBFull + s), 1);
+            mbar_init(bar(kWsAFull + s), 4);
+            mbar_init(bar(kWsEmpty + s), 1);
+        }
+        mbar_init(bar(kWsAcc), 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) tmem_alloc(smem_u32(tmem_slot), 128);
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t stage0 = smem_u32(smem);
+
+    if (warp == 4) {
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc<128>();
+            const float* pieces = img + (size_t)nt * chunks * (2 * kWsPiece / 4);
+            int requested = 0;
+            for (int kc = 0; kc < chunks; ++kc) {
+                // keep the weight pieces of the next stages on their way
+                while (requested < chunks && requested < kc + kWsStages) {
+                    const int s = requested % kWsStages;
+                    mbar_wait(bar(kWsEmpty + s), ((requested / kWsStages) & 1) ^ 1, abort_flag, kWsSpin);
+                    mbar_expect_tx(bar(kWsBFull + s), 2 * kWsPiece);
+                    bulk_load(stage0 + s * kWsStageBytes + 2 * kWsPiece, pieces + (size_t)requested * (2 * kWsPiece / 4),
+                              2 * kWsPiece, bar(kWsBFull + s));
+                    ++requested;
+                }
+                const int s = kc % kWsStages;
+                const uint32_t parity = (kc / kWsStages) & 1;
+                mbar_wait(bar(kWsBFull + s), parity, abort_flag, kWsSpin);
+                mbar_wait(bar(kWsAFull + s), parity, abort_flag, kWsSpin);
+                fence_after_sync();
+                const uint32_t base = stage0 + s * kWsStageBytes;
+                const uint64_t a_hi = make_desc(base), a_lo = make_desc(base + kWsPiece);
+                const uint64_t w_hi = make_desc(base + 2 * kWsPiece), w_lo = make_desc(base + 3 * kWsPiece);
+#pragma unroll
+                for (int k8 = 0; k8 < 4; ++k8)
+                    mma_tf32(tmem_base, a_lo + (uint64_t)(2 * k8), w_hi + (uint64_t)(2 * k8), idesc, (kc > 0 || k8 > 0) ? 1 : 0);
+#pragma unroll
+                for (int k8 = 0; k8 < 4; ++k8) mma_tf32(tmem_base, a_hi + (uint64_t)(2 * k8), w_lo + (uint64_t)(2 * k8), idesc, 1);
+#pragma unroll
+                for (int k8 = 0; k8 < 4; ++k8) mma_tf32(tmem_base, a_hi + (uint64_t)(2 * k8), w_hi + (uint64_t)(2 * k8), idesc, 1);
+                mma_commit(bar(kWsEmpty + s));
+            }
+            mma_commit(bar(kWsAcc));
+        }
+    } else {
+        // ------------------------------------------------------------------ loaders: 32 rows x 8 float4 per sweep
+        const int ld_row = warp * 8 + (lane & 7), ld_q = lane >> 3;
+        const float* src[4];
+        bool ok[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int row = row0 + ld_row + 32 * i;
+            ok[i] = row < m;
+            src[i] = a + (ok[i] ? amap(row) : 0);
+        }
+        float4 next[4][2];
+        ws_fetch(src, ok, 0, ld_q, next);
+        for (int kc = 0; kc < chunks; ++kc) {
+            float4 cur[4][2];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) cur[i][j] = next[i][j];
+            if (kc + 1 < chunks) ws_fetch(src, ok, kc + 1, ld_q, next);
+            const int s = kc % kWsStages;
+            mbar_wait(bar(kWsEmpty + s), ((kc / kWsStages) & 1) ^ 1, abort_flag, kWsSpin);
+            uint8_t* hi_tile = smem + s * kWsStageBytes;
+            uint8_t* lo_tile = hi_tile + kWsPiece;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const float4 v = cur[i][j];
+                    const float4 hi = make_float4(tf32_rna(v.x), tf32_rna(v.y), tf32_rna(v.z), tf32_rna(v.w));
+                    const float4 lo = make_float4(tf32_rna(v.x - hi.x), tf32_rna(v.y - hi.y), tf32_rna(v.z - hi.z),
+                                                  tf32_rna(v.w - hi.w));
+                    const uint32_t off = tile_offset<128>(ld_row + 32 * i, (ld_q + 4 * j) * 4);
+                    *reinterpret_cast<float4*>(hi_tile + off) = hi;
+                    *reinterpret_cast<float4*>(lo_tile + off) = lo;
+                }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(kWsAFull + s));
+        }
+        // ------------------------------------------------------------------ epilogue: lane = row
+        mbar_wait(bar(kWsAcc), 0, abort_flag, kWsSpin);
+        fence_after_sync();
+        const int row = row0 + warp * 32 + lane;
+        const bool write = row < m && !(batch_species && batch_species[row / cmap.nm] != select);
+        float* dst_row = c_out + (row < m ? cmap(row) : 0) + nt * 128;
+#pragma unroll 1
+        for (int col = 0; col < 128; col += 16) {
+            float v[16];
+            tmem_load<16>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col, v);
+            if (write) {
+                float4* dst = reinterpret_cast<float4*>(dst_row + col);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    float4 o = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                    if (accumulate) {
+                        const float4 old = dst[q];
+                        o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                    }
+                    dst[q] = o;
+                }
+            }
+        }
+    }
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 4) {
+        __syncwarp();
+        if (lane == 0 && *abort_flag && batch.error_word) atomicOr(batch.error_word, FMB_STATUS_TENSOR_TIMEOUT);
+        tmem_free(tmem_base, 128);
+    }
+}
+
+}  // namespace
+
+int gemm_ws_batch(const GemmArgs* list, int count, cudaStream_t stream) {
+    if (count < 1 || count > kWsMaxProblems) return FMB_ERR_UNSUPPORTED;
+    WsBatch batch{};
+    batch.count = count;
+    batch.error_word = list[0].error_word;
+    int tiles = 0;
+    for (int q = 0; q < count; ++q) {
+        const GemmArgs& g = list[q];
+        if (!g.b_img || g.n % 128 != 0 || g.k % kWsTK != 0 || g.k < kWsTK) return FMB_ERR_UNSUPPORTED;
+        FMB_REQUIRE(g.a && g.c, "gemm_ws: null operand");
+        WsProblem& p = batch.p[q];
+        p.a = g.a; p.img = g.b_img; p.c = g.c;
+        p.m = g.m; p.n = g.n; p.k = g.k;
+        p.amap = WsRowMap{g.a_nm, g.a_bs, g.a_rs};
+        p.cmap = WsRowMap{g.c_nm, g.c_bs, g.c_rs};
+        p.accumulate = g.accumulate;
+        p.m_limit = g.m_limit; p.m_limit_offset = g.m_limit_offset;
+        p.batch_species = g.batch_species; p.select = g.select;
+        p.tile_begin = tiles;
+        tiles += ceil_div(std::max(g.m, 0), 128) * (g.n / 128);
+    }
+    if (tiles == 0) return FMB_OK;
+    static bool configured = false;
+    if (!configured) {
+        FMB_CUDA_CHECK(cudaFuncSetAttribute(k_gemm_ws, cudaFuncAttributeMaxDynamicSharedMemorySize, kWsBytes));
+        configured = true;
+    }
+    k_gemm_ws<<<tiles, kWsThreads, kWsBytes, stream>>>(batch);
+    FMB_LAUNCH_CHECK();
+    return FMB_OK;
+}
+
+}  // namespace fmb

@@ -44,6 +44,38 @@ def tensor_core_twin(blocks) -> torch.Tensor:
     return torch.cat(out)
 
 
+def _swizzled_tile_index() -> torch.Tensor:
+    """Float index inside a [128 rows][32 K] operand tile (K-major, 128-byte rows in 1024-byte groups of 8 rows, the
+    16-byte chunk index XORed with row mod 8) of element (row, k), flattened row-major."""
+    row = torch.arange(128).view(128, 1)
+    kk = torch.arange(32).view(1, 32)
+    return ((row >> 3) * 256 + (row & 7) * 32 + ((((kk >> 2) & 7) ^ (row & 7)) << 2) + (kk & 3)).reshape(-1)
+
+
+def tensor_core_image(blocks) -> torch.Tensor:
+    """For a list of fp32 [K][N] weight blocks: per block (at twice its float offset, like ``tensor_core_twin``) the
+    pieces the warp-specialised GEMM copies into shared memory -- for column tile nt and K chunk kc the [128][32] tile
+    of the transposed block as 4,096 tf32 values followed by their 4,096 remainders, both in the swizzled operand
+    layout. Blocks with N % 128 != 0 or K % 32 != 0 stay zero."""
+    index = _swizzled_tile_index()
+    out = []
+    for block in blocks:
+        k, n = block.shape
+        image = torch.zeros(2 * k * n, dtype=torch.float32)
+        if n % 128 == 0 and k % 32 == 0:
+            bt = block.to(torch.float32).t().contiguous()
+            hi = tf32_round(bt)
+            lo = tf32_round(bt - hi)
+            view = image.view(n // 128, k // 32, 2, 4096)
+            for nt in range(n // 128):
+                for kc in range(k // 32):
+                    rows, cols = slice(nt * 128, nt * 128 + 128), slice(kc * 32, kc * 32 + 32)
+                    view[nt, kc, 0, index] = hi[rows, cols].reshape(-1)
+                    view[nt, kc, 1, index] = lo[rows, cols].reshape(-1)
+        out.append(image)
+    return torch.cat(out)
+
+
 def radial_image(w4: torch.Tensor, channels: int = 128) -> torch.Tensor:
     """The last radial layer [64][paths * channels] (fp32, already scaled) as the fused tensor-product kernels stream it:
     per path p, K half h and part (0 = tf32 remainder, 1 = tf32 value) one 16 KB tile [128 channels][32 features] of the
@@ -167,19 +199,25 @@ class PackedModel:
                 layer.first[0] = self._put("l0.first", torch.cat([b.reshape(-1) for b in blocks]))
                 layer.first[1] = self._put("l0.first_t", torch.cat([b.t().contiguous().reshape(-1) for b in blocks]))
                 layer.first[2] = self._twin("l0.first", blocks)
+                layer.first_img[0] = self._image_of("l0.first")
                 layer.first[3] = self._twin("l0.first_t", [b.t().contiguous() for b in blocks])
+                layer.first_img[1] = self._image_of("l0.first_t")
             else:
                 up = torch.stack([w[f"l{t}.up.{l}"] / math.sqrt(c) for l in range(spec.l_in_max(t) + 1)])
                 layer.w_up = self._put(f"l{t}.w_up", up)
                 layer.w_up_t = self._put(f"l{t}.w_up_t", up.transpose(1, 2))
                 layer.tc[1] = self._twin(f"l{t}.w_up", list(self.tensors[f"l{t}.w_up"]))
+                layer.tc_img[1] = self._image_of(f"l{t}.w_up")
                 layer.tc[2] = self._twin(f"l{t}.w_up_t", list(self.tensors[f"l{t}.w_up_t"]))
+                layer.tc_img[2] = self._image_of(f"l{t}.w_up_t")
                 skip = torch.stack([w[f"l{t}.skip.{l}"][:, idx, :].permute(1, 0, 2) / math.sqrt(c * n_el)
                                     for l in range(spec.skip_lmax(t) + 1)])     # [L, nz, C, C]
                 layer.w_skip = self._put(f"l{t}.w_skip", skip)
                 layer.w_skip_t = self._put(f"l{t}.w_skip_t", skip.transpose(2, 3))
                 layer.tc[3] = self._twin(f"l{t}.w_skip", list(self.tensors[f"l{t}.w_skip"].reshape(-1, c, c)))
+                layer.tc_img[3] = self._image_of(f"l{t}.w_skip")
                 layer.tc[4] = self._twin(f"l{t}.w_skip_t", list(self.tensors[f"l{t}.w_skip_t"].reshape(-1, c, c)))
+                layer.tc_img[4] = self._image_of(f"l{t}.w_skip_t")
             lin, lin_t, lin_blocks = [], [], []
             for l_out in range(spec.sh_lmax + 1):
                 into = so3.paths_into(paths, l_out)
@@ -191,12 +229,16 @@ class PackedModel:
             layer.w_lin = self._put(f"l{t}.w_lin", torch.cat(lin))
             layer.w_lin_t = self._put(f"l{t}.w_lin_t", torch.cat(lin_t))
             layer.tc[5] = self._twin(f"l{t}.w_lin", lin_blocks)
+            layer.tc_img[5] = self._image_of(f"l{t}.w_lin")
             layer.tc[6] = self._twin(f"l{t}.w_lin_t", [b.t().contiguous() for b in lin_blocks])
+            layer.tc_img[6] = self._image_of(f"l{t}.w_lin_t")
             prod = torch.stack([w[f"l{t}.prod.{big_l}"] / math.sqrt(c) for big_l in range(spec.l_out_max(t) + 1)])
             layer.w_prod = self._put(f"l{t}.w_prod", prod)
             layer.w_prod_t = self._put(f"l{t}.w_prod_t", prod.transpose(1, 2))
             layer.tc[7] = self._twin(f"l{t}.w_prod", list(self.tensors[f"l{t}.w_prod"]))
+            layer.tc_img[7] = self._image_of(f"l{t}.w_prod")
             layer.tc[8] = self._twin(f"l{t}.w_prod_t", list(self.tensors[f"l{t}.w_prod_t"]))
+            layer.tc_img[8] = self._image_of(f"l{t}.w_prod_t")
             terms, coefs = contraction_terms(spec, weights, t, species_z)
             layer.n_sc_terms = len(terms)
             layer.sc_terms = self._put(f"l{t}.sc_terms", torch.from_numpy(terms), dtype=torch.int32)
@@ -217,9 +259,14 @@ class PackedModel:
     def _twin(self, name: str, blocks) -> int:
         """Tensor-core twin of fp32 [K][N] blocks that are already on the device (so the split is of the fp32 values
         the SIMT path reads)."""
-        twin = tensor_core_twin([b.cpu() for b in blocks]).to(self.device)
+        host = [b.cpu() for b in blocks]
+        twin = tensor_core_twin(host).to(self.device)
         self.tensors[name + ".tc"] = twin
+        self.tensors[name + ".img"] = tensor_core_image(host).to(self.device)
         return twin.data_ptr()
+
+    def _image_of(self, name: str) -> int:
+        return self.tensors[name + ".img"].data_ptr()
 
     def species_index(self, numbers) -> torch.Tensor:
         """[N] int32 index of each atom's species among the present ones."""
@@ -235,4 +282,4 @@ class PackedModel:
         return ctypes.byref(self.struct)
 
 
-__all__ = ["PackedModel", "contraction_terms", "radial_image", "tensor_core_twin", "tf32_round"]
+__all__ = ["PackedModel", "contraction_terms", "radial_image", "tensor_core_image", "tensor_core_twin", "tf32_round"]

@@ -152,6 +152,14 @@ typedef struct {
      * W4^T in the K-major 128-byte-swizzled operand layout, at float offset ((p * 2 + h) * 2 + part) * 4096.
      * Null = materialise the per-edge weights with a GEMM. */
     const float* rad_img;
+    /* The tensor-core twins again, packed for bulk copies into shared memory (warp-specialised GEMM): for a [K][N]
+     * block at float offset o the image starts at 2 o and holds, for column tile nt (128 columns) and K chunk kc
+     * (32 rows of the block) at float offset (nt * (K / 32) + kc) * 8192, the [128][32] tile of the transposed block in
+     * the K-major 128-byte-swizzled operand layout: 4,096 tf32 values, then their 4,096 tf32 remainders. Blocks whose
+     * N is not a multiple of 128 or whose K is not a multiple of 32 are left zero (the other kernels take them).
+     * tc_img[i] belongs to tc[i] (entry 0 unused), first_img[0 / 1] to first[2 / 3]. Null = not packed. */
+    const float* tc_img[9];
+    const float* first_img[2];
 } fmb_layer_t;
 
 typedef struct {

@@ -166,3 +166,43 @@ def test_gemm_kernels_against_torch():
             _lib.check(lib.fmb_gemm(*args, 1, impl, status.data_ptr(), _lib.current_stream()), "gemm")
             assert (c.double() - 2 * ref).abs().max().item() / scale <= 2 * tol
     assert int(status.item()) == 0
+
+
+_VARIANT_SCRIPT = r"""
+import json, sys
+import numpy as np
+sys.path.insert(0, {root!r})
+from tests.test_gpu_forces import _case
+from fastmace_b200.forcefield import B200ForceField
+spec, weights, s = _case({name!r})
+ff = B200ForceField(spec, weights, s.numbers, s.cell, compute_stress=True, chunk_edges={chunk})
+e, f, st = ff.evaluate(s, stress=True)
+print("RESULT " + json.dumps(dict(e=e, f=f.tolist(), s=st.tolist())))
+"""
+
+
+@pytest.mark.parametrize("env,name,chunk", [
+    ({"FMB_FUSED_ADJOINT": "1"}, "medium", 1 << 19),      # fused forward and adjoint (weights only in tensor memory)
+    ({"FMB_FUSED_ADJOINT": "1"}, "large", 4096),          # the same over several chunks, node l_max 2
+    ({"FMB_GEMM": "simt"}, "medium", 1 << 19),            # every contraction on the FP32 pipes
+])
+def test_kernel_variants_in_subprocess(env, name, chunk):
+    """The kernel variants are selected once per process by environment variables, so each runs in a child process
+    and is compared with the oracle like the default path."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = _VARIANT_SCRIPT.format(root=root, name=name, chunk=chunk)
+    out = subprocess.run([sys.executable, "-c", script], env={**os.environ, **env}, capture_output=True, text=True,
+                         timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = [l for l in out.stdout.splitlines() if l.startswith("RESULT ")][-1]
+    got = json.loads(line[len("RESULT "):])
+    spec, weights, s = _case(name)
+    e_ref, f_ref, s_ref = _oracle(spec, weights, s)
+    de, df, ds, fscale = _report(f"{name} {env}", got["e"], np.asarray(got["f"]), np.asarray(got["s"]), e_ref, f_ref,
+                                 s_ref, s.natoms)
+    assert de <= TOL_E and df <= TOL_F and ds <= TOL_S
+    assert df <= 2e-4 * fscale + 1e-7

@@ -139,22 +139,32 @@ def build_problem(workload: str, device):
     return spec, weights, structure, ff, state, integrator, engine
 
 
-def stage_bytes(spec, n_atoms: int, n_edges: int) -> dict:
+def stage_bytes(spec, n_atoms: int, n_edges: int, n_species: int = 2) -> dict:
     """Algorithmic (compulsory) bytes per force call of each timed stage: every operand read or written once."""
     c = spec.channels
     out = {}
     hid = (spec.hidden_lmax + 1) ** 2
-    p0, p1 = len(spec.paths(0)), len(spec.paths(1))
+    p1 = len(spec.paths(1))
     from fastmace_b200 import so3
-    m0, m1 = so3.mid_dim(spec.paths(0)), so3.mid_dim(spec.paths(1))
+    m1 = so3.mid_dim(spec.paths(1))
     out["edge_features"] = n_edges * (4 + 12 + 16 + 64 + 2 * 2 * 64 * 4) + n_atoms * 24
-    # forward: w of both layers; backward: w and dw/dr of both layers; each row reads 64 hidden values
-    out["radial_gemm"] = n_edges * ((p0 + p1) * c * 4 * 3 + 6 * 64 * 4)
-    out["tp_forward_l0"] = n_edges * (p0 * c * 4 + 64 + 4) + n_atoms * m0 * c * 4
+    # second interaction only (the first is reassociated): values in the forward pass, d/dr in the adjoint; each row
+    # reads its 64 hidden features
+    out["radial_gemm"] = n_edges * 2 * (p1 * c * 4 + 64 * 4)
+    # first interaction, reassociated: per edge 64 hidden features + 16 harmonics + sender; per atom the [16][Z][64] sums
+    out["tp_forward_l0"] = n_edges * (64 * 4 + 64 + 4) + n_atoms * 16 * n_species * 64 * 4
     out["tp_forward_l1"] = n_edges * (p1 * c * 4 + 64 + 4) + n_atoms * (m1 + hid) * c * 4
-    out["tp_backward_l0"] = n_edges * (2 * p0 * c * 4 + 64 + 16 + 4) + n_atoms * (m0 * c * 4 + 36)
+    out["tp_backward_l0"] = n_edges * (2 * 64 * 4 + 64 + 16 + 4 + 16 * 64 * 4) + n_atoms * (16 * n_species * 64 * 4 + 36)
     out["tp_backward_l1"] = n_edges * (2 * p1 * c * 4 + 64 + 16 + 4) + n_atoms * ((m1 + 2 * hid) * c * 4 + 36)
     return out
+
+
+# DRAM bytes (read + write) per edge of one launch of the stage's kernel, from the ncu capture summarised in
+# profiles/ncu_full_kernels_medium_nacl_1944.md (62,218 edges; the traffic is proportional to the edge count)
+TRAFFIC_PER_EDGE = {"tp_backward_l1": (751.827200e6 + 7.498752e6) / 62218,
+                    "tp_forward_l1": (327.796224e6 + 22.227200e6) / 62218,
+                    "radial_gemm": 2 * (17.277952e6 + 260.037120e6) / 62218,
+                    "edge_features": (1.429504e6 + 15.905792e6) / 62218}
 
 
 def cpu_oracle_sample(repeats: int = 2):
@@ -446,8 +456,9 @@ def main():
     top = max((k for k in stage_ms if k in algo), key=lambda k: stage_ms[k])
     pk = peaks()
     achieved = algo[top] / (stage_ms[top] * 1e-3) / 1e9
+    traffic = TRAFFIC_PER_EDGE[top] * n_edges if top in TRAFFIC_PER_EDGE and args.workload == DEFAULT_WORKLOAD else None
     roofline = dict(bound="hbm", kernel=top, achieved=achieved, peak=pk["hbm_gbs"], unit="GB/s",
-                    frac=achieved / pk["hbm_gbs"], traffic=None, peak_source=pk["source"],
+                    frac=achieved / pk["hbm_gbs"], traffic=traffic, peak_source=pk["source"],
                     ms_per_launch=stage_ms[top] / max(1, stages[top][1] // profile_calls),
                     algorithmic_bytes=algo[top], share_of_force_call=stage_ms[top] / force_ms,
                     stage_ms={k: round(v, 5) for k, v in stage_ms.items()})

@@ -159,12 +159,16 @@ k_reduce_partial(int n_atoms, int n_energy, const float* __restrict__ node_energ
     }
 }
 
-__global__ void k_reduce_final(int blocks, const double* __restrict__ partial, double inv_volume, int compute_stress,
-                               double* __restrict__ energy, float* __restrict__ stress, uint32_t* __restrict__ status) {
-    const int q = threadIdx.x;
-    if (q >= 7) return;
+// one warp per quantity (energy, six virial components): lane l adds blocks l, l + 32, ... in order, then a butterfly
+// in fixed order -- the same sum every run
+__global__ void __launch_bounds__(7 * 32)
+k_reduce_final(int blocks, const double* __restrict__ partial, double inv_volume, int compute_stress,
+               double* __restrict__ energy, float* __restrict__ stress, uint32_t* __restrict__ status) {
+    const int q = threadIdx.x >> 5, lane = threadIdx.x & 31;
     double v = 0.0;
-    for (int b = 0; b < blocks; ++b) v += partial[b * 8 + q];
+    for (int b = lane; b < blocks; b += 32) v += partial[b * 8 + q];
+    v = warp_sum(v);
+    if (lane != 0) return;
     if (q == 0) {
         *energy = v;
         if (!(v == v) || v > 1e300 || v < -1e300) atomicOr(status, FMB_STATUS_NONFINITE);
@@ -251,7 +255,7 @@ int reduce_outputs(const fmb_model_t* m, const fmb_work_t* w, int n_energy, doub
     k_reduce_partial<<<kReduceBlocks, 256, 0, stream>>>(w->n_atoms, n_energy, w->node_energy, w->species, e0,
                                                         w->compute_stress ? w->atom_virial : nullptr, w->partial);
     FMB_LAUNCH_CHECK();
-    k_reduce_final<<<1, 32, 0, stream>>>(kReduceBlocks, w->partial, 1.0 / volume, w->compute_stress, w->energy, w->stress,
+    k_reduce_final<<<1, 7 * 32, 0, stream>>>(kReduceBlocks, w->partial, 1.0 / volume, w->compute_stress, w->energy, w->stress,
                                          w->status);
     FMB_LAUNCH_CHECK();
     k_finish_forces<<<ceil_div(3LL * w->n_atoms, 256), 256, 0, stream>>>(3 * w->n_atoms, w->force_acc, w->forces);

@@ -22,6 +22,7 @@ STATUS_ROW_OVERFLOW = 2
 STATUS_BIN_OVERFLOW = 4
 STATUS_NONFINITE = 8
 STATUS_TENSOR_TIMEOUT = 16
+STATUS_NO_MIRROR = 32
 
 EXPORTS = ("fmb_version", "fmb_last_error", "fmb_sizeof", "fmb_launch_count", "fmb_nl_build", "fmb_nl_compact", "fmb_nl_compact_static",
            "fmb_nl_needs_rebuild",
@@ -78,6 +79,7 @@ class WorkStruct(ctypes.Structure):
         ("d_x", c_void_p), ("node_energy", c_void_p), ("atom_virial", c_void_p), ("force_acc", c_void_p),
         ("partial", c_void_p), ("energy", c_void_p), ("forces", c_void_p), ("stress", c_void_p), ("status", c_void_p),
         ("n_energy_atoms", c_int32), ("n_inner_atoms", c_int32),
+        ("mirror", c_void_p), ("edge_q", c_void_p), ("edge_dx", c_void_p),
     ]
 
 

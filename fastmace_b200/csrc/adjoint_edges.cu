@@ -1,0 +1,368 @@
+// Adjoint of the interactions with per-edge hand-over instead of the mirror evaluation (used when the edge list is a
+// single chunk, so that per-edge buffers of the whole list fit).
+//
+// The mirror kernels (interaction.cu) make every receiver's CTA evaluate each of its edges twice -- as stored and in
+// the opposite direction -- because that yields the sender-side gradient and the force without a scatter; the price is
+// the gather of the mirror receiver's whole message-gradient row (20 KB per edge for the medium model), which makes
+// that kernel L2-bandwidth bound. Here every directed edge is evaluated once, in its receiver's row, and hands over
+//   * the gradient of its sender's features  dxe[e] = dE/dx_sender from this edge   ([IN][128] floats), and
+//   * the gradient of its edge vector        qe[e]  = dE/dv_e                        (3 floats),
+// and two light gather kernels finish the job through the mirror map e -> e' (the edge sender(e) <- receiver(e) with
+// the opposite image; it exists because the neighbour list is full):
+//   dE/dx_a = sum over the row of a of dxe[e'],      F_a = -(sum over the row of qe[e] - qe[e']),
+//   virial_a = sum over the row of v_e (x) qe[e].
+// Everything is summed in a fixed order; there are no atomics. Per edge the L2 traffic drops from 37 KB to about 14 KB
+// and the coupling arithmetic halves.
+//
+// Replaces autograd through conv_tp + scatter_sum (fastmace/rewrites/generic/modules.py:485-486) like the mirror
+// kernels; the reference's own edge-owned kernel scatters with atomicAdd (factorized_projected.cuh:258-353).
+
+#include "stages.cuh"
+#include "edge_gradient.cuh"
+#include "generated/tp_generated.cuh"
+
+namespace fmb {
+
+namespace {
+
+template <int LIN, bool FLIP, bool NEED_DX> struct TpBackwardSel;
+#define FMB_TP_BACKWARD_SEL(LIN_)                                                                                      \
+    template <bool FLIP, bool NEED_DX> struct TpBackwardSel<LIN_, FLIP, NEED_DX> {                                     \
+        template <typename... A> static __device__ __forceinline__ void run(A&&... a) {                               \
+            tp_backward_##LIN_<FLIP, NEED_DX>(a...);                                                                   \
+        }                                                                                                              \
+    };
+FMB_TP_BACKWARD_SEL(0)
+FMB_TP_BACKWARD_SEL(1)
+FMB_TP_BACKWARD_SEL(2)
+
+constexpr int kBatch = 8;
+
+// mirror[e] = index of the edge (sender = receiver(e), receiver = sender(e), image = -image(e)), or -1
+__global__ void k_mirror(const long long* __restrict__ count_ptr, int capacity, const int32_t* __restrict__ edge_index,
+                         const float* __restrict__ unit_shifts, const int32_t* __restrict__ row_ptr,
+                         int32_t* __restrict__ mirror, uint32_t* __restrict__ status) {
+    const long long count = *count_ptr;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < count; e += (long long)gridDim.x * blockDim.x) {
+        const int s = edge_index[e], r = edge_index[capacity + e];
+        const float u0 = -unit_shifts[3 * e], u1 = -unit_shifts[3 * e + 1], u2 = -unit_shifts[3 * e + 2];
+        // row s is sorted by (sender, image): first entry whose sender is >= r
+        int lo = row_ptr[s], hi = row_ptr[s + 1];
+        const int end = hi;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (edge_index[mid] < r) lo = mid + 1; else hi = mid;
+        }
+        int found = -1;
+        for (int q = lo; q < end && edge_index[q] == r; ++q) {
+            if (unit_shifts[3 * q] == u0 && unit_shifts[3 * q + 1] == u1 && unit_shifts[3 * q + 2] == u2) {
+                found = q;
+                break;
+            }
+        }
+        mirror[e] = found;
+        if (found < 0) atomicOr(status, FMB_STATUS_NO_MIRROR);
+    }
+}
+
+// Per-edge adjoint of the tensor product: CTA per receiver, thread per channel.
+template <int LIN>
+__global__ void __launch_bounds__(kC, 2)
+k_tp_adjoint_edges(int n_rows, int n_valid, const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ senders,
+                   const float* __restrict__ x, const float* __restrict__ edge_sh, const float* __restrict__ edge_vec,
+                   const float* __restrict__ tp_w, long long tangent_offset, const float* __restrict__ d_mid,
+                   float* __restrict__ dxe, float4* __restrict__ qe) {
+    constexpr int P = TpShape<LIN>::kPaths, IN = TpShape<LIN>::kInDim, MID = TpShape<LIN>::kMidDim;
+    __shared__ float red[kBatch][4][18];
+    const int c = threadIdx.x, warp = c >> 5, lane = c & 31;
+    for (int a = blockIdx.x; a < n_rows; a += gridDim.x) {
+        const long long rb = row_ptr[a], re = row_ptr[a + 1];
+        if (a >= n_valid) {
+            // no message gradient on this receiver: its edges hand over zeros
+            for (long long e = rb; e < re; ++e) {
+#pragma unroll
+                for (int k = 0; k < IN; ++k) dxe[(e * IN + k) * kC + c] = 0.0f;
+                if (c == 0) qe[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            continue;
+        }
+        float g_a[MID];
+#pragma unroll
+        for (int k = 0; k < MID; ++k) g_a[k] = __ldg(d_mid + ((long long)a * MID + k) * kC + c);
+        for (long long batch = rb; batch < re; batch += kBatch) {
+            const int nb = (int)min((long long)kBatch, re - batch);
+            for (int k = 0; k < nb; ++k) {
+                const long long e = batch + k;
+                const int j = senders[e];
+                float Y[16], w[P], wp[P], x_j[IN], dY[16], dxj[IN];
+                {
+                    const float4* yp = reinterpret_cast<const float4*>(edge_sh + 16 * e);
+                    const float4 y0 = __ldg(yp), y1 = __ldg(yp + 1), y2 = __ldg(yp + 2), y3 = __ldg(yp + 3);
+                    Y[0] = y0.x; Y[1] = y0.y; Y[2] = y0.z; Y[3] = y0.w; Y[4] = y1.x; Y[5] = y1.y; Y[6] = y1.z; Y[7] = y1.w;
+                    Y[8] = y2.x; Y[9] = y2.y; Y[10] = y2.z; Y[11] = y2.w; Y[12] = y3.x; Y[13] = y3.y; Y[14] = y3.z; Y[15] = y3.w;
+                }
+                const float* wr = tp_w + e * (long long)(P * kC) + c;
+#pragma unroll
+                for (int p = 0; p < P; ++p) {
+                    w[p] = __ldg(wr + p * kC);
+                    wp[p] = __ldg(wr + tangent_offset + p * kC);
+                }
+#pragma unroll
+                for (int q = 0; q < IN; ++q) {
+                    x_j[q] = __ldg(x + ((long long)j * IN + q) * kC + c);
+                    dxj[q] = 0.0f;
+                }
+#pragma unroll
+                for (int q = 0; q < 16; ++q) dY[q] = 0.0f;
+                float dr = 0.0f;
+                TpBackwardSel<LIN, false, true>::run(x_j, Y, w, wp, g_a, dY, dr, dxj);
+#pragma unroll
+                for (int q = 0; q < IN; ++q) dxe[(e * IN + q) * kC + c] = dxj[q];
+                // 16 + 1 sums over the channels: transpose-reduce inside the warp, the four warps meet in shared memory
+                {
+#pragma unroll
+                    for (int half = 8, bit = 16; half >= 1; half >>= 1, bit >>= 1) {
+                        const bool upper = (lane & bit) != 0;
+#pragma unroll
+                        for (int i = 0; i < half; ++i) {
+                            const float keep = upper ? dY[i + half] : dY[i];
+                            const float send = upper ? dY[i] : dY[i + half];
+                            dY[i] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
+                        }
+                    }
+                    dY[0] += __shfl_xor_sync(0xffffffffu, dY[0], 1);
+                }
+                dr = warp_sum(dr);
+                if ((lane & 1) == 0) red[k][warp][lane >> 1] = dY[0];
+                if (lane == 0) red[k][warp][16] = dr;
+            }
+            __syncthreads();
+            if (c < nb) {
+                const long long e = batch + c;
+                float g[16];
+#pragma unroll
+                for (int q = 0; q < 16; ++q) g[q] = red[c][0][q] + red[c][1][q] + red[c][2][q] + red[c][3][q];
+                const float drt = red[c][0][16] + red[c][1][16] + red[c][2][16] + red[c][3][16];
+                const float4 uv = __ldg(reinterpret_cast<const float4*>(edge_vec) + e);
+                float q3[3];
+                edge_vector_gradient(g, drt, uv.x, uv.y, uv.z, uv.w, q3);
+                qe[e] = make_float4(q3[0], q3[1], q3[2], 0.0f);
+            }
+            __syncthreads();
+        }
+    }
+}
+
+// dE/dx_a = sum over the row of a of the hand-over of the mirror edges (rows at or beyond n_source hand over nothing)
+template <int IN>
+__global__ void __launch_bounds__(kC)
+k_gather_dx(int n_rows, int n_source, const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ senders,
+            const int32_t* __restrict__ mirror, const float* __restrict__ dxe, float* __restrict__ d_x) {
+    const int c = threadIdx.x;
+    for (int a = blockIdx.x; a < n_rows; a += gridDim.x) {
+        float acc[IN];
+#pragma unroll
+        for (int k = 0; k < IN; ++k) acc[k] = 0.0f;
+        const long long rb = row_ptr[a], re = row_ptr[a + 1];
+        for (long long e = rb; e < re; ++e) {
+            const int m = mirror[e];
+            if (m < 0 || senders[e] >= n_source) continue;
+#pragma unroll
+            for (int k = 0; k < IN; ++k) acc[k] += __ldg(dxe + ((long long)m * IN + k) * kC + c);
+        }
+#pragma unroll
+        for (int k = 0; k < IN; ++k) d_x[((long long)a * IN + k) * kC + c] = acc[k];
+    }
+}
+
+// First interaction (reassociated form), per-edge: the receiver's gradient block [16][Z][64] in shared memory,
+// dE/dY[lm] = sum_k dS[lm, z_j, k] hidden[k], dE/dr = sum_k hidden'[k] sum_lm dS[lm, z_j, k] Y[lm]; the edge-vector
+// gradient is added to qe (rows below n_add, which the later interaction wrote) or stored.
+__global__ void __launch_bounds__(kC)
+k_first_adjoint_edges(int n_rows, int n_valid, int n_add, int n_species, const int32_t* __restrict__ row_ptr,
+                      const int32_t* __restrict__ senders, const int32_t* __restrict__ species,
+                      const float* __restrict__ edge_sh, const float* __restrict__ edge_vec,
+                      const float* __restrict__ hidden, const float* __restrict__ hidden_tangent,
+                      const float* __restrict__ d_s, float4* __restrict__ qe) {
+    __shared__ float red[kBatch][4][18];
+    extern __shared__ float own[];                        // [16][n_species][64]
+    const int c = threadIdx.x, k = c & 63, half = c >> 6, warp = c >> 5, lane = c & 31;
+    const long long row_floats = (long long)kNSH * n_species * kRadial;
+    for (int a = blockIdx.x; a < n_rows; a += gridDim.x) {
+        const long long rb = row_ptr[a], re = row_ptr[a + 1];
+        if (a >= n_valid) {
+            if (a >= n_add)
+                for (long long e = rb + c; e < re; e += kC) qe[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+            continue;
+        }
+        __syncthreads();
+        for (int q = c; q < (int)row_floats; q += kC) own[q] = __ldg(d_s + a * row_floats + q);
+        __syncthreads();
+        for (long long batch = rb; batch < re; batch += kBatch) {
+            const int nb = (int)min((long long)kBatch, re - batch);
+            for (int b = 0; b < nb; ++b) {
+                const long long e = batch + b;
+                const int zj = species[senders[e]];
+                const float h = __ldg(hidden + e * kRadial + k), hp = __ldg(hidden_tangent + e * kRadial + k);
+                const float4* yp = reinterpret_cast<const float4*>(edge_sh + 16 * e + 8 * half);
+                const float4 y0 = __ldg(yp), y1 = __ldg(yp + 1);
+                const float Y[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
+                float part[9];
+                float dh = 0.0f;
+#pragma unroll
+                for (int m = 0; m < 8; ++m) {
+                    const float cc = own[((8 * half + m) * n_species + zj) * kRadial + k];
+                    part[m] = cc * h;
+                    dh = fmaf(cc, Y[m], dh);
+                }
+                part[8] = dh * hp;
+#pragma unroll
+                for (int halfw = 4, bit = 16; halfw >= 1; halfw >>= 1, bit >>= 1) {
+                    const bool upper = (lane & bit) != 0;
+#pragma unroll
+                    for (int m = 0; m < halfw; ++m) {
+                        const float keep = upper ? part[m + halfw] : part[m];
+                        const float send = upper ? part[m] : part[m + halfw];
+                        part[m] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
+                    }
+                }
+                part[0] += __shfl_xor_sync(0xffffffffu, part[0], 2);
+                part[0] += __shfl_xor_sync(0xffffffffu, part[0], 1);
+                part[8] = warp_sum(part[8]);
+                if ((lane & 3) == 0) red[b][warp][lane >> 2] = part[0];
+                if (lane == 0) red[b][warp][16] = part[8];
+            }
+            __syncthreads();
+            if (c < nb) {
+                const long long e = batch + c;
+                float g[16];
+#pragma unroll
+                for (int m = 0; m < 8; ++m) {
+                    g[m] = red[c][0][m] + red[c][1][m];
+                    g[8 + m] = red[c][2][m] + red[c][3][m];
+                }
+                const float drt = red[c][0][16] + red[c][1][16] + red[c][2][16] + red[c][3][16];
+                const float4 uv = __ldg(reinterpret_cast<const float4*>(edge_vec) + e);
+                float q3[3];
+                edge_vector_gradient(g, drt, uv.x, uv.y, uv.z, uv.w, q3);
+                float4 out = make_float4(q3[0], q3[1], q3[2], 0.0f);
+                if (a < n_add) {
+                    const float4 old = qe[e];
+                    out.x += old.x; out.y += old.y; out.z += old.z;
+                }
+                qe[e] = out;
+            }
+            __syncthreads();
+        }
+    }
+}
+
+// F_a = -(sum_row qe[e] - qe[mirror e]), virial_a = sum_row v_e (x) qe[e]; one warp per atom, lanes over its edges,
+// folded with a fixed butterfly.
+__global__ void __launch_bounds__(256)
+k_force_gather(int n_atoms, const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ mirror,
+               const float4* __restrict__ qe, const float* __restrict__ edge_vec, float* __restrict__ force_acc,
+               float* __restrict__ atom_virial) {
+    const int a = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (a >= n_atoms) return;
+    float f[3] = {0.f, 0.f, 0.f}, vir[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (long long e = row_ptr[a] + lane; e < row_ptr[a + 1]; e += 32) {
+        const float4 q = qe[e];
+        const int m = mirror[e];
+        const float4 qm = m >= 0 ? qe[m] : make_float4(0.f, 0.f, 0.f, 0.f);
+        f[0] += q.x - qm.x; f[1] += q.y - qm.y; f[2] += q.z - qm.z;
+        const float4 uv = __ldg(reinterpret_cast<const float4*>(edge_vec) + e);
+        const float vx = uv.x * uv.w, vy = uv.y * uv.w, vz = uv.z * uv.w;
+        vir[0] += vx * q.x; vir[1] += vy * q.y; vir[2] += vz * q.z;
+        vir[3] += 0.5f * (vy * q.z + vz * q.y);
+        vir[4] += 0.5f * (vx * q.z + vz * q.x);
+        vir[5] += 0.5f * (vx * q.y + vy * q.x);
+    }
+#pragma unroll
+    for (int q = 0; q < 3; ++q) f[q] = warp_sum(f[q]);
+#pragma unroll
+    for (int q = 0; q < 6; ++q) vir[q] = warp_sum(vir[q]);
+    if (lane == 0) {
+#pragma unroll
+        for (int q = 0; q < 3; ++q) force_acc[3 * (long long)a + q] = f[q];
+#pragma unroll
+        for (int q = 0; q < 6; ++q) atom_virial[6 * (long long)a + q] = vir[q];
+    }
+}
+
+int grid_for(const void* kernel, int rows, int threads, size_t smem) {
+    int per_sm = 0, sms = 148, dev = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess || per_sm < 1) per_sm = 1;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int cap = per_sm * sms * 4;
+    return rows < cap ? rows : cap;
+}
+
+}  // namespace
+
+int mirror_map(const fmb_nl_t* nl, int32_t* mirror, uint32_t* status, cudaStream_t stream) {
+    const int blocks = ceil_div(nl->capacity, 256);
+    k_mirror<<<blocks < 1184 ? blocks : 1184, 256, 0, stream>>>((const long long*)nl->count, nl->capacity, nl->edge_index,
+                                                               nl->unit_shifts, nl->edge_row_ptr, mirror, status);
+    FMB_LAUNCH_CHECK();
+    return FMB_OK;
+}
+
+int tp_adjoint_edges(const EdgeAdjointArgs& t, cudaStream_t stream) {
+    if (t.n_rows <= 0) return FMB_OK;
+    if (t.lin == 0) {
+        static const int grid_cap = grid_for((const void*)k_tp_adjoint_edges<0>, 1 << 30, kC, 0);
+        k_tp_adjoint_edges<0><<<t.n_rows < grid_cap ? t.n_rows : grid_cap, kC, 0, stream>>>(
+            t.n_rows, t.n_valid, t.row_ptr, t.senders, t.x, t.edge_sh, t.edge_vec, t.tp_w, t.tangent_offset, t.d_mid, t.dxe,
+            reinterpret_cast<float4*>(t.qe));
+    } else if (t.lin == 1) {
+        static const int grid_cap = grid_for((const void*)k_tp_adjoint_edges<1>, 1 << 30, kC, 0);
+        k_tp_adjoint_edges<1><<<t.n_rows < grid_cap ? t.n_rows : grid_cap, kC, 0, stream>>>(
+            t.n_rows, t.n_valid, t.row_ptr, t.senders, t.x, t.edge_sh, t.edge_vec, t.tp_w, t.tangent_offset, t.d_mid, t.dxe,
+            reinterpret_cast<float4*>(t.qe));
+    } else if (t.lin == 2) {
+        static const int grid_cap = grid_for((const void*)k_tp_adjoint_edges<2>, 1 << 30, kC, 0);
+        k_tp_adjoint_edges<2><<<t.n_rows < grid_cap ? t.n_rows : grid_cap, kC, 0, stream>>>(
+            t.n_rows, t.n_valid, t.row_ptr, t.senders, t.x, t.edge_sh, t.edge_vec, t.tp_w, t.tangent_offset, t.d_mid, t.dxe,
+            reinterpret_cast<float4*>(t.qe));
+    } else {
+        return FMB_ERR_UNSUPPORTED;
+    }
+    FMB_LAUNCH_CHECK();
+    const int in_dim = (t.lin + 1) * (t.lin + 1);
+    if (in_dim == 1) {
+        k_gather_dx<1><<<t.n_rows < 1184 ? t.n_rows : 1184, kC, 0, stream>>>(t.n_rows, t.n_rows, t.row_ptr, t.senders, t.mirror,
+                                                                              t.dxe, t.d_x);
+    } else if (in_dim == 4) {
+        k_gather_dx<4><<<t.n_rows < 1184 ? t.n_rows : 1184, kC, 0, stream>>>(t.n_rows, t.n_rows, t.row_ptr, t.senders, t.mirror,
+                                                                              t.dxe, t.d_x);
+    } else {
+        k_gather_dx<9><<<t.n_rows < 1184 ? t.n_rows : 1184, kC, 0, stream>>>(t.n_rows, t.n_rows, t.row_ptr, t.senders, t.mirror,
+                                                                              t.dxe, t.d_x);
+    }
+    FMB_LAUNCH_CHECK();
+    return FMB_OK;
+}
+
+int first_adjoint_edges(const FirstArgs& f, int n_add, float* qe, cudaStream_t stream) {
+    if (f.n_rows <= 0) return FMB_OK;
+    const size_t smem = (size_t)f.n_species * kNSH * kRadial * sizeof(float);
+    static int grid_cap = 0;
+    if (grid_cap == 0) grid_cap = grid_for((const void*)k_first_adjoint_edges, 1 << 30, kC, smem);
+    k_first_adjoint_edges<<<f.n_rows < grid_cap ? f.n_rows : grid_cap, kC, smem, stream>>>(
+        f.n_rows, f.n_valid, n_add, f.n_species, f.row_ptr, f.senders, f.species, f.edge_sh, f.edge_vec, f.hidden,
+        f.hidden_tangent, f.d_s, reinterpret_cast<float4*>(qe));
+    FMB_LAUNCH_CHECK();
+    return FMB_OK;
+}
+
+int force_gather(int n_atoms, const int32_t* row_ptr, const int32_t* mirror, const float* qe, const float* edge_vec,
+                 float* force_acc, float* atom_virial, cudaStream_t stream) {
+    if (n_atoms <= 0) return FMB_OK;
+    k_force_gather<<<ceil_div(n_atoms, 8), 256, 0, stream>>>(n_atoms, row_ptr, mirror, reinterpret_cast<const float4*>(qe),
+                                                             edge_vec, force_acc, atom_virial);
+    FMB_LAUNCH_CHECK();
+    return FMB_OK;
+}
+
+}  // namespace fmb

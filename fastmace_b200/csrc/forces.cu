@@ -100,6 +100,13 @@ bool keeps_forward_weights(const Ctx& c, int layer) {
            c.n0 == c.n && c.n1 == c.n;
 }
 
+// Per-edge hand-over adjoint (adjoint_edges.cu) instead of the mirror evaluation: the buffers exist, the list is one
+// chunk and the first interaction is in its reassociated form (its per-edge kernel closes the chain).
+bool edge_local_adjoint(const Ctx& c) {
+    return c.n_chunks == 1 && c.w->mirror && c.w->edge_q && c.w->edge_dx && c.m->n_layers == 2 &&
+           c.m->layer[0].first[0] != nullptr;
+}
+
 float* h_of(const Ctx& c, int layer) {
     return layer == 0 ? c.w->h : c.w->h + (long long)c.n * c.hidden_dim * kC;
 }
@@ -337,6 +344,14 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
         f.hidden = hidden_of(c, 0, 0); f.hidden_tangent = hidden_of(c, 0, 1); f.d_s = c.w->d_mid;
         f.force_acc = c.w->force_acc; f.atom_virial = c.w->atom_virial; f.first_layer_of_pass = first_layer_of_pass;
         StageScope scope(c.stream, kStTpBwd0);
+        if (edge_local_adjoint(c)) {
+            // the later interaction has written the edge-vector gradients of the rows below n0; add this one's and
+            // turn the per-edge gradients into forces and virials
+            FMB_TRY(first_adjoint_edges(f, first_layer_of_pass ? 0 : c.n0, c.w->edge_q, c.stream));
+            FMB_TRY(force_gather(c.n, c.nl->edge_row_ptr, c.w->mirror, c.w->edge_q, c.w->edge_vec, c.w->force_acc,
+                                 c.w->atom_virial, c.stream));
+            return FMB_OK;
+        }
         FMB_TRY(first_backward_launch(f, c.stream));
         return FMB_OK;
     }
@@ -345,6 +360,24 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
                      lin_weight_offset(ml, l), c.w->d_mid, (long long)ml.mid_dim * kC, (long long)ml.base[l] * kC,
                      ml.segs[l] * kC, l, 0);
     FMB_TRY(run_linears(c, lb));
+    if (layer > 0 && edge_local_adjoint(c)) {
+        const long long* limit = edge_limits(c);
+        FMB_TRY(radial_weights(c, layer, 0, keeps_forward_weights(c, layer) ? 1 : 0, 1, limit));
+        EdgeAdjointArgs t{};
+        t.lin = L.l_in_max; t.n_rows = c.n0; t.n_valid = rows; t.row_ptr = c.nl->edge_row_ptr; t.senders = c.nl->edge_index;
+        t.mirror = c.w->mirror; t.x = c.w->x; t.edge_sh = c.w->edge_sh; t.edge_vec = c.w->edge_vec; t.tp_w = c.w->tp_w;
+        t.tangent_offset = c.chunk * L.n_paths * kC; t.d_mid = c.w->d_mid; t.dxe = c.w->edge_dx; t.qe = c.w->edge_q;
+        t.d_x = c.w->d_x;
+        {
+            StageScope scope(c.stream, kStTpBwd1);
+            FMB_TRY(tp_adjoint_edges(t, c.stream));
+        }
+        for (int l = 0; l <= L.l_in_max; ++l)
+            block_linear(lb, c, c.n0, c.w->d_x, (long long)in_dim * kC, (long long)l * l * kC, kC, L.w_up_t, L.tc[2], L.tc_img[2],
+                         (long long)l * kC * kC, d_h_in, (long long)c.hidden_dim * kC, (long long)l * l * kC, kC, l, 1);
+        FMB_TRY(run_linears(c, lb));
+        return FMB_OK;
+    }
     bool fused = false;
     // The fused adjoint executes more instructions per edge than the edge-major kernel (one reduction over channels per
     // path) and measures slower on the 1,944-atom cell; FMB_FUSED_ADJOINT=1 selects it (it needs no weight buffer).
@@ -428,7 +461,12 @@ extern "C" FMB_API int fmb_edge_features(const fmb_model_t* model, const fmb_nl_
                                  const double* positions, fmb_stream_t stream) {
     FMB_REQUIRE(model && nl && work && positions, "fmb_edge_features: null argument");
     StageScope scope((cudaStream_t)stream, kStEdge);
-    return edge_features(model, nl, work, positions, (cudaStream_t)stream);
+    const int rc = edge_features(model, nl, work, positions, (cudaStream_t)stream);
+    if (rc) return rc;
+    // opposite-edge map for the per-edge adjoint (the compaction reorders edges every step)
+    if (work->mirror && work->edge_q && work->edge_dx && work->chunk_edges >= nl->capacity)
+        return mirror_map(nl, work->mirror, work->status, (cudaStream_t)stream);
+    return FMB_OK;
 }
 
 extern "C" FMB_API int fmb_forward(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, fmb_stream_t stream) {

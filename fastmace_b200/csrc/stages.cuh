@@ -87,6 +87,33 @@ struct FirstArgs {
 int first_accumulate_launch(const FirstArgs& f, cudaStream_t stream);
 int first_backward_launch(const FirstArgs& f, cudaStream_t stream);
 
+// Adjoint with per-edge hand-over (adjoint_edges.cu)
+struct EdgeAdjointArgs {
+    int lin;
+    int n_rows;            // receivers [0, n_rows)
+    int n_valid;           // atoms [0, n_valid) have a message gradient
+    const int32_t* row_ptr;
+    const int32_t* senders;
+    const int32_t* mirror;
+    const float* x;
+    const float* edge_sh;
+    const float* edge_vec;
+    const float* tp_w;             // [edges][paths * C] values, d/dr behind them at tangent_offset
+    long long tangent_offset;
+    const float* d_mid;
+    float* dxe;                    // [edges][(lin + 1)^2][C]
+    float* qe;                     // [edges][4]
+    float* d_x;                    // [n_rows][(lin + 1)^2][C]
+};
+int mirror_map(const fmb_nl_t* nl, int32_t* mirror, uint32_t* status, cudaStream_t stream);
+// per-edge adjoint of an interaction after the first, then the gather of the sender-side gradient into d_x
+int tp_adjoint_edges(const EdgeAdjointArgs& t, cudaStream_t stream);
+// first interaction: adds its edge-vector gradients to qe (rows below n_add) or stores them
+int first_adjoint_edges(const FirstArgs& f, int n_add, float* qe, cudaStream_t stream);
+// forces (as gradients) and per-atom virials from the per-edge gradients
+int force_gather(int n_atoms, const int32_t* row_ptr, const int32_t* mirror, const float* qe, const float* edge_vec,
+                 float* force_acc, float* atom_virial, cudaStream_t stream);
+
 int symcon_forward(int n_atoms, int n_terms, int out_dim, const int32_t* terms, const float* coef,
                    const int32_t* species, const float* msg, float* basis, cudaStream_t stream);
 int symcon_backward(int n_atoms, int n_terms, int out_dim, const int32_t* terms, const float* coef,

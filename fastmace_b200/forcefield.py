@@ -130,6 +130,12 @@ class B200ForceField:
             "force_acc": torch.zeros(n, 3, **f32),
             "partial": torch.zeros(1024 * 8, dtype=torch.float64, device=dev),
         }
+        # per-edge hand-over buffers of the adjoint: only when the whole edge list is one chunk
+        self.edge_local = cap <= chunk
+        if self.edge_local:
+            buf["mirror"] = torch.zeros(cap, dtype=torch.int32, device=dev)
+            buf["edge_q"] = torch.zeros(cap, 4, **f32)
+            buf["edge_dx"] = torch.zeros(cap, hid, c, **f32)
         self.buf = buf
         w = _lib.WorkStruct()
         w.n_atoms, w.edge_capacity, w.chunk_edges, w.compute_stress = n, cap, chunk, int(self._compute_stress)
@@ -190,8 +196,13 @@ class B200ForceField:
 
     def check_status(self) -> None:
         self.neighbours.check_status()
-        if int(self.status.item()) & _lib.STATUS_NONFINITE:
+        status = int(self.status.item())
+        if status & _lib.STATUS_NONFINITE:
             raise _lib.Fmb200Error("the force call produced a non-finite energy")
+        if status & _lib.STATUS_NO_MIRROR:
+            raise _lib.Fmb200Error("an edge has no opposite edge: the neighbour list is not full")
+        if status & _lib.STATUS_TENSOR_TIMEOUT:
+            raise _lib.Fmb200Error("a tensor-core kernel gave up waiting (FMB_STATUS_TENSOR_TIMEOUT)")
 
     def per_atom_energies(self):
         return self.buf["node_energy"].double().cpu().numpy()

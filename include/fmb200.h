@@ -35,6 +35,7 @@ extern "C" {
 #define FMB_STATUS_BIN_OVERFLOW 4u    /* internal: cell-list bins inconsistent */
 #define FMB_STATUS_NONFINITE 8u       /* a non-finite energy was produced */
 #define FMB_STATUS_TENSOR_TIMEOUT 16u /* a tensor-core kernel gave up waiting for its own MMA completion barrier */
+#define FMB_STATUS_NO_MIRROR 32u      /* an edge has no opposite edge: the neighbour list is not a full list */
 
 #define FMB_MAX_ROW 1024              /* candidates per receiver the in-kernel sort can hold */
 #define FMB_MAX_LAYERS 2
@@ -215,6 +216,13 @@ typedef struct {
      * species-only senders of the first layer. Forces come out for every atom (partial sums for halo atoms). */
     int32_t n_energy_atoms;
     int32_t n_inner_atoms;
+    /* Optional per-edge hand-over buffers of the adjoint (all three or none; used when the edge list is one chunk):
+     * mirror [edge_capacity] int32 (index of the opposite edge), edge_q [edge_capacity][4] (gradient of the edge vector),
+     * edge_dx [edge_capacity][(hidden_lmax + 1)^2][C] (gradient of the sender's features from that edge). Null = the
+     * mirror-evaluation kernels. */
+    int32_t* mirror;
+    float* edge_q;
+    float* edge_dx;
 } fmb_work_t;
 
 /* MACEForceField.__call__ (fastmace/model/forces.py:1127-1136,1220-1240): energy (float64), forces and stress of the

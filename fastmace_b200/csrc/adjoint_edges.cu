@@ -21,6 +21,8 @@
 #include "edge_gradient.cuh"
 #include "generated/tp_generated.cuh"
 
+#include <cstdlib>
+
 namespace fmb {
 
 namespace {
@@ -66,8 +68,8 @@ __global__ void k_mirror(const long long* __restrict__ count_ptr, int capacity, 
 }
 
 // Per-edge adjoint of the tensor product: CTA per receiver, thread per channel.
-template <int LIN>
-__global__ void __launch_bounds__(kC, 2)
+template <int LIN, int MINB>
+__global__ void __launch_bounds__(kC, MINB)
 k_tp_adjoint_edges(int n_rows, int n_valid, const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ senders,
                    const float* __restrict__ x, const float* __restrict__ edge_sh, const float* __restrict__ edge_vec,
                    const float* __restrict__ tp_w, long long tangent_offset, const float* __restrict__ d_mid,
@@ -164,11 +166,25 @@ k_gather_dx(int n_rows, int n_source, const int32_t* __restrict__ row_ptr, const
 #pragma unroll
         for (int k = 0; k < IN; ++k) acc[k] = 0.0f;
         const long long rb = row_ptr[a], re = row_ptr[a + 1];
-        for (long long e = rb; e < re; ++e) {
-            const int m = mirror[e];
-            if (m < 0 || senders[e] >= n_source) continue;
+        // four edges at a time: their mirror indices first, then all the rows, so that the loads overlap
+        for (long long e = rb; e < re; e += 4) {
+            int m[4];
 #pragma unroll
-            for (int k = 0; k < IN; ++k) acc[k] += __ldg(dxe + ((long long)m * IN + k) * kC + c);
+            for (int q = 0; q < 4; ++q) {
+                const bool live = e + q < re;
+                m[q] = live ? mirror[e + q] : -1;
+                if (live && senders[e + q] >= n_source) m[q] = -1;
+            }
+            float v[4][IN];
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+#pragma unroll
+                for (int k = 0; k < IN; ++k)
+                    v[q][k] = m[q] >= 0 ? __ldg(dxe + ((long long)m[q] * IN + k) * kC + c) : 0.0f;
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+#pragma unroll
+                for (int k = 0; k < IN; ++k) acc[k] += v[q][k];
         }
 #pragma unroll
         for (int k = 0; k < IN; ++k) d_x[((long long)a * IN + k) * kC + c] = acc[k];
@@ -311,18 +327,31 @@ int mirror_map(const fmb_nl_t* nl, int32_t* mirror, uint32_t* status, cudaStream
 int tp_adjoint_edges(const EdgeAdjointArgs& t, cudaStream_t stream) {
     if (t.n_rows <= 0) return FMB_OK;
     if (t.lin == 0) {
-        static const int grid_cap = grid_for((const void*)k_tp_adjoint_edges<0>, 1 << 30, kC, 0);
-        k_tp_adjoint_edges<0><<<t.n_rows < grid_cap ? t.n_rows : grid_cap, kC, 0, stream>>>(
+        static const int grid_cap = grid_for((const void*)k_tp_adjoint_edges<0, 2>, 1 << 30, kC, 0);
+        k_tp_adjoint_edges<0, 2><<<t.n_rows < grid_cap ? t.n_rows : grid_cap, kC, 0, stream>>>(
             t.n_rows, t.n_valid, t.row_ptr, t.senders, t.x, t.edge_sh, t.edge_vec, t.tp_w, t.tangent_offset, t.d_mid, t.dxe,
             reinterpret_cast<float4*>(t.qe));
     } else if (t.lin == 1) {
-        static const int grid_cap = grid_for((const void*)k_tp_adjoint_edges<1>, 1 << 30, kC, 0);
-        k_tp_adjoint_edges<1><<<t.n_rows < grid_cap ? t.n_rows : grid_cap, kC, 0, stream>>>(
-            t.n_rows, t.n_valid, t.row_ptr, t.senders, t.x, t.edge_sh, t.edge_vec, t.tp_w, t.tangent_offset, t.d_mid, t.dxe,
-            reinterpret_cast<float4*>(t.qe));
+        static const int occupancy = [] {
+            const char* env = std::getenv("FMB_ADJOINT_OCCUPANCY");      // CTAs per SM the compiler targets (tuning knob)
+            return env ? std::atoi(env) : 4;
+        }();
+#define FMB_ADJ1(MINB_)                                                                                                \
+    {                                                                                                                  \
+        static const int grid_cap = grid_for((const void*)k_tp_adjoint_edges<1, MINB_>, 1 << 30, kC, 0);               \
+        k_tp_adjoint_edges<1, MINB_><<<t.n_rows < grid_cap ? t.n_rows : grid_cap, kC, 0, stream>>>(                    \
+            t.n_rows, t.n_valid, t.row_ptr, t.senders, t.x, t.edge_sh, t.edge_vec, t.tp_w, t.tangent_offset, t.d_mid, t.dxe, \
+            reinterpret_cast<float4*>(t.qe));                                                                          \
+    }
+        if (occupancy >= 6) FMB_ADJ1(6)
+        else if (occupancy == 5) FMB_ADJ1(5)
+        else if (occupancy == 4) FMB_ADJ1(4)
+        else if (occupancy == 3) FMB_ADJ1(3)
+        else FMB_ADJ1(2)
+#undef FMB_ADJ1
     } else if (t.lin == 2) {
-        static const int grid_cap = grid_for((const void*)k_tp_adjoint_edges<2>, 1 << 30, kC, 0);
-        k_tp_adjoint_edges<2><<<t.n_rows < grid_cap ? t.n_rows : grid_cap, kC, 0, stream>>>(
+        static const int grid_cap = grid_for((const void*)k_tp_adjoint_edges<2, 2>, 1 << 30, kC, 0);
+        k_tp_adjoint_edges<2, 2><<<t.n_rows < grid_cap ? t.n_rows : grid_cap, kC, 0, stream>>>(
             t.n_rows, t.n_valid, t.row_ptr, t.senders, t.x, t.edge_sh, t.edge_vec, t.tp_w, t.tangent_offset, t.d_mid, t.dxe,
             reinterpret_cast<float4*>(t.qe));
     } else {

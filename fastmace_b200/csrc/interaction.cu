@@ -80,6 +80,8 @@ k_tp_forward(int n_atoms, int n_rows, long long chunk_e0, long long chunk_edges,
             for (int k = 0; k < MID; ++k) acc[k] = 0.0f;
         }
         const long long b = max(rb, e0), en = min(re, e1);
+        // unrolled so that the loads of several edges are in flight together (the loop is bound by their latency)
+#pragma unroll 4
         for (long long e = b; e < en; ++e) {
             const int s = senders[e];
             float xs[IN], Y[16], w[P];

@@ -70,15 +70,31 @@ __global__ void k_mirror(const long long* __restrict__ count_ptr, int capacity, 
 // Per-edge adjoint of the tensor product: CTA per receiver, thread per channel.
 template <int LIN, int MINB>
 __global__ void __launch_bounds__(kC, MINB)
-k_tp_adjoint_edges(int n_rows, int n_valid, const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ senders,
-                   const float* __restrict__ x, const float* __restrict__ edge_sh, const float* __restrict__ edge_vec,
-                   const float* __restrict__ tp_w, long long tangent_offset, const float* __restrict__ d_mid,
-                   float* __restrict__ dxe, float4* __restrict__ qe) {
+k_tp_adjoint_edges(int n_atoms, int n_rows, int n_valid, long long chunk_e0, long long chunk_edges,
+                   const long long* __restrict__ count_ptr, const int32_t* __restrict__ row_ptr,
+                   const int32_t* __restrict__ senders, const float* __restrict__ x, const float* __restrict__ edge_sh,
+                   const float* __restrict__ edge_vec, const float* __restrict__ tp_w, long long tangent_offset,
+                   const float* __restrict__ d_mid, float* __restrict__ dxe, float4* __restrict__ qe) {
     constexpr int P = TpShape<LIN>::kPaths, IN = TpShape<LIN>::kInDim, MID = TpShape<LIN>::kMidDim;
     __shared__ float red[kBatch][4][18];
     const int c = threadIdx.x, warp = c >> 5, lane = c & 31;
-    for (int a = blockIdx.x; a < n_rows; a += gridDim.x) {
-        const long long rb = row_ptr[a], re = row_ptr[a + 1];
+    // this launch covers the edges [e0, e1) (a chunk of the list: tp_w holds their weights); a row that straddles two
+    // chunks is simply visited by both, every edge is independent
+    const long long count = *count_ptr;
+    const long long e0 = chunk_e0, e1 = min(count, chunk_e0 + chunk_edges);
+    if (e0 >= e1) return;
+    int first = 0;
+    if (e0 > 0) {
+        int lo = 0, hi = n_atoms;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (row_ptr[mid + 1] > e0) hi = mid; else lo = mid + 1;
+        }
+        first = lo;
+    }
+    for (int a = first + blockIdx.x; a < n_rows; a += gridDim.x) {
+        const long long rb = max((long long)row_ptr[a], e0), re = min((long long)row_ptr[a + 1], e1);
+        if (rb >= e1) break;
         if (a >= n_valid) {
             // no message gradient on this receiver: its edges hand over zeros
             for (long long e = rb; e < re; ++e) {
@@ -103,7 +119,7 @@ k_tp_adjoint_edges(int n_rows, int n_valid, const int32_t* __restrict__ row_ptr,
                     Y[0] = y0.x; Y[1] = y0.y; Y[2] = y0.z; Y[3] = y0.w; Y[4] = y1.x; Y[5] = y1.y; Y[6] = y1.z; Y[7] = y1.w;
                     Y[8] = y2.x; Y[9] = y2.y; Y[10] = y2.z; Y[11] = y2.w; Y[12] = y3.x; Y[13] = y3.y; Y[14] = y3.z; Y[15] = y3.w;
                 }
-                const float* wr = tp_w + e * (long long)(P * kC) + c;
+                const float* wr = tp_w + (e - chunk_e0) * (long long)(P * kC) + c;
 #pragma unroll
                 for (int p = 0; p < P; ++p) {
                     w[p] = __ldg(wr + p * kC);
@@ -329,7 +345,8 @@ int tp_adjoint_edges(const EdgeAdjointArgs& t, cudaStream_t stream) {
     if (t.lin == 0) {
         static const int grid_cap = grid_for((const void*)k_tp_adjoint_edges<0, 2>, 1 << 30, kC, 0);
         k_tp_adjoint_edges<0, 2><<<t.n_rows < grid_cap ? t.n_rows : grid_cap, kC, 0, stream>>>(
-            t.n_rows, t.n_valid, t.row_ptr, t.senders, t.x, t.edge_sh, t.edge_vec, t.tp_w, t.tangent_offset, t.d_mid, t.dxe,
+            t.n_atoms, t.n_rows, t.n_valid, t.chunk_e0, t.chunk_edges, t.count, t.row_ptr, t.senders, t.x, t.edge_sh, t.edge_vec,
+            t.tp_w, t.tangent_offset, t.d_mid, t.dxe,
             reinterpret_cast<float4*>(t.qe));
     } else if (t.lin == 1) {
         static const int occupancy = [] {
@@ -340,7 +357,8 @@ int tp_adjoint_edges(const EdgeAdjointArgs& t, cudaStream_t stream) {
     {                                                                                                                  \
         static const int grid_cap = grid_for((const void*)k_tp_adjoint_edges<1, MINB_>, 1 << 30, kC, 0);               \
         k_tp_adjoint_edges<1, MINB_><<<t.n_rows < grid_cap ? t.n_rows : grid_cap, kC, 0, stream>>>(                    \
-            t.n_rows, t.n_valid, t.row_ptr, t.senders, t.x, t.edge_sh, t.edge_vec, t.tp_w, t.tangent_offset, t.d_mid, t.dxe, \
+            t.n_atoms, t.n_rows, t.n_valid, t.chunk_e0, t.chunk_edges, t.count, t.row_ptr, t.senders, t.x, t.edge_sh,   \
+            t.edge_vec, t.tp_w, t.tangent_offset, t.d_mid, t.dxe,                                                       \
             reinterpret_cast<float4*>(t.qe));                                                                          \
     }
         if (occupancy >= 6) FMB_ADJ1(6)
@@ -352,22 +370,28 @@ int tp_adjoint_edges(const EdgeAdjointArgs& t, cudaStream_t stream) {
     } else if (t.lin == 2) {
         static const int grid_cap = grid_for((const void*)k_tp_adjoint_edges<2, 2>, 1 << 30, kC, 0);
         k_tp_adjoint_edges<2, 2><<<t.n_rows < grid_cap ? t.n_rows : grid_cap, kC, 0, stream>>>(
-            t.n_rows, t.n_valid, t.row_ptr, t.senders, t.x, t.edge_sh, t.edge_vec, t.tp_w, t.tangent_offset, t.d_mid, t.dxe,
+            t.n_atoms, t.n_rows, t.n_valid, t.chunk_e0, t.chunk_edges, t.count, t.row_ptr, t.senders, t.x, t.edge_sh, t.edge_vec,
+            t.tp_w, t.tangent_offset, t.d_mid, t.dxe,
             reinterpret_cast<float4*>(t.qe));
     } else {
         return FMB_ERR_UNSUPPORTED;
     }
     FMB_LAUNCH_CHECK();
+    return FMB_OK;
+}
+
+int gather_sender_gradient(const EdgeAdjointArgs& t, cudaStream_t stream) {
+    if (t.n_rows <= 0) return FMB_OK;
     const int in_dim = (t.lin + 1) * (t.lin + 1);
+    const int grid = t.n_rows < 1184 ? t.n_rows : 1184;
     if (in_dim == 1) {
-        k_gather_dx<1><<<t.n_rows < 1184 ? t.n_rows : 1184, kC, 0, stream>>>(t.n_rows, t.n_rows, t.row_ptr, t.senders, t.mirror,
-                                                                              t.dxe, t.d_x);
+        k_gather_dx<1><<<grid, kC, 0, stream>>>(t.n_rows, t.n_rows, t.row_ptr, t.senders, t.mirror, t.dxe, t.d_x);
     } else if (in_dim == 4) {
-        k_gather_dx<4><<<t.n_rows < 1184 ? t.n_rows : 1184, kC, 0, stream>>>(t.n_rows, t.n_rows, t.row_ptr, t.senders, t.mirror,
-                                                                              t.dxe, t.d_x);
+        k_gather_dx<4><<<grid, kC, 0, stream>>>(t.n_rows, t.n_rows, t.row_ptr, t.senders, t.mirror, t.dxe, t.d_x);
+    } else if (in_dim == 9) {
+        k_gather_dx<9><<<grid, kC, 0, stream>>>(t.n_rows, t.n_rows, t.row_ptr, t.senders, t.mirror, t.dxe, t.d_x);
     } else {
-        k_gather_dx<9><<<t.n_rows < 1184 ? t.n_rows : 1184, kC, 0, stream>>>(t.n_rows, t.n_rows, t.row_ptr, t.senders, t.mirror,
-                                                                              t.dxe, t.d_x);
+        return FMB_ERR_UNSUPPORTED;
     }
     FMB_LAUNCH_CHECK();
     return FMB_OK;

@@ -100,11 +100,10 @@ bool keeps_forward_weights(const Ctx& c, int layer) {
            c.n0 == c.n && c.n1 == c.n;
 }
 
-// Per-edge hand-over adjoint (adjoint_edges.cu) instead of the mirror evaluation: the buffers exist, the list is one
-// chunk and the first interaction is in its reassociated form (its per-edge kernel closes the chain).
+// Per-edge hand-over adjoint (adjoint_edges.cu) instead of the mirror evaluation: the buffers exist and the first
+// interaction is in its reassociated form (its per-edge kernel closes the chain).
 bool edge_local_adjoint(const Ctx& c) {
-    return c.n_chunks == 1 && c.w->mirror && c.w->edge_q && c.w->edge_dx && c.m->n_layers == 2 &&
-           c.m->layer[0].first[0] != nullptr;
+    return c.w->mirror && c.w->edge_q && c.w->edge_dx && c.m->n_layers == 2 && c.m->layer[0].first[0] != nullptr;
 }
 
 float* h_of(const Ctx& c, int layer) {
@@ -361,16 +360,22 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
                      ml.segs[l] * kC, l, 0);
     FMB_TRY(run_linears(c, lb));
     if (layer > 0 && edge_local_adjoint(c)) {
-        const long long* limit = edge_limits(c);
-        FMB_TRY(radial_weights(c, layer, 0, keeps_forward_weights(c, layer) ? 1 : 0, 1, limit));
         EdgeAdjointArgs t{};
-        t.lin = L.l_in_max; t.n_rows = c.n0; t.n_valid = rows; t.row_ptr = c.nl->edge_row_ptr; t.senders = c.nl->edge_index;
-        t.mirror = c.w->mirror; t.x = c.w->x; t.edge_sh = c.w->edge_sh; t.edge_vec = c.w->edge_vec; t.tp_w = c.w->tp_w;
+        t.lin = L.l_in_max; t.n_atoms = c.n; t.n_rows = c.n0; t.n_valid = rows; t.count = (const long long*)c.nl->count;
+        t.row_ptr = c.nl->edge_row_ptr; t.senders = c.nl->edge_index; t.mirror = c.w->mirror; t.x = c.w->x;
+        t.edge_sh = c.w->edge_sh; t.edge_vec = c.w->edge_vec; t.tp_w = c.w->tp_w;
         t.tangent_offset = c.chunk * L.n_paths * kC; t.d_mid = c.w->d_mid; t.dxe = c.w->edge_dx; t.qe = c.w->edge_q;
         t.d_x = c.w->d_x;
-        {
+        for (int k = 0; k < c.n_chunks; ++k) {
+            const long long e0 = (long long)k * c.chunk;
+            FMB_TRY(radial_weights(c, layer, e0, keeps_forward_weights(c, layer) ? 1 : 0, 1, edge_limits(c)));
+            t.chunk_e0 = e0; t.chunk_edges = c.chunk;
             StageScope scope(c.stream, kStTpBwd1);
             FMB_TRY(tp_adjoint_edges(t, c.stream));
+        }
+        {
+            StageScope scope(c.stream, kStTpBwd1);
+            FMB_TRY(gather_sender_gradient(t, c.stream));
         }
         for (int l = 0; l <= L.l_in_max; ++l)
             block_linear(lb, c, c.n0, c.w->d_x, (long long)in_dim * kC, (long long)l * l * kC, kC, L.w_up_t, L.tc[2], L.tc_img[2],
@@ -464,7 +469,7 @@ extern "C" FMB_API int fmb_edge_features(const fmb_model_t* model, const fmb_nl_
     const int rc = edge_features(model, nl, work, positions, (cudaStream_t)stream);
     if (rc) return rc;
     // opposite-edge map for the per-edge adjoint (the compaction reorders edges every step)
-    if (work->mirror && work->edge_q && work->edge_dx && work->chunk_edges >= nl->capacity)
+    if (work->mirror && work->edge_q && work->edge_dx)
         return mirror_map(nl, work->mirror, work->status, (cudaStream_t)stream);
     return FMB_OK;
 }

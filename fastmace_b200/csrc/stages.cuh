@@ -90,15 +90,18 @@ int first_backward_launch(const FirstArgs& f, cudaStream_t stream);
 // Adjoint with per-edge hand-over (adjoint_edges.cu)
 struct EdgeAdjointArgs {
     int lin;
+    int n_atoms;           // atoms of the list
     int n_rows;            // receivers [0, n_rows)
     int n_valid;           // atoms [0, n_valid) have a message gradient
+    long long chunk_e0, chunk_edges;   // this launch covers the edges [chunk_e0, chunk_e0 + chunk_edges) below the count
+    const long long* count;
     const int32_t* row_ptr;
     const int32_t* senders;
     const int32_t* mirror;
     const float* x;
     const float* edge_sh;
     const float* edge_vec;
-    const float* tp_w;             // [edges][paths * C] values, d/dr behind them at tangent_offset
+    const float* tp_w;             // [chunk edges][paths * C] values, d/dr behind them at tangent_offset
     long long tangent_offset;
     const float* d_mid;
     float* dxe;                    // [edges][(lin + 1)^2][C]
@@ -106,8 +109,10 @@ struct EdgeAdjointArgs {
     float* d_x;                    // [n_rows][(lin + 1)^2][C]
 };
 int mirror_map(const fmb_nl_t* nl, int32_t* mirror, uint32_t* status, cudaStream_t stream);
-// per-edge adjoint of an interaction after the first, then the gather of the sender-side gradient into d_x
+// per-edge adjoint of an interaction after the first for one chunk of edges; after the last chunk the gather of the
+// sender-side gradients into d_x
 int tp_adjoint_edges(const EdgeAdjointArgs& t, cudaStream_t stream);
+int gather_sender_gradient(const EdgeAdjointArgs& t, cudaStream_t stream);
 // first interaction: adds its edge-vector gradients to qe (rows below n_add) or stores them
 int first_adjoint_edges(const FirstArgs& f, int n_add, float* qe, cudaStream_t stream);
 // forces (as gradients) and per-atom virials from the per-edge gradients

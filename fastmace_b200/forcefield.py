@@ -130,8 +130,10 @@ class B200ForceField:
             "force_acc": torch.zeros(n, 3, **f32),
             "partial": torch.zeros(1024 * 8, dtype=torch.float64, device=dev),
         }
-        # per-edge hand-over buffers of the adjoint: only when the whole edge list is one chunk
-        self.edge_local = cap <= chunk
+        # per-edge hand-over buffers of the adjoint (2 KB per edge for the medium model): when they take at most a
+        # quarter of the device memory, else the mirror-evaluation kernels run
+        budget = torch.cuda.get_device_properties(dev).total_memory // 4
+        self.edge_local = cap * hid * c * 4 <= budget
         if self.edge_local:
             buf["mirror"] = torch.zeros(cap, dtype=torch.int32, device=dev)
             buf["edge_q"] = torch.zeros(cap, 4, **f32)

@@ -216,7 +216,7 @@ typedef struct {
      * species-only senders of the first layer. Forces come out for every atom (partial sums for halo atoms). */
     int32_t n_energy_atoms;
     int32_t n_inner_atoms;
-    /* Optional per-edge hand-over buffers of the adjoint (all three or none; used when the edge list is one chunk):
+    /* Optional per-edge hand-over buffers of the adjoint (all three or none):
      * mirror [edge_capacity] int32 (index of the opposite edge), edge_q [edge_capacity][4] (gradient of the edge vector),
      * edge_dx [edge_capacity][(hidden_lmax + 1)^2][C] (gradient of the sender's features from that edge). Null = the
      * mirror-evaluation kernels. */

@@ -202,6 +202,63 @@ def _emit_symcon(l_out_max: int) -> str:
     return "\n".join(fwd + bwd)
 
 
+def _emit_symcon_group(l_out_max: int) -> str:
+    """The same polynomial for R atoms of one species at once: every coefficient is loaded once and used R times
+    (the single-atom bodies are bound by their coefficient loads: 410 per atom and channel for outputs 0e + 1o)."""
+    keys = so3.contraction_keys(l_out_max)
+    n_out = (l_out_max + 1) ** 2
+    index = {key: t for t, key in enumerate(keys)}
+    by_mono: dict[tuple, list] = {}
+    for (m_out, nu, mono), t in index.items():
+        by_mono.setdefault(mono, []).append((m_out, t))
+    deg1 = sorted(m for m in by_mono if len(m) == 1)
+    deg2 = sorted(m for m in by_mono if len(m) == 2)
+    deg3 = sorted(m for m in by_mono if len(m) == 3)
+    prefixes = sorted({m[:2] for m in deg3} | set(deg2))
+    loop = "_Pragma(\"unroll\") for (int r = 0; r < R; ++r)"
+    fwd = [f"template <int R> __device__ __forceinline__ void symcon_forward_group_{l_out_max}(const float (&x)[R][16], "
+           f"const float* __restrict__ cf, float (&y)[R][{n_out}]) {{"]
+
+    def consume(mono, expr, lines):
+        for m_out, t in sorted(by_mono.get(mono, ())):
+            lines.append(f"    {{ const float w = __ldg(cf + {t * 128}); {loop} y[r][{m_out}] = fmaf(w, {expr}, y[r][{m_out}]); }}")
+
+    for mono in deg1:
+        consume(mono, f"x[r][{mono[0]}]", fwd)
+    for pre in prefixes:
+        fwd.append(f"    {{ float p[R]; {loop} p[r] = x[r][{pre[0]}] * x[r][{pre[1]}];")
+        consume(pre, "p[r]", fwd)
+        for mono in (m for m in deg3 if m[:2] == pre):
+            consume(mono, f"(p[r] * x[r][{mono[2]}])", fwd)
+        fwd.append("    }")
+    fwd += ["}", ""]
+    bwd = [f"template <int R> __device__ __forceinline__ void symcon_backward_group_{l_out_max}(const float (&x)[R][16], "
+           f"const float* __restrict__ cf, const float (&g)[R][{n_out}], float (&dx)[R][16]) {{"]
+
+    def adjoint_into(mono, target, lines):
+        for m_out, t in sorted(by_mono[mono]):
+            lines.append(f"      {{ const float w = __ldg(cf + {t * 128}); {loop} {target}[r] = fmaf(w, g[r][{m_out}], {target}[r]); }}")
+
+    for mono in deg1:
+        bwd.append(f"    {{ float h[R]; {loop} h[r] = 0.0f;")
+        adjoint_into(mono, "h", bwd)
+        bwd.append(f"      {loop} dx[r][{mono[0]}] += h[r]; }}")
+    for pre in prefixes:
+        i, j = pre
+        bwd.append(f"    {{ float p[R], hp[R]; {loop} {{ p[r] = x[r][{i}] * x[r][{j}]; hp[r] = 0.0f; }}")
+        if pre in by_mono:
+            adjoint_into(pre, "hp", bwd)
+        for mono in (m for m in deg3 if m[:2] == pre):
+            k = mono[2]
+            bwd.append(f"      {{ float h[R]; {loop} h[r] = 0.0f;")
+            adjoint_into(mono, "h", bwd)
+            bwd.append(f"        {loop} {{ dx[r][{k}] = fmaf(h[r], p[r], dx[r][{k}]); hp[r] = fmaf(h[r], x[r][{k}], hp[r]); }} }}")
+        bwd.append(f"      {loop} {{ dx[r][{i}] = fmaf(hp[r], x[r][{j}], dx[r][{i}]); dx[r][{j}] = fmaf(hp[r], x[r][{i}], dx[r][{j}]); }}")
+        bwd.append("    }")
+    bwd += ["}", ""]
+    return "\n".join(fwd + bwd)
+
+
 def render_symcon() -> str:
     head = ["// GENERATED by fastmace_b200/codegen.py from fastmace_b200/so3.py -- do not edit.",
             "// Symmetric contraction (correlation 3) of the 16 message components as a polynomial per (atom, channel):",
@@ -216,7 +273,8 @@ def render_symcon() -> str:
             "template <int LOUT> __device__ __forceinline__ void symcon_backward_body(const float (&x)[16], "
             "const float* __restrict__ cf, const float (&g)[(LOUT + 1) * (LOUT + 1)], float (&dx)[16]);",
             ""]
-    return "\n".join(head + [_emit_symcon(l) for l in (0, 1, 2)] + ["}  // namespace fmb", ""])
+    return "\n".join(head + [_emit_symcon(l) for l in (0, 1, 2)] + [_emit_symcon_group(l) for l in (0, 1, 2)] +
+                     ["}  // namespace fmb", ""])
 
 
 def _write(path: str, text: str) -> None:

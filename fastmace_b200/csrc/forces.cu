@@ -294,7 +294,7 @@ int forward_layer(const Ctx& c, int layer) {
     {
         StageScope scope(c.stream, kStSymFwd);
         FMB_TRY(symcon_forward(rows, L.n_sc_terms, out_dim, L.sc_terms, L.sc_coef, c.w->species, msg, c.w->basis,
-                               c.stream));
+                               c.w->symcon_groups, c.w->n_symcon_groups, c.stream));
     }
     for (int l = 0; l <= L.l_out_max; ++l)
         block_linear(lb, c, rows, c.w->basis, (long long)out_dim * kC, (long long)l * l * kC, kC, L.w_prod, L.tc[7], L.tc_img[7],
@@ -325,7 +325,7 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
     {
         StageScope scope(c.stream, kStSymBwd);
         FMB_TRY(symcon_backward(rows, L.n_sc_terms, out_dim, L.sc_terms, L.sc_coef, c.w->species, msg_of(c, layer),
-                                c.w->d_basis, c.w->d_msg, c.stream));
+                                c.w->d_basis, c.w->d_msg, c.w->symcon_groups, c.w->n_symcon_groups, c.stream));
     }
     if (layer == 0 && L.first[0] != nullptr) {
         // reassociated first layer: gradient of the outer-product sums, then the per-edge kernel

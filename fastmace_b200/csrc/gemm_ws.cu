@@ -86,6 +86,10 @@ k_gemm_ws(const __grid_constant__ WsBatch batch) {
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int slot) { return bar0 + 8u * (uint32_t)slot; };
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef FMB_GEMM_PROFILE
+    const long long t_begin = clock64();
+    long long t_loop = 0, t_acc = 0;
+#endif
 
     int which = 0;
 #pragma unroll
@@ -201,30 +205,61 @@ k_gemm_ws(const __grid_constant__ WsBatch batch) {
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(kWsAFull + s));
         }
+#ifdef FMB_GEMM_PROFILE
+        t_loop = clock64();
+#endif
         // ------------------------------------------------------------------ epilogue: lane = row
-        mbar_wait(bar(kWsAcc), 0, abort_flag, kWsSpin);
-        fence_after_sync();
         const int row = row0 + warp * 32 + lane;
         const bool write = row < m && !(batch_species && batch_species[row / cmap.nm] != select);
         float* dst_row = c_out + (row < m ? cmap(row) : 0) + nt * 128;
-#pragma unroll 1
-        for (int col = 0; col < 128; col += 16) {
-            float v[16];
-            tmem_load<16>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col, v);
-            if (write) {
-                float4* dst = reinterpret_cast<float4*>(dst_row + col);
+        if (accumulate) {
+            // the old values of the whole row are requested before the accumulator is waited for: one memory round trip
+            // instead of one per 16 columns (measured 18,000 -> 4,000 cycles for this epilogue)
+            float4 old[32];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    float4 o = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                    if (accumulate) {
-                        const float4 old = dst[q];
-                        o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+            for (int q = 0; q < 32; ++q)
+                old[q] = write ? *(reinterpret_cast<const float4*>(dst_row) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+            mbar_wait(bar(kWsAcc), 0, abort_flag, kWsSpin);
+#ifdef FMB_GEMM_PROFILE
+            t_acc = clock64();
+#endif
+            fence_after_sync();
+#pragma unroll
+            for (int col = 0; col < 128; col += 16) {
+                float v[16];
+                tmem_load<16>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col, v);
+                if (write) {
+                    float4* dst = reinterpret_cast<float4*>(dst_row + col);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float4 o = old[col / 4 + q];
+                        dst[q] = make_float4(v[4 * q] + o.x, v[4 * q + 1] + o.y, v[4 * q + 2] + o.z, v[4 * q + 3] + o.w);
                     }
-                    dst[q] = o;
+                }
+            }
+        } else {
+            mbar_wait(bar(kWsAcc), 0, abort_flag, kWsSpin);
+#ifdef FMB_GEMM_PROFILE
+            t_acc = clock64();
+#endif
+            fence_after_sync();
+#pragma unroll 1
+            for (int col = 0; col < 128; col += 16) {
+                float v[16];
+                tmem_load<16>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col, v);
+                if (write) {
+                    float4* dst = reinterpret_cast<float4*>(dst_row + col);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
                 }
             }
         }
     }
+#ifdef FMB_GEMM_PROFILE
+    if (blockIdx.x == 0 && tid == 0)
+        printf("gemm_ws grid %d k %d n %d acc %d | prologue+loop %lld wait_acc %lld epilogue %lld total %lld\n", (int)gridDim.x, k, pr.n,
+               accumulate, t_loop - t_begin, t_acc - t_loop, clock64() - t_acc, clock64() - t_begin);
+#endif
     fence_before_sync();
     __syncthreads();
     if (warp == 4) {

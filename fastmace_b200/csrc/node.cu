@@ -52,6 +52,94 @@ k_symcon_backward(int n_atoms, int n_terms, const float* __restrict__ coef, cons
     for (int k = 0; k < kNSH; ++k) d_msg[((long long)a * kNSH + k) * kC + c] = dx[k];
 }
 
+// The same for kSymGroup atoms of one species per CTA (groups[g][0 .. kSymGroup), -1 = empty slot): a coefficient is
+// loaded once and used for every atom of the group. Atoms at or beyond n_rows are skipped.
+constexpr int kSymGroup = 4;
+
+template <int LOUT, int R> struct SymconGroup;
+#define FMB_SYMCON_GROUP(L_)                                                                                           \
+    template <int R> struct SymconGroup<L_, R> {                                                                       \
+        template <typename... A> static __device__ __forceinline__ void forward(A&&... a) {                           \
+            symcon_forward_group_##L_<R>(a...);                                                                        \
+        }                                                                                                              \
+        template <typename... A> static __device__ __forceinline__ void backward(A&&... a) {                          \
+            symcon_backward_group_##L_<R>(a...);                                                                       \
+        }                                                                                                              \
+    };
+FMB_SYMCON_GROUP(0)
+FMB_SYMCON_GROUP(1)
+FMB_SYMCON_GROUP(2)
+
+template <int LOUT>
+__global__ void __launch_bounds__(kC)
+k_symcon_forward_group(int n_groups, int n_rows, int n_terms, const float* __restrict__ coef,
+                       const int32_t* __restrict__ species, const int32_t* __restrict__ groups,
+                       const float* __restrict__ msg, float* __restrict__ basis) {
+    constexpr int OUT = SymconShape<LOUT>::kOut, R = 2;       // half a group per CTA, like the adjoint
+    const int c = threadIdx.x;
+    int atom[R];
+    int lead = -1;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        atom[r] = groups[blockIdx.x * R + r];
+        if (atom[r] >= n_rows) atom[r] = -1;
+        if (lead < 0 && atom[r] >= 0) lead = atom[r];
+    }
+    if (lead < 0) return;
+    float x[R][kNSH], y[R][OUT];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+#pragma unroll
+        for (int k = 0; k < kNSH; ++k) x[r][k] = atom[r] >= 0 ? msg[((long long)atom[r] * kNSH + k) * kC + c] : 0.0f;
+#pragma unroll
+        for (int k = 0; k < OUT; ++k) y[r][k] = 0.0f;
+    }
+    SymconGroup<LOUT, R>::forward(x, coef + (long long)species[lead] * n_terms * kC + c, y);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        if (atom[r] < 0) continue;
+#pragma unroll
+        for (int k = 0; k < OUT; ++k) basis[((long long)atom[r] * OUT + k) * kC + c] = y[r][k];
+    }
+}
+
+// adjoint: two atoms per CTA (half a group), the registers hold x, dx and g of both
+template <int LOUT>
+__global__ void __launch_bounds__(kC)
+k_symcon_backward_group(int n_groups, int n_rows, int n_terms, const float* __restrict__ coef,
+                        const int32_t* __restrict__ species, const int32_t* __restrict__ groups,
+                        const float* __restrict__ msg, const float* __restrict__ d_basis, float* __restrict__ d_msg) {
+    constexpr int OUT = SymconShape<LOUT>::kOut, R = 2;
+    const int c = threadIdx.x;
+    int atom[R];
+    int lead = -1;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        atom[r] = groups[blockIdx.x * R + r];
+        if (atom[r] >= n_rows) atom[r] = -1;
+        if (lead < 0 && atom[r] >= 0) lead = atom[r];
+    }
+    if (lead < 0) return;
+    float x[R][kNSH], dx[R][kNSH], g[R][OUT];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+#pragma unroll
+        for (int k = 0; k < kNSH; ++k) {
+            x[r][k] = atom[r] >= 0 ? msg[((long long)atom[r] * kNSH + k) * kC + c] : 0.0f;
+            dx[r][k] = 0.0f;
+        }
+#pragma unroll
+        for (int k = 0; k < OUT; ++k) g[r][k] = atom[r] >= 0 ? d_basis[((long long)atom[r] * OUT + k) * kC + c] : 0.0f;
+    }
+    SymconGroup<LOUT, R>::backward(x, coef + (long long)species[lead] * n_terms * kC + c, g, dx);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        if (atom[r] < 0) continue;
+#pragma unroll
+        for (int k = 0; k < kNSH; ++k) d_msg[((long long)atom[r] * kNSH + k) * kC + c] = dx[r][k];
+    }
+}
+
 // h[a][k][c] = table[species[a]][k][c]  (layer 0's species-only skip connection)
 __global__ void k_fill_from_species(int n_atoms, int row, const int32_t* __restrict__ species,
                                     const float* __restrict__ table, float* __restrict__ out) {
@@ -199,12 +287,18 @@ __global__ void k_commit(int n3, const float* __restrict__ forces, const double*
 }  // namespace
 
 int symcon_forward(int n_atoms, int n_terms, int out_dim, const int32_t* terms, const float* coef,
-                   const int32_t* species, const float* msg, float* basis, cudaStream_t stream) {
+                   const int32_t* species, const float* msg, float* basis, const int32_t* groups, int n_groups,
+                   cudaStream_t stream) {
     (void)terms;
+    if (n_atoms <= 0) return FMB_OK;
 #define FMB_SYM(L_)                                                                                              \
     {                                                                                                            \
         FMB_REQUIRE(n_terms == SymconShape<L_>::kTerms, "symcon: coefficient table does not match the kernel"); \
-        k_symcon_forward<L_><<<n_atoms, kC, 0, stream>>>(n_atoms, n_terms, coef, species, msg, basis);           \
+        if (groups && n_groups > 0)                                                                              \
+            k_symcon_forward_group<L_><<<2 * n_groups, kC, 0, stream>>>(2 * n_groups, n_atoms, n_terms, coef, species,   \
+                                                                        groups, msg, basis);                     \
+        else                                                                                                     \
+            k_symcon_forward<L_><<<n_atoms, kC, 0, stream>>>(n_atoms, n_terms, coef, species, msg, basis);       \
     }
     if (out_dim == 1) FMB_SYM(0) else if (out_dim == 4) FMB_SYM(1) else if (out_dim == 9) FMB_SYM(2) else {
         FMB_REQUIRE(false, "symcon: unsupported output irreps");
@@ -215,12 +309,18 @@ int symcon_forward(int n_atoms, int n_terms, int out_dim, const int32_t* terms, 
 }
 
 int symcon_backward(int n_atoms, int n_terms, int out_dim, const int32_t* terms, const float* coef,
-                    const int32_t* species, const float* msg, const float* d_basis, float* d_msg, cudaStream_t stream) {
+                    const int32_t* species, const float* msg, const float* d_basis, float* d_msg, const int32_t* groups,
+                    int n_groups, cudaStream_t stream) {
     (void)terms;
+    if (n_atoms <= 0) return FMB_OK;
 #define FMB_SYM(L_)                                                                                                  \
     {                                                                                                                \
         FMB_REQUIRE(n_terms == SymconShape<L_>::kTerms, "symcon: coefficient table does not match the kernel");     \
-        k_symcon_backward<L_><<<n_atoms, kC, 0, stream>>>(n_atoms, n_terms, coef, species, msg, d_basis, d_msg);     \
+        if (groups && n_groups > 0)                                                                                  \
+            k_symcon_backward_group<L_><<<2 * n_groups, kC, 0, stream>>>(2 * n_groups, n_atoms, n_terms, coef, species,  \
+                                                                         groups, msg, d_basis, d_msg);               \
+        else                                                                                                         \
+            k_symcon_backward<L_><<<n_atoms, kC, 0, stream>>>(n_atoms, n_terms, coef, species, msg, d_basis, d_msg); \
     }
     if (out_dim == 1) FMB_SYM(0) else if (out_dim == 4) FMB_SYM(1) else if (out_dim == 9) FMB_SYM(2) else {
         FMB_REQUIRE(false, "symcon: unsupported output irreps");

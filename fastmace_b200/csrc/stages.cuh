@@ -120,9 +120,11 @@ int force_gather(int n_atoms, const int32_t* row_ptr, const int32_t* mirror, con
                  float* force_acc, float* atom_virial, cudaStream_t stream);
 
 int symcon_forward(int n_atoms, int n_terms, int out_dim, const int32_t* terms, const float* coef,
-                   const int32_t* species, const float* msg, float* basis, cudaStream_t stream);
+                   const int32_t* species, const float* msg, float* basis, const int32_t* groups, int n_groups,
+                   cudaStream_t stream);
 int symcon_backward(int n_atoms, int n_terms, int out_dim, const int32_t* terms, const float* coef,
-                    const int32_t* species, const float* msg, const float* d_basis, float* d_msg, cudaStream_t stream);
+                    const int32_t* species, const float* msg, const float* d_basis, float* d_msg, const int32_t* groups,
+                    int n_groups, cudaStream_t stream);
 int fill_from_species(int n_atoms, int row, const int32_t* species, const float* table, float* out, cudaStream_t stream);
 int readout(const fmb_model_t* m, int n_atoms, int n_energy, const float* h_first, const float* h_last, float* node_energy,
             float* d_h_first, float* d_h_last, cudaStream_t stream);

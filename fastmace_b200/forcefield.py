@@ -57,6 +57,7 @@ class B200ForceField:
             PackedModel(spec, weights, sorted(set(int(z) for z in self.numbers)), self._device)
         self.n_owned, self.n_inner = int(n_owned), int(n_inner)
         self.species = self.packed.species_index(self.numbers)
+        self.symcon_groups = self._species_groups(self.species.cpu().numpy(), 4).to(self._device)
         self.neighbours = CellListNeighbours(self.cell, spec.r_cut, self._device, torch.float32, neighbours)
         # FMB_CHUNK_EDGES overrides the chunk size (a tuning knob: small chunks keep the per-edge weights in L2)
         self.chunk_edges = int(os.environ.get("FMB_CHUNK_EDGES", chunk_edges))
@@ -91,6 +92,19 @@ class B200ForceField:
     @property
     def edge_capacity(self) -> int:
         return self.neighbours.capacity
+
+    @staticmethod
+    def _species_groups(species: np.ndarray, size: int) -> torch.Tensor:
+        """[n_groups, size] int32 atom indices, same species within a group, -1 in unused slots (in index order, so that
+        the atoms below a row limit fill the first groups of their species)."""
+        rows = []
+        for z in np.unique(species):
+            atoms = np.nonzero(species == z)[0].astype(np.int32)
+            padded = np.full(-(-len(atoms) // size) * size, -1, dtype=np.int32)
+            padded[:len(atoms)] = atoms
+            rows.append(padded.reshape(-1, size))
+        groups = np.concatenate(rows) if rows else np.zeros((0, size), dtype=np.int32)
+        return torch.from_numpy(np.ascontiguousarray(groups))
 
     # ------------------------------------------------------------------ buffers
     def _outputs(self):
@@ -147,6 +161,7 @@ class B200ForceField:
         w.energy, w.forces, w.stress = self.energy.data_ptr(), self.forces.data_ptr(), self.stress.data_ptr()
         w.status = self.status.data_ptr()
         w.n_energy_atoms, w.n_inner_atoms = self.n_owned, self.n_inner
+        w.symcon_groups, w.n_symcon_groups = self.symcon_groups.data_ptr(), int(self.symcon_groups.shape[0])
         self.work = w
 
     # ------------------------------------------------------------------ protocol methods

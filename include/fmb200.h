@@ -223,6 +223,12 @@ typedef struct {
     int32_t* mirror;
     float* edge_q;
     float* edge_dx;
+    /* Optional: atoms grouped four at a time by species for the symmetric contraction ([n_symcon_groups][4] atom
+     * indices, -1 = empty slot; every atom exactly once; all atoms of a group have the same species). Null = one atom per
+     * CTA. */
+    const int32_t* symcon_groups;
+    int32_t n_symcon_groups;
+    int32_t pad_;
 } fmb_work_t;
 
 /* MACEForceField.__call__ (fastmace/model/forces.py:1127-1136,1220-1240): energy (float64), forces and stress of the

@@ -364,7 +364,9 @@ k_edge_features_mma(EdgeParams p, const double* __restrict__ x, const int32_t* _
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         const float a = cv[mt][nt][i];
-                        const float sig = 1.0f / (1.0f + expf(-a));
+                        // ex2.approx + rcp.approx: relative error of a few 1e-7 on the sigmoid, far inside the fp32
+                        // tolerance of the forces, and a third of the instructions of expf and an IEEE division
+                        const float sig = __fdividef(1.0f, 1.0f + __expf(-a));
                         cv[mt][nt][i] = p.silu_norm * a * sig;
                         ct[mt][nt][i] = p.silu_norm * sig * (1.0f + a * (1.0f - sig)) * ct[mt][nt][i];
                     }

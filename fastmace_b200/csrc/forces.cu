@@ -280,7 +280,7 @@ int forward_layer(const Ctx& c, int layer) {
         FMB_TRY(radial_weights(c, layer, e0, 0, 0, edge_limits(c) + (layer == 0 ? 0 : 1)));
         TpArgs t{};
         t.lin = L.l_in_max; t.species_x = layer == 0; t.n_atoms = c.n; t.n_rows = rows;
-        t.chunk_e0 = e0; t.chunk_edges = c.chunk;
+        t.chunk_e0 = e0; t.chunk_edges = c.chunk; t.whole_list = c.n_chunks == 1; t.error_word = c.w->status;
         t.count = (const long long*)c.nl->count; t.row_ptr = c.nl->edge_row_ptr; t.senders = c.nl->edge_index;
         t.species = c.w->species; t.x = x; t.edge_sh = c.w->edge_sh; t.tp_w = c.w->tp_w; t.mid = c.w->mid;
         StageScope scope(c.stream, layer == 0 ? kStTpFwd0 : kStTpFwd1);

@@ -17,6 +17,7 @@
 #include "stages.cuh"
 #include "generated/tp_generated.cuh"
 #include "edge_gradient.cuh"
+#include "tc_common.cuh"
 
 #include <cstdlib>
 #include <map>
@@ -100,6 +101,82 @@ k_tp_forward(int n_atoms, int n_rows, long long chunk_e0, long long chunk_edges,
 #pragma unroll
         for (int k = 0; k < MID; ++k) out[(long long)k * kC] = acc[k];
     }
+}
+
+// The same forward pass with the radial weights streamed through shared memory (whole edge list in one chunk): the
+// direct-load kernel above spends its time waiting for the 4 P C bytes of weights per edge, which come from HBM
+// (long-scoreboard stalls: 8.6 per issued instruction). Here a CTA owns a contiguous block of receivers, so its weights
+// are one contiguous range of rows of tp_w, and one thread keeps kFwdStages rows ahead of the consumers with bulk
+// copies that complete on mbarriers; a stage is handed back by one arrival per warp.
+constexpr int kFwdStages = 8;
+constexpr unsigned kFwdSpin = 1u << 20;
+
+template <int LIN>
+__global__ void __launch_bounds__(kC)
+k_tp_forward_stream(int n_rows, const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ senders,
+                    const float* __restrict__ x, const float* __restrict__ edge_sh, const float* __restrict__ tp_w,
+                    float* __restrict__ mid, uint32_t* __restrict__ error_word) {
+    constexpr int P = TpShape<LIN>::kPaths, IN = TpShape<LIN>::kInDim, MID = TpShape<LIN>::kMidDim;
+    constexpr int kRow = P * kC;                       // floats of one edge's weights
+    extern __shared__ __align__(128) float ring[];     // [kFwdStages][kRow]
+    __shared__ uint64_t bars[2 * kFwdStages];
+    __shared__ int abort_sh;
+    volatile int* abort_flag = &abort_sh;
+    const int c = threadIdx.x, lane = c & 31;
+    const int per_cta = (n_rows + gridDim.x - 1) / gridDim.x;
+    const int r0 = blockIdx.x * per_cta, r1 = min(n_rows, r0 + per_cta);
+    if (r0 >= r1) return;
+    const long long eb = row_ptr[r0], ee = row_ptr[r1];
+    const uint32_t bar0 = tc::smem_u32(bars), ring0 = tc::smem_u32(ring);
+    if (c == 0) {
+        for (int s = 0; s < kFwdStages; ++s) {
+            tc::mbar_init(bar0 + 8 * s, 1);                        // full
+            tc::mbar_init(bar0 + 8 * (kFwdStages + s), 4);         // empty: one arrival per warp
+        }
+        abort_sh = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    long long issued = eb;                                         // thread 0: next edge whose weights to request
+    auto issue = [&]() {
+        const long long k = issued - eb;
+        const uint32_t s = (uint32_t)(k % kFwdStages);
+        tc::mbar_wait(bar0 + 8 * (kFwdStages + s), (uint32_t)((k / kFwdStages) & 1) ^ 1u, abort_flag, kFwdSpin);
+        tc::mbar_expect_tx(bar0 + 8 * s, kRow * 4);
+        tc::bulk_load(ring0 + s * (kRow * 4), tp_w + issued * kRow, kRow * 4, bar0 + 8 * s);
+        ++issued;
+    };
+    if (c == 0)
+        while (issued < ee && issued < eb + kFwdStages - 1) issue();
+    for (int i = r0; i < r1; ++i) {
+        const long long rb = row_ptr[i], re = row_ptr[i + 1];
+        float acc[MID];
+#pragma unroll
+        for (int k = 0; k < MID; ++k) acc[k] = 0.0f;
+        for (long long e = rb; e < re; ++e) {
+            // the stage the previous edge used has been handed back by now: refill it
+            if (c == 0 && issued < ee && issued < e + kFwdStages) issue();
+            const int s_atom = senders[e];
+            float xs[IN], Y[16], w[P];
+#pragma unroll
+            for (int k = 0; k < IN; ++k) xs[k] = __ldg(x + ((long long)s_atom * IN + k) * kC + c);
+            load_sh(edge_sh, e, Y);
+            const long long k = e - eb;
+            const uint32_t s = (uint32_t)(k % kFwdStages);
+            tc::mbar_wait(bar0 + 8 * s, (uint32_t)((k / kFwdStages) & 1), abort_flag, kFwdSpin);
+            const float* st = ring + s * kRow + c;
+#pragma unroll
+            for (int p = 0; p < P; ++p) w[p] = st[p * kC];
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(bar0 + 8 * (kFwdStages + s));
+            tp_forward<LIN>(xs, Y, w, acc);
+        }
+        float* out = mid + ((long long)i * MID) * kC + c;
+#pragma unroll
+        for (int k = 0; k < MID; ++k) out[(long long)k * kC] = acc[k];
+    }
+    __syncthreads();
+    if (c == 0 && abort_sh && error_word) atomicOr(error_word, FMB_STATUS_TENSOR_TIMEOUT);
 }
 
 // ---------------------------------------------------------------------------------------------- backward
@@ -412,6 +489,15 @@ int persistent_grid(const void* kernel, int n_atoms) {
 
 }  // namespace
 
+// FMB_TP_STREAM=0 keeps the direct-load forward kernel (A/B tests)
+static bool stream_weights() {
+    static const bool on = [] {
+        const char* env = std::getenv("FMB_TP_STREAM");
+        return !(env && env[0] == '0');
+    }();
+    return on;
+}
+
 int tp_forward_launch(const TpArgs& t, cudaStream_t stream) {
     if (t.n_rows <= 0) return FMB_OK;
 #define FMB_FWD(LIN_, SP_)                                                                                             \
@@ -421,11 +507,30 @@ int tp_forward_launch(const TpArgs& t, cudaStream_t stream) {
         kernel<<<grid, kC, 0, stream>>>(t.n_atoms, t.n_rows, t.chunk_e0, t.chunk_edges, t.count, t.row_ptr, t.senders, \
                                         t.species, t.x, t.edge_sh, t.tp_w, t.mid);                                     \
     }
+#define FMB_FWD_STREAM(LIN_)                                                                                           \
+    {                                                                                                                  \
+        constexpr int smem = kFwdStages * TpShape<LIN_>::kPaths * kC * 4;                                              \
+        static int grid_cap = 0;                                                                                       \
+        if (grid_cap == 0) {                                                                                           \
+            FMB_CUDA_CHECK(cudaFuncSetAttribute(k_tp_forward_stream<LIN_>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
+            int per_sm = 0, sms = 148, dev = 0;                                                                        \
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_tp_forward_stream<LIN_>, kC, smem) != cudaSuccess || \
+                per_sm < 1)                                                                                            \
+                per_sm = 1;                                                                                            \
+            if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); \
+            grid_cap = per_sm * sms;                                                                                   \
+        }                                                                                                              \
+        const int grid = t.n_rows < grid_cap ? t.n_rows : grid_cap;                                                    \
+        k_tp_forward_stream<LIN_><<<grid, kC, smem, stream>>>(t.n_rows, t.row_ptr, t.senders, t.x, t.edge_sh, t.tp_w,  \
+                                                              t.mid, t.error_word);                                    \
+    }
     if (t.species_x) {
         FMB_REQUIRE(t.lin == 0, "tp_forward: species table only for scalar senders");
         FMB_FWD(0, true)
     } else if (t.lin == 0) {
         FMB_FWD(0, false)
+    } else if (t.whole_list && (t.lin == 1 || t.lin == 2) && stream_weights()) {
+        if (t.lin == 1) FMB_FWD_STREAM(1) else FMB_FWD_STREAM(2)
     } else if (t.lin == 1) {
         FMB_FWD(1, false)
     } else if (t.lin == 2) {
@@ -434,6 +539,7 @@ int tp_forward_launch(const TpArgs& t, cudaStream_t stream) {
         FMB_REQUIRE(false, "tp_forward: unsupported node l_max");
     }
 #undef FMB_FWD
+#undef FMB_FWD_STREAM
     FMB_LAUNCH_CHECK();
     return FMB_OK;
 }

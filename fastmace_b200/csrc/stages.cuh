@@ -16,6 +16,7 @@ struct TpArgs {
     int n_valid;           // backward: atoms [0, n_valid) have a message gradient, the others read as zero
     int fresh_from;        // backward: atoms at or beyond this start their force / virial sums from zero
     long long chunk_e0, chunk_edges, tangent_offset;
+    bool whole_list;       // the launch covers the whole edge list (one chunk): the streaming forward kernel applies
     const long long* count;
     const int32_t* row_ptr;
     const int32_t* senders;

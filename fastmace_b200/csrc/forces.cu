@@ -102,8 +102,16 @@ bool keeps_forward_weights(const Ctx& c, int layer) {
 
 // Per-edge hand-over adjoint (adjoint_edges.cu) instead of the mirror evaluation: the buffers exist and the first
 // interaction is in its reassociated form (its per-edge kernel closes the chain).
+bool fused_adjoint_selected() {
+    static const bool on = [] {
+        const char* env = std::getenv("FMB_FUSED_ADJOINT");
+        return env && env[0] == '1';
+    }();
+    return on;
+}
+
 bool edge_local_adjoint(const Ctx& c) {
-    return c.w->mirror && c.w->edge_q && c.w->edge_dx && c.m->n_layers == 2 && c.m->layer[0].first[0] != nullptr;
+    return !fused_adjoint_selected() && c.w->mirror && c.w->edge_q && c.w->edge_dx && c.m->n_layers == 2 && c.m->layer[0].first[0] != nullptr;
 }
 
 float* h_of(const Ctx& c, int layer) {
@@ -384,13 +392,9 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
         return FMB_OK;
     }
     bool fused = false;
-    // The fused adjoint executes more instructions per edge than the edge-major kernel (one reduction over channels per
+    // The fused adjoint executes more instructions per edge than the edge-major kernels (one reduction over channels per
     // path) and measures slower on the 1,944-atom cell; FMB_FUSED_ADJOINT=1 selects it (it needs no weight buffer).
-    static const bool fused_adjoint = [] {
-        const char* env = std::getenv("FMB_FUSED_ADJOINT");
-        return env && env[0] == '1';
-    }();
-    if (fused_adjoint && layer > 0 && L.rad_img && tensor_cores_enabled()) {
+    if (fused_adjoint_selected() && layer > 0 && L.rad_img && tensor_cores_enabled()) {
         FusedArgs f{};
         f.lin = L.l_in_max; f.n_rows = c.n0; f.n_valid = rows; f.fresh_from = 0; f.first_layer_of_pass = first_layer_of_pass;
         f.row_ptr = c.nl->edge_row_ptr; f.senders = c.nl->edge_index; f.x = c.w->x; f.edge_sh = c.w->edge_sh;

@@ -147,7 +147,8 @@ class B200ForceField:
         # per-edge hand-over buffers of the adjoint (2 KB per edge for the medium model): when they take at most a
         # quarter of the device memory, else the mirror-evaluation kernels run
         budget = torch.cuda.get_device_properties(dev).total_memory // 4
-        self.edge_local = cap * hid * c * 4 <= budget
+        # FMB_EDGE_ADJOINT=0 keeps the mirror-evaluation kernels (A/B tests)
+        self.edge_local = cap * hid * c * 4 <= budget and os.environ.get("FMB_EDGE_ADJOINT", "1") != "0"
         if self.edge_local:
             buf["mirror"] = torch.zeros(cap, dtype=torch.int32, device=dev)
             buf["edge_q"] = torch.zeros(cap, 4, **f32)

@@ -185,6 +185,9 @@ print("RESULT " + json.dumps(dict(e=e, f=f.tolist(), s=st.tolist())))
     ({"FMB_FUSED_ADJOINT": "1"}, "medium", 1 << 19),      # fused forward and adjoint (weights only in tensor memory)
     ({"FMB_FUSED_ADJOINT": "1"}, "large", 4096),          # the same over several chunks, node l_max 2
     ({"FMB_GEMM": "simt"}, "medium", 1 << 19),            # every contraction on the FP32 pipes
+    ({"FMB_EDGE_ADJOINT": "0"}, "medium", 1 << 19),       # mirror-evaluation adjoint (the path of lists too large for
+    ({"FMB_EDGE_ADJOINT": "0"}, "large", 4096),           # the per-edge hand-over buffers), one chunk and several
+    ({"FMB_TP_STREAM": "0"}, "medium", 1 << 19),          # direct-load forward kernel
 ])
 def test_kernel_variants_in_subprocess(env, name, chunk):
     """The kernel variants are selected once per process by environment variables, so each runs in a child process

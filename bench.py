@@ -155,16 +155,18 @@ def stage_bytes(spec, n_atoms: int, n_edges: int, n_species: int = 2) -> dict:
     out["tp_forward_l0"] = n_edges * (64 * 4 + 64 + 4) + n_atoms * 16 * n_species * 64 * 4
     out["tp_forward_l1"] = n_edges * (p1 * c * 4 + 64 + 4) + n_atoms * (m1 + hid) * c * 4
     out["tp_backward_l0"] = n_edges * (2 * 64 * 4 + 64 + 16 + 4 + 16 * 64 * 4) + n_atoms * (16 * n_species * 64 * 4 + 36)
-    out["tp_backward_l1"] = n_edges * (2 * p1 * c * 4 + 64 + 16 + 4) + n_atoms * ((m1 + 2 * hid) * c * 4 + 36)
+    # per-edge adjoint: weights and d/dr, harmonics, edge vector, hand-over of the sender gradient written and read back
+    out["tp_backward_l1"] = n_edges * (2 * p1 * c * 4 + 64 + 16 + 4 + 2 * hid * c * 4 + 2 * 16) + \
+        n_atoms * ((m1 + 2 * hid) * c * 4 + 36)
     return out
 
 
 # DRAM bytes (read + write) per edge of one launch of the stage's kernel, from the ncu capture summarised in
 # profiles/ncu_full_kernels_medium_nacl_1944.md (62,218 edges; the traffic is proportional to the edge count)
-TRAFFIC_PER_EDGE = {"tp_backward_l1": (751.827200e6 + 7.498752e6) / 62218,
-                    "tp_forward_l1": (327.796224e6 + 22.227200e6) / 62218,
-                    "radial_gemm": 2 * (17.277952e6 + 260.037120e6) / 62218,
-                    "edge_features": (1.429504e6 + 15.905792e6) / 62218}
+TRAFFIC_PER_EDGE = {"tp_backward_l1": (688.05e6 + 117.0e6 + 128.0e6 + 5.0e6) / 62218,     # adjoint + gather launches
+                    "tp_forward_l1": (329.0e6 + 29.0e6) / 62218,
+                    "radial_gemm": 2 * (17.3e6 + 260.0e6) / 62218,
+                    "edge_features": (1.4e6 + 17.0e6) / 62218}
 
 
 def cpu_oracle_sample(repeats: int = 2):

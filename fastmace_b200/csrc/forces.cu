@@ -50,6 +50,41 @@ struct StageScope {
     }
 };
 
+// A second stream per device for the radial-weight producer: its output depends only on the edge features, so it runs
+// beside the first interaction's node kernels (forward) and beside the readout / product / contraction adjoints
+// (backward), which are latency-bound launches of a few dozen CTAs. Created on the first eager call; captured calls
+// record the fork / join as graph dependencies.
+struct SideStream {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+};
+
+SideStream* side_stream(cudaStream_t main) {
+    static SideStream per_device[16];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;
+    SideStream& s = per_device[dev];
+    if (!s.stream) {
+        cudaStreamCaptureStatus status = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(main, &status) != cudaSuccess || status != cudaStreamCaptureStatusNone) return nullptr;
+        if (cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) != cudaSuccess) { s.stream = nullptr; return nullptr; }
+        if (cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) != cudaSuccess) {
+            s.stream = nullptr;
+            return nullptr;
+        }
+    }
+    return &s;
+}
+
+bool overlap_enabled() {
+    static const bool on = [] {
+        const char* env = std::getenv("FMB_OVERLAP");        // FMB_OVERLAP=0: everything on the caller's stream
+        return !(env && env[0] == '0');
+    }();
+    return on && !g_timer.on;       // the stage timers attribute time on one stream
+}
+
 inline int dim_of(int lmax) { return (lmax + 1) * (lmax + 1); }
 
 // K-contiguous message layout: per output irrep l the block starts at component base[l] and holds (2l+1) rows of
@@ -89,6 +124,7 @@ struct Ctx {
     long long count_cap; // entries of the edge buffers
     int n_chunks;
     long long chunk;
+    cudaEvent_t radial_ready = nullptr;   // set when the radial weights of this pass are being produced on the side stream
 };
 
 // When the whole edge list is one chunk, the last interaction's radial weights written by the forward pass are still
@@ -132,17 +168,21 @@ __global__ void k_edge_limits(const int32_t* __restrict__ row_ptr, int n0, int n
 long long* edge_limits(const Ctx& c) { return reinterpret_cast<long long*>(c.w->partial + 4096); }
 
 // first .. last: 0 = values, 1 = their d/dr (second half of tp_w)
-int radial_weights(const Ctx& c, int layer, long long e0, int first, int last, const long long* limit) {
+// `stream` / `max_ctas`: the producer can run on the side stream with fewer CTAs than SMs (it is one persistent CTA per
+// SM with all of its shared and tensor memory, so the SMs it leaves free are what the kernels beside it run on)
+int radial_weights(const Ctx& c, int layer, long long e0, int first, int last, const long long* limit,
+                   cudaStream_t stream = nullptr, int max_ctas = 0) {
     const fmb_layer_t& L = c.m->layer[layer];
     const long long rows = std::min<long long>(c.chunk, c.count_cap - e0);
-    StageScope scope(c.stream, kStRadial);
+    if (!stream) stream = c.stream;
+    StageScope scope(stream, kStRadial);
     if (L.rad_img && tensor_cores_enabled()) {
         // the fused kernels' tensor-core pipeline as a plain producer (one launch per matrix)
         bool done = true;
         for (int tangent = first; tangent <= last && done; ++tangent) {
             const int rc = radial_weights_tc(hidden_of(c, layer, tangent) + e0 * kRadial, L.rad_img,
                                              c.w->tp_w + (long long)tangent * c.chunk * L.n_paths * kC, (int)rows, L.n_paths,
-                                             limit, e0, c.w->status, c.stream);
+                                             limit, e0, c.w->status, max_ctas, stream);
             if (rc == FMB_ERR_UNSUPPORTED) done = false;
             else if (rc) return rc;
         }
@@ -168,7 +208,7 @@ int radial_weights(const Ctx& c, int layer, long long e0, int first, int last, c
         g.m_limit = limit;
         g.m_limit_offset = e0;
     }
-    return gemm_batch(list, count, c.stream);
+    return gemm_batch(list, count, stream);
 }
 
 // A group of independent per-irrep linears that go out as one launch.
@@ -285,7 +325,11 @@ int forward_layer(const Ctx& c, int layer) {
     }
     for (int k = 0; k < c.n_chunks && !fused; ++k) {
         const long long e0 = (long long)k * c.chunk;
-        FMB_TRY(radial_weights(c, layer, e0, 0, 0, edge_limits(c) + (layer == 0 ? 0 : 1)));
+        if (c.radial_ready && layer > 0) {
+            FMB_CUDA_CHECK(cudaStreamWaitEvent(c.stream, c.radial_ready, 0));     // produced beside the first interaction
+        } else {
+            FMB_TRY(radial_weights(c, layer, e0, 0, 0, edge_limits(c) + (layer == 0 ? 0 : 1)));
+        }
         TpArgs t{};
         t.lin = L.l_in_max; t.species_x = layer == 0; t.n_atoms = c.n; t.n_rows = rows;
         t.chunk_e0 = e0; t.chunk_edges = c.chunk; t.whole_list = c.n_chunks == 1; t.error_word = c.w->status;
@@ -376,7 +420,11 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
         t.d_x = c.w->d_x;
         for (int k = 0; k < c.n_chunks; ++k) {
             const long long e0 = (long long)k * c.chunk;
-            FMB_TRY(radial_weights(c, layer, e0, keeps_forward_weights(c, layer) ? 1 : 0, 1, edge_limits(c)));
+            if (c.radial_ready) {
+                FMB_CUDA_CHECK(cudaStreamWaitEvent(c.stream, c.radial_ready, 0));
+            } else {
+                FMB_TRY(radial_weights(c, layer, e0, keeps_forward_weights(c, layer) ? 1 : 0, 1, edge_limits(c)));
+            }
             t.chunk_e0 = e0; t.chunk_edges = c.chunk;
             StageScope scope(c.stream, kStTpBwd1);
             FMB_TRY(tp_adjoint_edges(t, c.stream));
@@ -410,8 +458,12 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
     }
     for (int k = 0; k < c.n_chunks && !fused; ++k) {
         const long long e0 = (long long)k * c.chunk;
-        FMB_TRY(radial_weights(c, layer, e0, keeps_forward_weights(c, layer) ? 1 : 0, 1,
-                               layer == 0 ? (const long long*)c.nl->count : edge_limits(c)));
+        if (c.radial_ready && layer > 0) {
+            FMB_CUDA_CHECK(cudaStreamWaitEvent(c.stream, c.radial_ready, 0));
+        } else {
+            FMB_TRY(radial_weights(c, layer, e0, keeps_forward_weights(c, layer) ? 1 : 0, 1,
+                                   layer == 0 ? (const long long*)c.nl->count : edge_limits(c)));
+        }
         TpArgs t{};
         t.lin = L.l_in_max; t.species_x = layer == 0; t.n_atoms = c.n;
         // every atom that sends into a row with a gradient gets a force; first-layer senders are all atoms
@@ -478,11 +530,34 @@ extern "C" FMB_API int fmb_edge_features(const fmb_model_t* model, const fmb_nl_
     return FMB_OK;
 }
 
+// Starts the radial-weight producer of the last interaction (values: which = 0, d/dr: which = 1) on the side stream
+// when the pass will use kept weights (one chunk, no domain restriction); the layer code then waits for it instead of
+// launching it.
+int fork_radial(Ctx& c, int which) {
+    const int layer = c.m->n_layers - 1;
+    if (!overlap_enabled() || !keeps_forward_weights(c, layer) || !c.m->layer[layer].rad_img || !tensor_cores_enabled())
+        return FMB_OK;
+    if (fused_adjoint_selected()) return FMB_OK;
+    SideStream* side = side_stream(c.stream);
+    if (!side) return FMB_OK;
+    static const int side_ctas = [] {
+        const char* env = std::getenv("FMB_SIDE_CTAS");
+        return env ? std::atoi(env) : 120;
+    }();
+    FMB_CUDA_CHECK(cudaEventRecord(side->fork, c.stream));
+    FMB_CUDA_CHECK(cudaStreamWaitEvent(side->stream, side->fork, 0));
+    FMB_TRY(radial_weights(c, layer, 0, which, which, edge_limits(c) + (which == 0 ? 1 : 0), side->stream, side_ctas));
+    FMB_CUDA_CHECK(cudaEventRecord(side->join, side->stream));
+    c.radial_ready = side->join;
+    return FMB_OK;
+}
+
 extern "C" FMB_API int fmb_forward(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, fmb_stream_t stream) {
     Ctx c;
     FMB_TRY(make_ctx(c, model, nl, work, (cudaStream_t)stream));
     k_edge_limits<<<1, 1, 0, c.stream>>>(nl->edge_row_ptr, c.n0, c.n1, edge_limits(c));
     FMB_LAUNCH_CHECK();
+    FMB_TRY(fork_radial(c, 0));
     FMB_TRY(forward_layer(c, 0));
     FMB_TRY(forward_layer(c, 1));
     // readout; the gradient of the last layer's scalars is parked in `basis` (free after the forward pass)
@@ -496,6 +571,7 @@ extern "C" FMB_API int fmb_backward(const fmb_model_t* model, const fmb_nl_t* nl
     FMB_TRY(make_ctx(c, model, nl, work, (cudaStream_t)stream));
     k_edge_limits<<<1, 1, 0, c.stream>>>(nl->edge_row_ptr, c.n0, c.n1, edge_limits(c));
     FMB_LAUNCH_CHECK();
+    FMB_TRY(fork_radial(c, 1));
     FMB_TRY(backward_layer(c, 1, work->basis, work->d_h, 1));
     FMB_TRY(backward_layer(c, 0, work->d_h, nullptr, 0));
     StageScope scope(c.stream, kStReadout);

@@ -66,7 +66,7 @@ int tp_fused_backward(const FusedArgs& f, cudaStream_t stream);
 // Per-edge radial weights (or their d/dr) [rows][n_paths * 128] = hidden [rows][64] x last radial layer, through the
 // fused kernels' tensor-core pipeline (tp_fused.cu); FMB_ERR_UNSUPPORTED without the weight image.
 int radial_weights_tc(const float* hidden, const float* image, float* out, int rows, int n_paths, const long long* limit,
-                      long long limit_offset, uint32_t* error_word, cudaStream_t stream);
+                      long long limit_offset, uint32_t* error_word, int max_ctas, cudaStream_t stream);
 
 // first layer in reassociated form (outer products per receiver and sender species)
 struct FirstArgs {

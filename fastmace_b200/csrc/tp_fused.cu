@@ -685,7 +685,7 @@ int launch_fused(const FusedArgs& f, cudaStream_t stream) {
 }  // namespace
 
 int radial_weights_tc(const float* hidden, const float* image, float* out, int rows, int n_paths, const long long* limit,
-                      long long limit_offset, uint32_t* error_word, cudaStream_t stream) {
+                      long long limit_offset, uint32_t* error_word, int max_ctas, cudaStream_t stream) {
     if (!image || n_paths < 1) return FMB_ERR_UNSUPPORTED;
     if (rows <= 0) return FMB_OK;
     static int sms = 0;
@@ -698,7 +698,8 @@ int radial_weights_tc(const float* hidden, const float* image, float* out, int r
     }
     WeightArgs a{hidden, image, out, limit, limit_offset, rows, n_paths, error_word};
     const int tiles = (rows + kWeightTile - 1) / kWeightTile;
-    k_radial_weights<<<tiles < sms ? tiles : sms, kFusedThreads, kWeightBytes, stream>>>(a);
+    const int ctas = max_ctas > 0 && max_ctas < sms ? max_ctas : sms;
+    k_radial_weights<<<tiles < ctas ? tiles : ctas, kFusedThreads, kWeightBytes, stream>>>(a);
     FMB_LAUNCH_CHECK();
     return FMB_OK;
 }

@@ -188,6 +188,7 @@ print("RESULT " + json.dumps(dict(e=e, f=f.tolist(), s=st.tolist())))
     ({"FMB_EDGE_ADJOINT": "0"}, "medium", 1 << 19),       # mirror-evaluation adjoint (the path of lists too large for
     ({"FMB_EDGE_ADJOINT": "0"}, "large", 4096),           # the per-edge hand-over buffers), one chunk and several
     ({"FMB_TP_STREAM": "0"}, "medium", 1 << 19),          # direct-load forward kernel
+    ({"FMB_OVERLAP": "0"}, "medium", 1 << 19),            # radial-weight producer on the caller's stream
 ])
 def test_kernel_variants_in_subprocess(env, name, chunk):
     """The kernel variants are selected once per process by environment variables, so each runs in a child process

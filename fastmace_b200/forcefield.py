@@ -144,11 +144,12 @@ class B200ForceField:
             "force_acc": torch.zeros(n, 3, **f32),
             "partial": torch.zeros(1024 * 8, dtype=torch.float64, device=dev),
         }
-        # per-edge hand-over buffers of the adjoint (2 KB per edge for the medium model): when they take at most a
-        # quarter of the device memory, else the mirror-evaluation kernels run
-        budget = torch.cuda.get_device_properties(dev).total_memory // 4
+        # per-edge hand-over buffers of the adjoint (2 KB per edge for the medium model): when they fit in the memory
+        # that is free now with a tenth of the device kept back, else the mirror-evaluation kernels run
+        free, total = torch.cuda.mem_get_info(dev)
+        need = cap * (hid * c * 4 + 20)
         # FMB_EDGE_ADJOINT=0 keeps the mirror-evaluation kernels (A/B tests)
-        self.edge_local = cap * hid * c * 4 <= budget and os.environ.get("FMB_EDGE_ADJOINT", "1") != "0"
+        self.edge_local = need <= free - total // 10 and os.environ.get("FMB_EDGE_ADJOINT", "1") != "0"
         if self.edge_local:
             buf["mirror"] = torch.zeros(cap, dtype=torch.int32, device=dev)
             buf["edge_q"] = torch.zeros(cap, 4, **f32)

@@ -147,6 +147,7 @@ class B200ForceField:
         # per-edge hand-over buffers of the adjoint (2 KB per edge for the medium model): when they fit in the memory
         # that is free now with a tenth of the device kept back, else the mirror-evaluation kernels run
         free, total = torch.cuda.mem_get_info(dev)
+        free += torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)   # blocks torch holds but does not use
         need = cap * (hid * c * 4 + 20)
         # FMB_EDGE_ADJOINT=0 keeps the mirror-evaluation kernels (A/B tests)
         self.edge_local = need <= free - total // 10 and os.environ.get("FMB_EDGE_ADJOINT", "1") != "0"

@@ -3,8 +3,10 @@
 Follows ``fastmace/integrators/langevin.py``: coefficients ``:184-198``, ``first_half`` ``:233-257`` (random terms,
 centre-of-mass projection "ase" or "mass_weighted", half kick, drift, velocity from the displacement),
 ``second_half`` ``:259-263``. Unit constants are ASE's (CODATA 2014), restated in ``fastmace_b200.structures``
-because ASE is not installed here; the algebra itself is pinned by the reference file, not by a run of it
-(``fastmace.integrators.langevin`` imports ``ase.units`` and cannot be imported in this container).
+because ASE is not installed here. Pinned: ``tests/test_oracle_langevin.py`` compares it with trajectories of the
+reference's own ``Langevin`` (three cases: ASE projection, mass-weighted projection, no centre-of-mass constraint),
+written by ``tests/golden/make_langevin_golden.py``, which imports the reference module unchanged behind a stand-in for
+the two ``ase.units`` constants it reads.
 
 Only ``tests/``, ``__graft_entry__.smoke()`` and ``bench.py``'s CPU-baseline legs may import this module.
 """

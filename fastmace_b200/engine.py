@@ -30,6 +30,10 @@ from .state import SimulationState
 
 
 class B200Engine:
+    """Runs MD steps of one force field, integrator and state: the members of the reference's ``Engine``
+    (``fastmace/engine/base.py``). ``mode="graph"`` replays one captured CUDA graph per step; ``"checked"`` launches
+    the stages one by one and reads the status word every step."""
+
     def __init__(self, force_field: B200ForceField, integrator: Langevin, state: SimulationState, *,
                  mode: str = "graph", check_every: int = 256, warmup_steps: int = 3):
         if mode not in ("graph", "checked"):

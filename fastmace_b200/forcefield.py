@@ -36,6 +36,10 @@ class ForceOutput(NamedTuple):
 
 
 class B200ForceField:
+    """Energy, forces and (optionally) stress of one configuration through the CUDA library, with the neighbour list
+    it owns: the members of the reference's ``ForceField`` protocol (``fastmace/model/forces.py``) under the same names.
+    There is no CPU path: construction fails without a CUDA device or without the built library."""
+
     def __init__(self, spec: MaceSpec, weights, numbers, cell, *, compute_stress: bool = False, device="cuda",
                  neighbours: NeighbourConfig | None = None, chunk_edges: int = DEFAULT_CHUNK_EDGES,
                  positions=None, packed: PackedModel | None = None, n_owned: int = 0, n_inner: int = 0):

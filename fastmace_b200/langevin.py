@@ -44,6 +44,9 @@ def noise_steps(limit: int, numbers: int) -> int:
 
 
 class Langevin:
+    """NVT Langevin step in the reference's split (``prepare_step`` / ``first_half`` / forces / ``second_half``,
+    ``fastmace/integrators/langevin.py``), each half one CUDA kernel on float64 state that stays on the device."""
+
     def __init__(self, state: SimulationState, config: IntegratorConfig | None = None, *, temperature_K: float = 0.0,
                  force_buffer: torch.Tensor | None = None, noise: str = "host", device_seed: int = 0):
         """``noise="host"``: the reference's NumPy stream, uploaded in batches. ``noise="device"``: counter-based
@@ -174,6 +177,10 @@ class Langevin:
         _lib.check(self.lib.fmb_langevin_second_half(ctypes.byref(self.struct), _lib.current_stream()),
                    "fmb_langevin_second_half")
 
+    def start(self, state: SimulationState) -> None:
+        """Called once after the initial force evaluation; Langevin has nothing to prepare
+        (``integrators/base.py:123-128``)."""
+
     def mid_step_tensors(self, state: SimulationState):
         return (state.velocities,)
 
@@ -185,6 +192,15 @@ class Langevin:
         kinetic = (0.5 * (state.masses * state.velocities ** 2).sum()).reshape(1)
         return dict(positions=state.positions, momenta=state.velocities * state.masses, forces=state.forces,
                     energy=state.energy.reshape(-1)[:1], kinetic=kinetic)
+
+    def state_dict(self) -> dict:
+        """Langevin carries no state of its own between steps: the noise stream lives in ``state.rng``
+        (``integrators/langevin.py:275-280``)."""
+        return {}
+
+    def load_state_dict(self, state_dict) -> None:
+        if state_dict:
+            raise ValueError(f"Langevin has no internal state, got {sorted(state_dict)}")
 
 
 __all__ = ["Langevin", "IntegratorConfig", "noise_steps", "NOISE_BATCH_BYTES"]

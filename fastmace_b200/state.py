@@ -8,6 +8,7 @@ All tensors are float64 on the device except ``species``; velocities (not moment
 from __future__ import annotations
 
 import dataclasses
+from types import SimpleNamespace
 from typing import Any
 
 import numpy as np
@@ -51,6 +52,19 @@ class SimulationState:
                    forces=torch.zeros_like(positions), energy=torch.zeros(1, **f64),
                    stress=torch.zeros((3, 3), **f64) if compute_stress else None,
                    rng=RandomStream(np.random.default_rng(seed)))
+
+    @classmethod
+    def from_atoms(cls, atoms: Any, device, seed: int, compute_stress: bool = False) -> "SimulationState":
+        """From an ASE-style object (``get_positions``, ``get_velocities``, ``get_masses``, ``get_cell``,
+        ``get_atomic_numbers``; ``state.py:340-378``). Constraints are outside this path and raise."""
+        if getattr(atoms, "constraints", None):
+            raise ValueError("constraints are not supported on this path")
+        velocities = atoms.get_velocities()
+        structure = SimpleNamespace(positions=np.asarray(atoms.get_positions()),
+                                    velocities=None if velocities is None else np.asarray(velocities),
+                                    masses=np.asarray(atoms.get_masses()), cell=np.asarray(atoms.get_cell()),
+                                    numbers=np.asarray(atoms.get_atomic_numbers()))
+        return cls.from_structure(structure, device, seed, compute_stress)
 
     @property
     def natoms(self) -> int:

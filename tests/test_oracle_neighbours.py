@@ -30,3 +30,12 @@ def test_edge_set_is_symmetric():
     g = np.load(os.path.join(GOLDEN, "neighbours_nacl216.npz"))
     edges = nlo.edge_set(g["edge_sender"], g["edge_receiver"], g["edge_unit_shifts"])
     assert all((r, s, -a, -b, -c) in edges for s, r, a, b, c in edges)
+
+
+def test_times_3x3_is_the_row_by_matrix_product():
+    """The reference checks its element-wise ``rows @ matrix`` against the library product at 1e-14
+    (``tests/cpu/test_neighbors.py:427-433``); the restatement meets the same bound on the same kind of input."""
+    rng = np.random.default_rng(0)
+    m = rng.normal(size=(3, 3)) + 3 * np.eye(3)
+    rows = rng.normal(size=(5, 3))
+    np.testing.assert_allclose(nlo.times_3x3(rows, m), rows @ m, rtol=1e-14, atol=1e-14)

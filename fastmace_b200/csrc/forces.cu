@@ -592,6 +592,10 @@ extern "C" FMB_API int fmb_gemm(const float* a, const float* b, const float* bt_
     GemmArgs g;
     g.a = a; g.b = b; g.bt_hi = bt_hi; g.bt_lo = bt_lo; g.error_word = status; g.c = c; g.m = m; g.n = n; g.k = k;
     g.a_bs = k; g.c_bs = n; g.accumulate = accumulate;
+    if (impl == 2) {
+        g.b_img = bt_hi;
+        return gemm_ws_batch(&g, 1, (cudaStream_t)stream);
+    }
     return impl == 1 ? gemm_tc(g, (cudaStream_t)stream) : gemm_simt(g, (cudaStream_t)stream);
 }
 

@@ -13,11 +13,15 @@
 //     and commits them to the stage's `empty` barrier; after the last chunk it commits to the accumulator barrier and
 //     the loader warps turn into the epilogue (lane = row; strided rows, accumulate, species mask).
 // One CTA computes one 128 x 128 tile of C; up to eight problems share a launch. Waits are bounded (tc::mbar_wait).
+// A launch with more narrow tiles than the GPU has SMs pairs adjacent column tiles instead (128 x 256 per CTA: two
+// weight pieces per stage, N = 256 per MMA): the MMA issue rate, not their width, bounds the K loop, and the activation
+// rows are loaded and split once instead of twice.
 
 #include "gemm.cuh"
 #include "tc_common.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 
 namespace fmb {
 
@@ -29,7 +33,8 @@ constexpr int kWsThreads = 160;          // 4 loader / epilogue warps + the cont
 constexpr int kWsStages = 2;
 constexpr int kWsTK = 32;                // K elements per stage
 constexpr int kWsPiece = 128 * kWsTK * 4;        // 16 KB: one of the value / remainder parts of an operand stage
-constexpr int kWsStageBytes = 4 * kWsPiece;      // A value, A remainder, W value, W remainder
+constexpr int kWsStageBytes = 6 * kWsPiece;      // A value, A remainder, W value (2 pieces), W remainder (2 pieces)
+constexpr int kWsWHi = 2 * kWsPiece, kWsWLo = 4 * kWsPiece;      // offsets of the weight parts inside a stage
 constexpr int kWsBytes = kWsStages * kWsStageBytes + 256 + 1024;
 constexpr unsigned kWsSpin = 1u << 20;
 constexpr int kWsMaxProblems = 8;
@@ -59,6 +64,7 @@ struct WsProblem {
 struct WsBatch {
     WsProblem p[kWsMaxProblems];
     int count;
+    int wide;                    // pair adjacent column tiles (128 x 256 per CTA) where a problem has two or more
     uint32_t* error_word;
 };
 
@@ -108,9 +114,13 @@ k_gemm_ws(const __grid_constant__ WsBatch batch) {
         const long long lim = *pr.m_limit - pr.m_limit_offset;
         if (lim < m) m = lim < 0 ? 0 : (int)lim;
     }
-    const int n_tiles = pr.n >> 7;
+    const int n128 = pr.n >> 7;
+    const int n_wide = batch.wide ? (n128 >> 1) : 0;
+    const int per_row_tile = n128 - n_wide;                  // wide pairs first, then the odd narrow tile
     const int local = blockIdx.x - pr.tile_begin;
-    const int row0 = (local / n_tiles) * 128, nt = local % n_tiles;
+    const int row0 = (local / per_row_tile) * 128, slot = local % per_row_tile;
+    const int nt = slot < n_wide ? 2 * slot : slot + n_wide;   // first 128-column tile of this CTA
+    const int tn = slot < n_wide ? 256 : 128;
     if (row0 >= m) return;
     const int chunks = k / kWsTK;
 
@@ -124,7 +134,7 @@ k_gemm_ws(const __grid_constant__ WsBatch batch) {
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 4) tmem_alloc(smem_u32(tmem_slot), 128);
+    if (warp == 4) tmem_alloc(smem_u32(tmem_slot), 256);
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
@@ -133,17 +143,22 @@ k_gemm_ws(const __grid_constant__ WsBatch batch) {
 
     if (warp == 4) {
         if (lane == 0) {
-            const uint32_t idesc = make_idesc<128>();
-            const float* pieces = img + (size_t)nt * chunks * (2 * kWsPiece / 4);
+            const uint32_t idesc = tn == 256 ? make_idesc<256>() : make_idesc<128>();
+            const size_t piece_floats = 2 * kWsPiece / 4;      // [value 16 KB][remainder 16 KB] of one (n tile, k chunk)
+            const float* pieces = img + (size_t)nt * chunks * piece_floats;
             int requested = 0;
             for (int kc = 0; kc < chunks; ++kc) {
                 // keep the weight pieces of the next stages on their way
                 while (requested < chunks && requested < kc + kWsStages) {
                     const int s = requested % kWsStages;
                     mbar_wait(bar(kWsEmpty + s), ((requested / kWsStages) & 1) ^ 1, abort_flag, kWsSpin);
-                    mbar_expect_tx(bar(kWsBFull + s), 2 * kWsPiece);
-                    bulk_load(stage0 + s * kWsStageBytes + 2 * kWsPiece, pieces + (size_t)requested * (2 * kWsPiece / 4),
-                              2 * kWsPiece, bar(kWsBFull + s));
+                    mbar_expect_tx(bar(kWsBFull + s), (tn >> 7) * 2 * kWsPiece);
+                    const uint32_t dst = stage0 + s * kWsStageBytes;
+                    for (int half = 0; half < (tn >> 7); ++half) {
+                        const float* piece = pieces + ((size_t)half * chunks + requested) * piece_floats;
+                        bulk_load(dst + kWsWHi + half * kWsPiece, piece, kWsPiece, bar(kWsBFull + s));
+                        bulk_load(dst + kWsWLo + half * kWsPiece, piece + kWsPiece / 4, kWsPiece, bar(kWsBFull + s));
+                    }
                     ++requested;
                 }
                 const int s = kc % kWsStages;
@@ -153,7 +168,7 @@ k_gemm_ws(const __grid_constant__ WsBatch batch) {
                 fence_after_sync();
                 const uint32_t base = stage0 + s * kWsStageBytes;
                 const uint64_t a_hi = make_desc(base), a_lo = make_desc(base + kWsPiece);
-                const uint64_t w_hi = make_desc(base + 2 * kWsPiece), w_lo = make_desc(base + 3 * kWsPiece);
+                const uint64_t w_hi = make_desc(base + kWsWHi), w_lo = make_desc(base + kWsWLo);
 #pragma unroll
                 for (int k8 = 0; k8 < 4; ++k8)
                     mma_tf32(tmem_base, a_lo + (uint64_t)(2 * k8), w_hi + (uint64_t)(2 * k8), idesc, (kc > 0 || k8 > 0) ? 1 : 0);
@@ -213,27 +228,32 @@ k_gemm_ws(const __grid_constant__ WsBatch batch) {
         const bool write = row < m && !(batch_species && batch_species[row / cmap.nm] != select);
         float* dst_row = c_out + (row < m ? cmap(row) : 0) + nt * 128;
         if (accumulate) {
-            // the old values of the whole row are requested before the accumulator is waited for: one memory round trip
-            // instead of one per 16 columns (measured 18,000 -> 4,000 cycles for this epilogue)
-            float4 old[32];
+            // the old values of 128 columns of the row are requested before the accumulator is waited for: one memory
+            // round trip instead of one per 16 columns (measured 18,000 -> 4,000 cycles for this epilogue)
+#pragma unroll 1
+            for (int c0 = 0; c0 < tn; c0 += 128) {
+                float4 old[32];
 #pragma unroll
-            for (int q = 0; q < 32; ++q)
-                old[q] = write ? *(reinterpret_cast<const float4*>(dst_row) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
-            mbar_wait(bar(kWsAcc), 0, abort_flag, kWsSpin);
+                for (int q = 0; q < 32; ++q)
+                    old[q] = write ? *(reinterpret_cast<const float4*>(dst_row + c0) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+                if (c0 == 0) {
+                    mbar_wait(bar(kWsAcc), 0, abort_flag, kWsSpin);
 #ifdef FMB_GEMM_PROFILE
-            t_acc = clock64();
+                    t_acc = clock64();
 #endif
-            fence_after_sync();
+                    fence_after_sync();
+                }
 #pragma unroll
-            for (int col = 0; col < 128; col += 16) {
-                float v[16];
-                tmem_load<16>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col, v);
-                if (write) {
-                    float4* dst = reinterpret_cast<float4*>(dst_row + col);
+                for (int col = 0; col < 128; col += 16) {
+                    float v[16];
+                    tmem_load<16>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c0 + col), v);
+                    if (write) {
+                        float4* dst = reinterpret_cast<float4*>(dst_row + c0 + col);
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const float4 o = old[col / 4 + q];
-                        dst[q] = make_float4(v[4 * q] + o.x, v[4 * q + 1] + o.y, v[4 * q + 2] + o.z, v[4 * q + 3] + o.w);
+                        for (int q = 0; q < 4; ++q) {
+                            const float4 o = old[col / 4 + q];
+                            dst[q] = make_float4(v[4 * q] + o.x, v[4 * q + 1] + o.y, v[4 * q + 2] + o.z, v[4 * q + 3] + o.w);
+                        }
                     }
                 }
             }
@@ -244,7 +264,7 @@ k_gemm_ws(const __grid_constant__ WsBatch batch) {
 #endif
             fence_after_sync();
 #pragma unroll 1
-            for (int col = 0; col < 128; col += 16) {
+            for (int col = 0; col < tn; col += 16) {
                 float v[16];
                 tmem_load<16>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col, v);
                 if (write) {
@@ -265,7 +285,7 @@ k_gemm_ws(const __grid_constant__ WsBatch batch) {
     if (warp == 4) {
         __syncwarp();
         if (lane == 0 && *abort_flag && batch.error_word) atomicOr(batch.error_word, FMB_STATUS_TENSOR_TIMEOUT);
-        tmem_free(tmem_base, 128);
+        tmem_free(tmem_base, 256);
     }
 }
 
@@ -276,6 +296,18 @@ int gemm_ws_batch(const GemmArgs* list, int count, cudaStream_t stream) {
     WsBatch batch{};
     batch.count = count;
     batch.error_word = list[0].error_word;
+    static const int sm_count = [] {
+        int device = 0, sms = 148;
+        if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        return sms;
+    }();
+    static const int wide_mode = [] {
+        const char* env = std::getenv("FMB_GEMM_WIDE");        // 0: never pair column tiles, 2: always (tuning knob)
+        return env ? std::atoi(env) : 1;
+    }();
+    int narrow_tiles = 0;
+    for (int q = 0; q < count; ++q) narrow_tiles += ceil_div(std::max(list[q].m, 0), 128) * (list[q].n / 128);
+    batch.wide = wide_mode == 2 || (wide_mode == 1 && narrow_tiles > sm_count) ? 1 : 0;
     int tiles = 0;
     for (int q = 0; q < count; ++q) {
         const GemmArgs& g = list[q];
@@ -290,7 +322,8 @@ int gemm_ws_batch(const GemmArgs* list, int count, cudaStream_t stream) {
         p.m_limit = g.m_limit; p.m_limit_offset = g.m_limit_offset;
         p.batch_species = g.batch_species; p.select = g.select;
         p.tile_begin = tiles;
-        tiles += ceil_div(std::max(g.m, 0), 128) * (g.n / 128);
+        const int n128 = g.n / 128;
+        tiles += ceil_div(std::max(g.m, 0), 128) * (n128 - (batch.wide ? n128 / 2 : 0));
     }
     if (tiles == 0) return FMB_OK;
     static bool configured = false;

@@ -246,7 +246,9 @@ FMB_API int fmb_backward(const fmb_model_t* model, const fmb_nl_t* nl, const fmb
 
 /* C[M, N] (+)= A[M, K] B[K, N] in fp32; exported for tests. impl 0: SIMT FMA kernel reading b ([K][N]); impl 1:
  * tcgen05 3xTF32 kernel reading bt_hi / bt_lo (B transposed [N][K], split in tf32 hi and lo; K and N multiples of
- * 64), status FMB_ERR_UNSUPPORTED otherwise. `status` (device word, may be null) receives FMB_STATUS_TENSOR_TIMEOUT. */
+ * 64), status FMB_ERR_UNSUPPORTED otherwise; impl 2: the warp-specialised tcgen05 kernel, bt_hi pointing at the
+ * pre-swizzled weight image (pieces of [128 columns][32 K]: 4,096 tf32 values, then their 4,096 remainders; N a
+ * multiple of 128, K of 32), bt_lo unused. `status` (device word, may be null) receives FMB_STATUS_TENSOR_TIMEOUT. */
 FMB_API int fmb_gemm(const float* a, const float* b, const float* bt_hi, const float* bt_lo, float* c, int m, int n,
                      int k, int accumulate, int impl, uint32_t* status, fmb_stream_t stream);
 

@@ -168,6 +168,32 @@ def test_gemm_kernels_against_torch():
     assert int(status.item()) == 0
 
 
+def test_warp_specialised_gemm_against_torch():
+    """The kernel behind the node linears, called alone through its weight image: launches below one wave use
+    128 x 128 tiles, larger ones pair column tiles (128 x 256), with an odd 128-wide tile left where N / 128 is odd."""
+    from fastmace_b200 import _lib
+    from fastmace_b200.packing import tensor_core_image
+    lib = _lib.load()
+    torch.manual_seed(1)
+    status = torch.zeros((), dtype=torch.int32, device="cuda")
+    for m, n, k in [(1000, 128, 128), (257, 256, 64), (4096, 1280, 64), (20000, 384, 128), (31104, 256, 128),
+                    (19000, 128, 256), (77, 128, 384)]:
+        a = torch.randn(m, k, device="cuda")
+        b = torch.randn(k, n, device="cuda")
+        ref = a.double() @ b.double()
+        scale = ref.abs().max().item()
+        image = tensor_core_image([b.cpu()]).cuda()
+        c = torch.zeros(m, n, device="cuda")
+        args = (a.data_ptr(), b.data_ptr(), image.data_ptr(), None, c.data_ptr(), m, n, k)
+        _lib.check(lib.fmb_gemm(*args, 0, 2, status.data_ptr(), _lib.current_stream()), "gemm")
+        err = (c.double() - ref).abs().max().item() / scale
+        print(f"gemm_ws {m}x{n}x{k}: rel err {err:.2e}")
+        assert err <= 1e-5, (m, n, k, err)
+        _lib.check(lib.fmb_gemm(*args, 1, 2, status.data_ptr(), _lib.current_stream()), "gemm")
+        assert (c.double() - 2 * ref).abs().max().item() / scale <= 2e-5
+    assert int(status.item()) == 0
+
+
 _VARIANT_SCRIPT = r"""
 import json, sys
 import numpy as np
@@ -189,6 +215,8 @@ print("RESULT " + json.dumps(dict(e=e, f=f.tolist(), s=st.tolist())))
     ({"FMB_EDGE_ADJOINT": "0"}, "large", 4096),           # the per-edge hand-over buffers), one chunk and several
     ({"FMB_TP_STREAM": "0"}, "medium", 1 << 19),          # direct-load forward kernel
     ({"FMB_OVERLAP": "0"}, "medium", 1 << 19),            # radial-weight producer on the caller's stream
+    ({"FMB_GEMM_WIDE": "2"}, "medium", 1 << 19),          # 128 x 256 tiles in every node linear that has two column
+    ({"FMB_GEMM_WIDE": "2"}, "large", 4096),              # tiles (by default only launches of more than one wave)
 ])
 def test_kernel_variants_in_subprocess(env, name, chunk):
     """The kernel variants are selected once per process by environment variables, so each runs in a child process

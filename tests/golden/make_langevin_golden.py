@@ -1,6 +1,6 @@
 """Writes ``tests/golden/langevin.npz``: trajectories of the reference's own Langevin integrator.
 
-Run where the reference tree is present (``python tests/golden/make_langevin_golden.py [reference root]``). It imports
+Run where the reference tree is present (``python tests/golden/make_langevin_golden.py <reference root>``). It imports
 ``fastmace.integrators.langevin.Langevin`` and ``fastmace.state.SimulationState`` unchanged and steps them on CPU
 float64 tensors with a harmonic force. The reference module imports ``ase.units`` for two constants only (``fs`` and
 ``kB``); ASE is not installed here, so a two-attribute stand-in carrying ASE's CODATA 2014 values is registered before
@@ -80,8 +80,9 @@ def run_case(name: str, n: int, steps: int, *, fixcm: bool, projection: str, tem
 
 
 def main() -> None:
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
-    sys.path.insert(0, root)
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_langevin_golden.py <root of the reference tree>")
+    sys.path.insert(0, sys.argv[1])
     _stub_ase()
     data = {}
     data.update(run_case("ase", 17, 9, fixcm=True, projection="ase", temperature=300.0, friction_per_fs=0.01, seed=3))

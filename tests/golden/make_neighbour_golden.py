@@ -88,4 +88,6 @@ def main(reference_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_neighbour_golden.py <root of the reference tree>")
+    main(sys.argv[1])

@@ -120,6 +120,11 @@ class B200ForceField:
 
     def _allocate_work(self):
         spec, n, cap, dev = self.spec, self.natoms, self.neighbours.capacity, self._device
+        if getattr(self, "buf", None) is not None:
+            # the edge capacity grew: give the old buffers back to the device before the new ones are sized, so that the
+            # two sets never exist side by side (the per-edge buffers of a large brick are tens of GB each)
+            self.work, self.buf = None, None
+            torch.cuda.empty_cache()
         c = spec.channels
         chunk = min(self.chunk_edges, cap)
         max_paths = max(len(spec.paths(t)) for t in range(spec.num_interactions))
@@ -156,9 +161,16 @@ class B200ForceField:
         # FMB_EDGE_ADJOINT=0 keeps the mirror-evaluation kernels (A/B tests)
         self.edge_local = need <= free - total // 10 and os.environ.get("FMB_EDGE_ADJOINT", "1") != "0"
         if self.edge_local:
-            buf["mirror"] = torch.zeros(cap, dtype=torch.int32, device=dev)
-            buf["edge_q"] = torch.zeros(cap, 4, **f32)
-            buf["edge_dx"] = torch.zeros(cap, hid, c, **f32)
+            try:
+                buf["mirror"] = torch.zeros(cap, dtype=torch.int32, device=dev)
+                buf["edge_q"] = torch.zeros(cap, 4, **f32)
+                buf["edge_dx"] = torch.zeros(cap, hid, c, **f32)
+            except torch.OutOfMemoryError:
+                # the free memory was there but not in one piece: run the mirror-evaluation adjoint instead
+                for name in ("mirror", "edge_q", "edge_dx"):
+                    buf.pop(name, None)
+                torch.cuda.empty_cache()
+                self.edge_local = False
         self.buf = buf
         w = _lib.WorkStruct()
         w.n_atoms, w.edge_capacity, w.chunk_edges, w.compute_stress = n, cap, chunk, int(self._compute_stress)

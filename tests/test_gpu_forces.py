@@ -129,6 +129,21 @@ def test_repeat_calls_are_bitwise_identical():
     assert torch.equal(e0, b.energy) and torch.equal(f0, b.forces) and torch.equal(s0, b.stress)
 
 
+def test_work_buffers_are_released_before_they_are_reallocated():
+    """When the edge capacity grows the old buffers go back to the device first, so that the two sets never coexist;
+    the call after the reallocation gives the same bits."""
+    from fastmace_b200.forcefield import B200ForceField
+    spec, weights, s = _case("medium")
+    ff = B200ForceField(spec, weights, s.numbers, s.cell, compute_stress=True)
+    e0, f0, s0 = ff.evaluate(s, stress=True)
+    torch.cuda.synchronize()
+    held = torch.cuda.memory_allocated()
+    ff._allocate_work()
+    assert torch.cuda.memory_allocated() <= held + (1 << 20)
+    e1, f1, s1 = ff.evaluate(s, stress=True)
+    assert e1 == e0 and np.array_equal(f1, f0) and np.array_equal(s1, s0)
+
+
 def test_medium_216_atoms():
     from fastmace_b200.forcefield import B200ForceField
     spec, weights, s = _case("medium216")

@@ -26,7 +26,7 @@ STATUS_NO_MIRROR = 32
 
 EXPORTS = ("fmb_version", "fmb_last_error", "fmb_sizeof", "fmb_launch_count", "fmb_nl_build", "fmb_nl_compact", "fmb_nl_compact_static",
            "fmb_nl_needs_rebuild",
-           "fmb_forces", "fmb_edge_features", "fmb_forward", "fmb_backward", "fmb_gemm", "fmb_langevin_first_half",
+           "fmb_forces", "fmb_edge_features", "fmb_harmonics_probe", "fmb_forward", "fmb_backward", "fmb_gemm", "fmb_langevin_first_half",
            "fmb_langevin_second_half", "fmb_langevin_device_noise", "fmb_commit_forces", "fmb_profile_enable", "fmb_profile_read")
 
 
@@ -123,6 +123,7 @@ def load() -> ctypes.CDLL:
     lib.fmb_nl_needs_rebuild.argtypes = [POINTER(NlStruct), P, c_double, P]
     lib.fmb_forces.argtypes = [POINTER(ModelStruct), POINTER(NlStruct), POINTER(WorkStruct), P, P]
     lib.fmb_edge_features.argtypes = [POINTER(ModelStruct), POINTER(NlStruct), POINTER(WorkStruct), P, P]
+    lib.fmb_harmonics_probe.argtypes = [P, P, P, P, c_int, P]
     lib.fmb_forward.argtypes = [POINTER(ModelStruct), POINTER(NlStruct), POINTER(WorkStruct), P]
     lib.fmb_backward.argtypes = [POINTER(ModelStruct), POINTER(NlStruct), POINTER(WorkStruct), P]
     lib.fmb_gemm.argtypes = [P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P]

@@ -4,7 +4,9 @@
 
 #include <atomic>
 #include <mutex>
+#include <set>
 #include <string>
+#include <utility>
 
 namespace fmb {
 
@@ -19,6 +21,19 @@ void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 void set_error(const char* what, cudaError_t err, const char* file, int line) {
     std::lock_guard<std::mutex> lock(g_mutex);
     g_error = std::string(what) + ": " + cudaGetErrorString(err) + " (" + file + ":" + std::to_string(line) + ")";
+}
+
+cudaError_t opt_in_shared_memory(const void* kernel, int bytes) {
+    static std::mutex mutex;
+    static std::set<std::pair<int, const void*>> done;
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    std::lock_guard<std::mutex> lock(mutex);
+    if (done.count({dev, kernel})) return cudaSuccess;
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (err == cudaSuccess) done.insert({dev, kernel});
+    return err;
 }
 
 void set_error_text(const char* text) {

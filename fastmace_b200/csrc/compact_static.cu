@@ -57,6 +57,7 @@ int scratch_for_current_device(int32_t** out) {
 
 extern "C" FMB_API int fmb_nl_compact_static(const fmb_nl_t* nl, const double* positions, fmb_stream_t stream) {
     FMB_REQUIRE(nl && positions, "fmb_nl_compact_static: null argument");
+    FMB_REQUIRE(nl->n_atoms > 0, "fmb_nl_compact_static: the list has no atoms");
     if (nl->n_atoms > fmb::kMaxAtoms) {
         fmb::set_error_text("fmb_nl_compact_static: more atoms than FMB_STATIC_COMPACT_MAX_ATOMS (262144); "
                             "use fmb_nl_compact with caller-provided scratch");

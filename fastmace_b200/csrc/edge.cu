@@ -3,11 +3,16 @@
 // derivative with respect to the edge length in the same pass (forward-mode), which is what the analytic force
 // kernels need instead of an autograd tape.
 //
+// The 16 polynomials of sh16 below, their constants and their order are those of the reference's kernel
+// (fastmace/kernels/triton/edge_sh.py:40-58); the gradient used by the adjoint kernels (edge_gradient.cuh) follows
+// the same file's backward (:82-126).
+//
 // Reference: edge geometry inside ScaleShiftMACE.forward (fastmace/model/energy.py:62-100), spherical harmonics
 // fastmace/kernels/triton/edge_sh.py:40-78, radial network call site fastmace/rewrites/generic/modules.py:454 with
 // e3nn's FullyConnectedNet scaling (:148-150). The envelope multiplies the 8 Bessel inputs of a bias-free network, so
 // an edge at or beyond the cutoff yields exactly zero weights (fastmace/model/capabilities.py:369-394).
 
+#include "edge_gradient.cuh"
 #include "gemm.cuh"
 #include "stages.cuh"
 
@@ -406,6 +411,26 @@ k_edge_features_mma(EdgeParams p, const double* __restrict__ x, const int32_t* _
     }
 }
 
+// The harmonics and their gradient exactly as the edge and adjoint kernels evaluate them, on plain vectors.
+__global__ void k_harmonics_probe(const float* __restrict__ vectors, const float* __restrict__ grad_sh,
+                                  float* __restrict__ sh, float* __restrict__ grad_vectors, int n) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n) return;
+    const float vx = vectors[3 * e], vy = vectors[3 * e + 1], vz = vectors[3 * e + 2];
+    const float len = sqrtf(vx * vx + vy * vy + vz * vz);
+    const float inv = 1.0f / fmaxf(len, 1e-12f);
+    const float ux = vx * inv, uy = vy * inv, uz = vz * inv;
+    float Y[16];
+    sh16(ux, uy, uz, Y);
+    for (int k = 0; k < 16; ++k) sh[16 * e + k] = Y[k];
+    if (grad_sh && grad_vectors) {
+        float g[16], q[3];
+        for (int k = 0; k < 16; ++k) g[k] = grad_sh[16 * e + k];
+        edge_vector_gradient(g, 0.0f, ux, uy, uz, len, q);
+        for (int a = 0; a < 3; ++a) grad_vectors[3 * e + a] = q[a];
+    }
+}
+
 }  // namespace
 
 int edge_features(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, const double* positions,
@@ -419,20 +444,11 @@ int edge_features(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t
     for (int t = 0; t < model->n_layers; ++t)
         for (int k = 0; k < 3; ++k) p.rad_w[t][k] = model->layer[t].rad_w[k];
     const size_t smem = (size_t)(2 * 64 * 128 + 64 * 64 + 2 * 8 * 128) * sizeof(float);
-    static bool configured = false;
-    if (!configured) {
-        FMB_CUDA_CHECK(cudaFuncSetAttribute(k_edge_features, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = true;
-    }
+    FMB_CUDA_CHECK(opt_in_shared_memory((const void*)k_edge_features, (int)smem));
     const int blocks = ceil_div(nl->capacity, kEdgesPerBlock);
     if (tensor_cores_enabled()) {
         const size_t smem_mma = (size_t)kMmaSmemFloats * sizeof(float);
-        static bool configured_mma = false;
-        if (!configured_mma) {
-            FMB_CUDA_CHECK(cudaFuncSetAttribute(k_edge_features_mma, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                (int)smem_mma));
-            configured_mma = true;
-        }
+        FMB_CUDA_CHECK(opt_in_shared_memory((const void*)k_edge_features_mma, (int)smem_mma));
         k_edge_features_mma<<<blocks, kThreads, smem_mma, stream>>>(p, positions, nl->edge_index, nl->unit_shifts,
                                                                     (const long long*)nl->count, work->edge_vec,
                                                                     work->edge_sh, work->edge_hidden);
@@ -447,3 +463,12 @@ int edge_features(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t
 }
 
 }  // namespace fmb
+
+extern "C" FMB_API int fmb_harmonics_probe(const float* vectors, const float* grad_sh, float* sh, float* grad_vectors, int n,
+                                           fmb_stream_t stream) {
+    FMB_REQUIRE(vectors && sh && n >= 0, "fmb_harmonics_probe: null argument");
+    if (n == 0) return FMB_OK;
+    fmb::k_harmonics_probe<<<fmb::ceil_div(n, 128), 128, 0, (cudaStream_t)stream>>>(vectors, grad_sh, sh, grad_vectors, n);
+    FMB_LAUNCH_CHECK();
+    return FMB_OK;
+}

@@ -12,6 +12,9 @@ namespace fmb {
 void set_error(const char* what, cudaError_t err, const char* file, int line);
 void count_launch();
 void set_error_text(const char* text);
+// Raises a kernel's dynamic shared-memory limit on the CURRENT device, once per (device, kernel): the attribute is
+// per device, so a process that drives several GPUs sets it on each of them.
+cudaError_t opt_in_shared_memory(const void* kernel, int bytes);
 
 #define FMB_CUDA_CHECK(expr)                                            \
     do {                                                                \

@@ -461,12 +461,7 @@ k_gemm_tc(const __grid_constant__ Batch batch) {
 
 template <bool SWAP, int TN>
 int launch(const Batch& batch, int tiles, cudaStream_t stream) {
-    static bool configured = false;
-    if (!configured) {
-        FMB_CUDA_CHECK(cudaFuncSetAttribute(k_gemm_tc<SWAP, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            smem_bytes<TN>()));
-        configured = true;
-    }
+    FMB_CUDA_CHECK(opt_in_shared_memory((const void*)k_gemm_tc<SWAP, TN>, smem_bytes<TN>()));
     k_gemm_tc<SWAP, TN><<<tiles, kThreads, smem_bytes<TN>(), stream>>>(batch);
     FMB_LAUNCH_CHECK();
     return FMB_OK;

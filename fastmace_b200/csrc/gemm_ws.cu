@@ -326,11 +326,7 @@ int gemm_ws_batch(const GemmArgs* list, int count, cudaStream_t stream) {
         tiles += ceil_div(std::max(g.m, 0), 128) * (n128 - (batch.wide ? n128 / 2 : 0));
     }
     if (tiles == 0) return FMB_OK;
-    static bool configured = false;
-    if (!configured) {
-        FMB_CUDA_CHECK(cudaFuncSetAttribute(k_gemm_ws, cudaFuncAttributeMaxDynamicSharedMemorySize, kWsBytes));
-        configured = true;
-    }
+    FMB_CUDA_CHECK(opt_in_shared_memory((const void*)k_gemm_ws, kWsBytes));
     k_gemm_ws<<<tiles, kWsThreads, kWsBytes, stream>>>(batch);
     FMB_LAUNCH_CHECK();
     return FMB_OK;

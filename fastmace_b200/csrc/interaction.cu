@@ -511,8 +511,8 @@ int tp_forward_launch(const TpArgs& t, cudaStream_t stream) {
     {                                                                                                                  \
         constexpr int smem = kFwdStages * TpShape<LIN_>::kPaths * kC * 4;                                              \
         static int grid_cap = 0;                                                                                       \
+        FMB_CUDA_CHECK(opt_in_shared_memory((const void*)k_tp_forward_stream<LIN_>, smem));                            \
         if (grid_cap == 0) {                                                                                           \
-            FMB_CUDA_CHECK(cudaFuncSetAttribute(k_tp_forward_stream<LIN_>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
             int per_sm = 0, sms = 148, dev = 0;                                                                        \
             if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_tp_forward_stream<LIN_>, kC, smem) != cudaSuccess || \
                 per_sm < 1)                                                                                            \

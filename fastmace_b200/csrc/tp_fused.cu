@@ -667,9 +667,8 @@ k_radial_weights(const __grid_constant__ WeightArgs a) {
 template <int LIN, bool BWD>
 int launch_fused(const FusedArgs& f, cudaStream_t stream) {
     static int sms = 0;
+    FMB_CUDA_CHECK(opt_in_shared_memory((const void*)k_tp_fused<LIN, BWD>, FusedShape<BWD>::kBytes));
     if (sms == 0) {
-        FMB_CUDA_CHECK(cudaFuncSetAttribute(k_tp_fused<LIN, BWD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            FusedShape<BWD>::kBytes));
         int dev = 0, count = 148;
         FMB_CUDA_CHECK(cudaGetDevice(&dev));
         FMB_CUDA_CHECK(cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev));
@@ -689,8 +688,8 @@ int radial_weights_tc(const float* hidden, const float* image, float* out, int r
     if (!image || n_paths < 1) return FMB_ERR_UNSUPPORTED;
     if (rows <= 0) return FMB_OK;
     static int sms = 0;
+    FMB_CUDA_CHECK(opt_in_shared_memory((const void*)k_radial_weights, kWeightBytes));
     if (sms == 0) {
-        FMB_CUDA_CHECK(cudaFuncSetAttribute(k_radial_weights, cudaFuncAttributeMaxDynamicSharedMemorySize, kWeightBytes));
         int dev = 0, count = 148;
         FMB_CUDA_CHECK(cudaGetDevice(&dev));
         FMB_CUDA_CHECK(cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev));

@@ -244,6 +244,14 @@ FMB_API int fmb_edge_features(const fmb_model_t* model, const fmb_nl_t* nl, cons
 FMB_API int fmb_forward(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, fmb_stream_t stream);
 FMB_API int fmb_backward(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, fmb_stream_t stream);
 
+/* The real spherical harmonics l <= 3 (component normalised, on v / max(|v|, 1e-12)) and, when grad_sh and
+ * grad_vectors are given, the gradient of sum(grad_sh * sh) with respect to the vectors, through the same device
+ * functions the edge and adjoint kernels call: fastmace/kernels/triton/edge_sh.py:40-78 (edge_sh3) and :82-126 (its
+ * backward). vectors [n][3], grad_sh / sh [n][16], grad_vectors [n][3], all fp32 on the device; exported for the
+ * parity test against the reference kernel's fixture. */
+FMB_API int fmb_harmonics_probe(const float* vectors, const float* grad_sh, float* sh, float* grad_vectors, int n,
+                                fmb_stream_t stream);
+
 /* C[M, N] (+)= A[M, K] B[K, N] in fp32; exported for tests. impl 0: SIMT FMA kernel reading b ([K][N]); impl 1:
  * tcgen05 3xTF32 kernel reading bt_hi / bt_lo (B transposed [N][K], split in tf32 hi and lo; K and N multiples of
  * 64), status FMB_ERR_UNSUPPORTED otherwise; impl 2: the warp-specialised tcgen05 kernel, bt_hi pointing at the

@@ -16,7 +16,14 @@ the reference itself restates it:
 
 PARITY UNPINNED against mace-torch 0.3.16: the reference holds no golden energies/forces, and mace/e3nn cannot be
 imported here. What IS pinned: the spherical harmonics (against the reference kernel run under the Triton
-interpreter, fixture in ``tests/golden``), equivariance/invariance properties, and finite-difference forces.
+interpreter, fixture ``tests/golden/edge_sh.npz``, checked in ``tests/test_oracle_so3.py``), equivariance /
+invariance properties and finite-difference forces and stress (same test file).
+
+The coupling tables (Wigner tensors, tensor-product paths, coupling trees, the SiLU constant) come from
+``oracle/so3_oracle.py``, which derives them from Racah's formula and SciPy's complex harmonics; nothing of the
+product package ``fastmace_b200`` is imported: the model description is read from plain integer / float attributes
+(``channels, hidden_lmax, sh_lmax, correlation, num_interactions, r_cut, num_bessel, cutoff_p, num_elements,
+mlp_hidden, avg_num_neighbors, scale, shift``) of whatever object is passed as ``spec``.
 
 Only ``tests/``, ``__graft_entry__.smoke()`` and ``bench.py``'s CPU-baseline legs may import this module. The
 product path never does.
@@ -29,37 +36,39 @@ import math
 import numpy as np
 import torch
 
-from fastmace_b200 import so3
-from fastmace_b200.model import SILU_NORM, MaceSpec, e0_table
+from . import so3_oracle as so3
 
-S3, S5, S56, S38 = so3.S3, so3.S5, so3.S56, so3.S38
-C1, C2, C3 = so3.C1, so3.C2, so3.C3
+SILU_NORM = so3.silu_second_moment_norm()
+
+
+def l_in_max(spec, layer: int) -> int:
+    return 0 if layer == 0 else spec.hidden_lmax
+
+
+def l_out_max(spec, layer: int) -> int:
+    return spec.hidden_lmax if layer < spec.num_interactions - 1 else 0
+
+
+def out_dim(spec, layer: int) -> int:
+    return (l_out_max(spec, layer) + 1) ** 2
+
+
+def skip_lmax(spec, layer: int) -> int:
+    return min(l_in_max(spec, layer), l_out_max(spec, layer))
+
+
+def paths_of(spec, layer: int):
+    return so3.tp_paths(l_in_max(spec, layer))
 
 
 def spherical_harmonics(vectors: torch.Tensor) -> torch.Tensor:
     """[E, 3] -> [E, 16]; ``v / max(|v|, eps)`` like ``torch.nn.functional.normalize`` (edge_sh.py:30-37)."""
     n = torch.linalg.norm(vectors, dim=1, keepdim=True)
     u = vectors / torch.clamp(n, min=1e-12)
-    x, y, z = u[:, 0], u[:, 1], u[:, 2]
-    s20 = S3 * x * z
-    s21 = S3 * x * y
-    y2 = y * y
-    x2z2 = x * x + z * z
-    s22 = y2 - 0.5 * x2z2
-    s23 = S3 * y * z
-    s24 = S3 / 2.0 * (z * z - x * x)
-    s30 = S56 * (s20 * z + s24 * x)
-    s31 = S5 * s20 * y
-    s32 = S38 * (4.0 * y2 - x2z2) * x
-    s33 = 0.5 * y * (2.0 * y2 - 3.0 * x2z2)
-    s34 = S38 * z * (4.0 * y2 - x2z2)
-    s35 = S5 * s24 * y
-    s36 = S56 * (s24 * z - s20 * x)
-    return torch.stack([torch.ones_like(x), C1 * x, C1 * y, C1 * z, C2 * s20, C2 * s21, C2 * s22, C2 * s23, C2 * s24,
-                        C3 * s30, C3 * s31, C3 * s32, C3 * s33, C3 * s34, C3 * s35, C3 * s36], dim=1)
+    return torch.stack(so3.harmonics_of_unit(u[:, 0], u[:, 1], u[:, 2]), dim=1)
 
 
-def bessel_cutoff(r: torch.Tensor, spec: MaceSpec) -> torch.Tensor:
+def bessel_cutoff(r: torch.Tensor, spec) -> torch.Tensor:
     """[E] -> [E, num_bessel]: sqrt(2/rc) sin(n pi r / rc) / r times the polynomial envelope (p = cutoff_p)."""
     rc, p = spec.r_cut, float(spec.cutoff_p)
     n = torch.arange(1, spec.num_bessel + 1, dtype=r.dtype)
@@ -88,32 +97,28 @@ def radial_mlp(edge_feats: torch.Tensor, weights, layer: int, hidden_only: bool 
     return x
 
 
-def _cg(l_in, l_edge, l_out, dtype):
-    return torch.tensor(so3.wigner_3j(l_in, l_edge, l_out) * math.sqrt(2 * l_out + 1), dtype=dtype)
-
-
 def interaction(spec, weights, layer, h, species, sender, receiver, sh, edge_feats, keep=None):
     """One residual interaction: returns (message [N, 16, C], sc [N, out_dim, C])."""
     c, dtype, n = spec.channels, h.dtype, h.shape[0]
     n_el = spec.num_elements
-    out_dim = spec.out_dim(layer)
-    sc = torch.zeros(n, out_dim, c, dtype=dtype)
-    for l in range(spec.skip_lmax(layer) + 1):
+    sc = torch.zeros(n, out_dim(spec, layer), c, dtype=dtype)
+    for l in range(skip_lmax(spec, layer) + 1):
         w = weights[f"l{layer}.skip.{l}"][:, species, :]  # [C, N, C]
         sl = slice(l * l, (l + 1) ** 2)
         sc[:, sl, :] = torch.einsum("nmc,cnd->nmd", h[:, sl, :], w) / math.sqrt(c * n_el)
     x = torch.zeros_like(h)
-    for l in range(spec.l_in_max(layer) + 1):
+    for l in range(l_in_max(spec, layer) + 1):
         sl = slice(l * l, (l + 1) ** 2)
         x[:, sl, :] = h[:, sl, :] @ (weights[f"l{layer}.up.{l}"] / math.sqrt(c))
-    paths = spec.paths(layer)
+    paths = paths_of(spec, layer)
     tp_w = radial_mlp(edge_feats, weights, layer).reshape(-1, len(paths), c)
     mid = torch.zeros(n, so3.mid_dim(paths), c, dtype=dtype)
     xs = x[sender]
     for p, path in enumerate(paths):
         li, le, lo = path["l_in"], path["l_edge"], path["l_out"]
-        cg = _cg(li, le, lo, dtype)
-        t = torch.einsum("abd,eac,eb->edc", cg, xs[:, li * li:(li + 1) ** 2, :], sh[:, le * le:(le + 1) ** 2])
+        cg = torch.tensor(path["cg"], dtype=dtype)
+        coupled = torch.einsum("abd,eb->ead", cg, sh[:, le * le:(le + 1) ** 2])       # harmonics first: [E, in, out]
+        t = torch.einsum("ead,eac->edc", coupled, xs[:, li * li:(li + 1) ** 2, :])
         mji = t * tp_w[:, p, None, :]
         seg = slice(path["out_off"], path["out_off"] + 2 * lo + 1)
         mid[:, seg, :] = mid[:, seg, :].index_add(0, receiver, mji)
@@ -142,13 +147,13 @@ def symmetric_contraction(spec, weights, layer, message, species, chunk=128):
     Evaluated per present species (the weights are species-dependent) and in chunks of atoms to bound memory."""
     n, _, c = message.shape
     dtype = message.dtype
-    out = torch.zeros(n, spec.out_dim(layer), c, dtype=dtype)
+    out = torch.zeros(n, out_dim(spec, layer), c, dtype=dtype)
     for z in torch.unique(species).tolist():
         atoms = torch.nonzero(species == z).reshape(-1)
-        for big_l in range(spec.l_out_max(layer) + 1):
+        for big_l in range(l_out_max(spec, layer) + 1):
             uws = {}
             for nu in range(1, spec.correlation + 1):
-                u = torch.tensor(np.stack(so3.coupling_trees(nu, big_l, spec.sh_lmax), axis=0), dtype=dtype)
+                u = torch.tensor(np.stack(so3.coupling_trees(nu, big_l), axis=0), dtype=dtype)
                 uws[nu] = torch.einsum("k...,kc->...c", u, weights[f"l{layer}.sc.{big_l}.{nu}"][z])  # [M,16^nu,C]
             for start in range(0, len(atoms), chunk):
                 idx = atoms[start:start + chunk]
@@ -165,7 +170,7 @@ def product(spec, weights, layer, message, sc, species, keep=None):
     c = spec.channels
     basis = symmetric_contraction(spec, weights, layer, message, species)
     out = torch.zeros_like(basis)
-    for big_l in range(spec.l_out_max(layer) + 1):
+    for big_l in range(l_out_max(spec, layer) + 1):
         sl = slice(big_l * big_l, (big_l + 1) ** 2)
         out[:, sl, :] = basis[:, sl, :] @ (weights[f"l{layer}.prod.{big_l}"] / math.sqrt(c))
     if keep is not None:
@@ -182,7 +187,7 @@ def readout(spec, weights, layer, h):
     return hidden @ (weights[f"l{layer}.readout.1"] / math.sqrt(spec.mlp_hidden))
 
 
-def evaluate(spec: MaceSpec, weights, positions, cell, atomic_numbers, sender, receiver, unit_shifts,
+def evaluate(spec, weights, positions, cell, atomic_numbers, sender, receiver, unit_shifts,
              dtype=torch.float64, compute_stress=True, keep=None, n_energy=None):
     """Energy (float64 scalar), forces [N, 3], stress [3, 3] (ASE sign, dE/d(strain) / |det cell|).
 
@@ -222,7 +227,7 @@ def evaluate(spec: MaceSpec, weights, positions, cell, atomic_numbers, sender, r
             keep[f"l{t}.h"] = h
         node_energy = node_energy + readout(spec, weights, t, h)
     node_energy = spec.scale * node_energy + spec.shift
-    e0 = torch.tensor(e0_table(spec))[species]
+    e0 = torch.zeros(spec.num_elements, dtype=torch.float64)[species]    # the benchmark models have zero E0
     if n_energy is not None:
         e0, node_energy = e0[:n_energy], node_energy[:n_energy]
     energy = e0.sum() + node_energy.to(torch.float64).sum()

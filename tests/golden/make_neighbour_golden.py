@@ -4,6 +4,10 @@ Run once where the reference tree is available (it is not on the GPU box):
 
     python tests/golden/make_neighbour_golden.py /path/to/reference
 
+``neighbours_large.json`` holds SHA-256 digests instead of arrays for the shapes that are too big to commit (a
+10,648-atom triclinic primitive-FCC alloy cell and a 3,456-atom amorphous Si-O cell): the test regenerates the seeded
+positions, checks their digest, and compares the digests of its own lists.
+
 Neighbour fixtures: the reference's ``SkinNeighbourList.build_gpu`` on CPU float64 tensors (its pure-PyTorch path,
 ``fastmace/neighbors/pair_search.py:242-261`` + ``skin.py:421-497``) followed by ``compact`` (``skin.py:702-729``),
 for rattled, sheared and out-of-cell inputs. Spherical-harmonic fixture: the reference's Triton kernels
@@ -42,10 +46,59 @@ def neighbour_cases():
     return cases
 
 
+def large_cases():
+    """name -> (builder name, builder kwargs, cutoff, skin): big enough for several cell-list bins per axis, the
+    alloy's supercell triclinic, the Si-O box with the long rows (45-80 pairs) of the amorphous configuration."""
+    return {
+        "fcc10648_triclinic": ("fcc_alloy", dict(repeat=(22, 22, 22), sigma=0.1, seed=2), 6.0, 0.3),
+        "silica3456": ("silica", dict(n_si=1152, seed=1), 6.0, 0.3),
+    }
+
+
+def digest(array) -> str:
+    import hashlib
+    return hashlib.sha256(np.ascontiguousarray(array).tobytes()).hexdigest()
+
+
+def large_digests(nl_arrays):
+    """Digests of one list: ``nl_arrays`` maps the reference's buffer names to NumPy arrays cut to their live part."""
+    as_type = dict(candidate_index=np.int32, candidate_unit_shifts=np.int8, edge_index=np.int32, unit_shifts=np.int8,
+                   shifts=np.float32)
+    return {name: digest(np.asarray(nl_arrays[name]).astype(kind)) for name, kind in as_type.items()}
+
+
 def main(reference_root):
+    import json
+
+    from fastmace_b200 import structures
+
     sys.path.insert(0, reference_root)
     from fastmace.config import NeighbourConfig
     from fastmace.neighbors.skin import SkinNeighbourList
+
+    record = {}
+    for name, (builder, kwargs, cutoff, skin) in large_cases().items():
+        s = getattr(structures, builder)(**kwargs)
+        config = NeighbourConfig(skin=skin, sort_receivers="on", gpu_neighbour_list="on")
+        nl = SkinNeighbourList(s.cell, cutoff, "cpu", torch.float64, config)
+        nl.build_gpu(torch.tensor(s.positions, dtype=torch.float64))
+        n = nl.num_candidates
+        moved = s.positions + np.random.default_rng(1).normal(0, 0.03, s.positions.shape)
+        nl.compact(torch.tensor(moved))
+        count = int(nl.count)
+        arrays = dict(candidate_index=nl.candidate_index[:, :n].numpy(),
+                      candidate_unit_shifts=nl.candidate_unit_shifts[:n].numpy(),
+                      edge_index=nl.edge_index[:, :count].numpy(), unit_shifts=nl.unit_shifts[:count].numpy(),
+                      shifts=nl.shifts[:count].numpy())
+        rows = np.bincount(arrays["edge_index"][1], minlength=s.natoms)
+        record[name] = dict(builder=builder, kwargs={k: list(v) if isinstance(v, tuple) else v for k, v in kwargs.items()},
+                            cutoff=cutoff, skin=skin, natoms=s.natoms, positions=digest(s.positions),
+                            moved=digest(moved), num_candidates=int(n), capacity=int(nl.capacity), count=count,
+                            longest_row=int(rows.max()), shortest_row=int(rows.min()),
+                            needs_rebuild=bool(nl.needs_rebuild(torch.tensor(moved))), **large_digests(arrays))
+        print(name, "candidates", n, "edges", count, "capacity", nl.capacity, "rows", rows.min(), rows.max())
+    with open(os.path.join(HERE, "neighbours_large.json"), "w") as handle:
+        json.dump(record, handle, indent=1, sort_keys=True)
 
     for name, (positions, cell, cutoff, skin) in neighbour_cases().items():
         config = NeighbourConfig(skin=skin, sort_receivers="on", gpu_neighbour_list="on")

@@ -14,7 +14,7 @@ TOL_E, TOL_F, TOL_S = 1e-5, 1e-4, 1e-6
 
 def _case(name):
     from fastmace_b200.model import LARGE, MEDIUM, SMALL, init_weights
-    from fastmace_b200.structures import fcc_alloy, nacl
+    from fastmace_b200.structures import fcc_alloy, nacl, silica
     if name == "small":
         return SMALL, init_weights(SMALL, 0), nacl((2, 2, 2), 0.05, 0)
     if name == "medium":
@@ -25,6 +25,11 @@ def _case(name):
         import dataclasses
         spec = dataclasses.replace(LARGE, avg_num_neighbors=54.0)
         return spec, init_weights(spec, 2), fcc_alloy((4, 4, 4), 0.1, 2)
+    if name == "silica":
+        # the amorphous Si-O configuration in small: same density and rejection rule, 300 atoms, rows of 45-75 edges
+        import dataclasses
+        spec = dataclasses.replace(MEDIUM, avg_num_neighbors=60.0)
+        return spec, init_weights(spec, 1), silica(n_si=100, seed=1)
     raise KeyError(name)
 
 
@@ -42,7 +47,7 @@ def _report(name, e, f, st, e_ref, f_ref, s_ref, natoms):
     return de, df, ds, fscale
 
 
-@pytest.mark.parametrize("name", ["small", "medium", "large"])
+@pytest.mark.parametrize("name", ["small", "medium", "large", "silica"])
 def test_energy_forces_stress_against_oracle(name):
     from fastmace_b200.forcefield import B200ForceField
     spec, weights, s = _case(name)

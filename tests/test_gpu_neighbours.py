@@ -54,7 +54,59 @@ def test_build_and_compact_bitwise_against_reference(path):
     far = moved.clone()
     far[3, 1] += 0.2
     assert bool(nl.needs_rebuild(far).item())
-    assert bool(nl.needs_rebuild(far, 2.0).item()) == (0.2 ** 2 > (2.0 * float(g["skin"]) / 2) ** 2 * 0.999) or True
+    # fraction scales the threshold (skin.py:685-693): the same test in NumPy float64 decides what to expect
+    for fraction in (2.0, 0.5, 1.0):
+        disp2 = ((far.cpu().numpy() - g["positions"]) ** 2).sum(axis=1).max()
+        threshold = (fraction * float(g["skin"]) / 2.0) ** 2
+        assert abs(disp2 - threshold) > 1e-9 * threshold          # not a borderline case
+        assert bool(nl.needs_rebuild(far, fraction).item()) == bool(disp2 > threshold)
+
+
+def _golden_module():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_neighbour_golden", os.path.join(GOLDEN, "make_neighbour_golden.py"))
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    return module
+
+
+@pytest.mark.parametrize("name", ["fcc10648_triclinic", "silica3456"])
+def test_large_shapes_bitwise_against_reference_digests(name):
+    """The shapes that are too big to commit as arrays: a 10,648-atom triclinic primitive-FCC alloy cell (several
+    cell-list bins per axis, oblique stencil) and a 3,456-atom amorphous Si-O cell (rows of 45-80 pairs). The fixture
+    holds SHA-256 digests of the reference's own candidate and edge arrays; equal digests mean equal pairs, shifts and
+    order, bit for bit."""
+    import json
+    from fastmace_b200 import structures
+    golden = _golden_module()
+    with open(os.path.join(GOLDEN, "neighbours_large.json")) as handle:
+        record = json.load(handle)[name]
+    s = getattr(structures, record["builder"])(**{k: tuple(v) if isinstance(v, list) else v
+                                                  for k, v in record["kwargs"].items()})
+    assert s.natoms == record["natoms"]
+    assert golden.digest(s.positions) == record["positions"], "the seeded structure differs from the generator's"
+    nl = _list(s.cell, record["cutoff"], record["skin"])
+    x = torch.tensor(s.positions, device="cuda")
+    nl.build(x)
+    n = nl.num_candidates
+    assert n == record["num_candidates"] and nl.capacity == record["capacity"]
+    moved_host = s.positions + np.random.default_rng(1).normal(0, 0.03, s.positions.shape)
+    assert golden.digest(moved_host) == record["moved"]
+    moved = torch.tensor(moved_host, device="cuda")
+    nl.compact(moved)
+    nl.check_status()
+    count = int(nl.count.item())
+    assert count == record["count"]
+    got = golden.large_digests(dict(candidate_index=nl.candidate_index[:, :n].cpu().numpy(),
+                                    candidate_unit_shifts=nl.candidate_unit_shifts[:n].cpu().numpy(),
+                                    edge_index=nl.edge_index[:, :count].cpu().numpy(),
+                                    unit_shifts=nl.unit_shifts[:count].cpu().numpy(),
+                                    shifts=nl.shifts[:count].cpu().numpy()))
+    for key, value in got.items():
+        assert value == record[key], key
+    rows = np.diff(nl.edge_row_ptr.cpu().numpy())
+    assert int(rows.max()) == record["longest_row"] and int(rows.min()) == record["shortest_row"]
+    assert bool(nl.needs_rebuild(moved).item()) == record["needs_rebuild"]
 
 
 def test_second_build_keeps_addresses_and_in_graph_rebuild_is_gated():

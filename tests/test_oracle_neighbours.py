@@ -26,6 +26,34 @@ def test_build_and_compact_match_reference(path):
     assert nlo.needs_rebuild(g["moved"], g["positions"], float(g["skin"])) == bool(g["needs_rebuild"])
 
 
+def test_large_amorphous_cell_matches_reference_digests():
+    """3,456-atom amorphous Si-O cell (rows of 45-80 pairs): digests of the reference's own lists
+    (``tests/golden/neighbours_large.json``, written by ``make_neighbour_golden.py``)."""
+    import json
+
+    from fastmace_b200 import structures
+    sys_path_golden = os.path.join(GOLDEN, "make_neighbour_golden.py")
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_neighbour_golden", sys_path_golden)
+    golden = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(golden)
+    with open(os.path.join(GOLDEN, "neighbours_large.json")) as handle:
+        record = json.load(handle)["silica3456"]
+    s = getattr(structures, record["builder"])(**record["kwargs"])
+    assert golden.digest(s.positions) == record["positions"], "the seeded structure differs from the generator's"
+    snd, rcv, u = nlo.build(s.positions, s.cell, record["cutoff"], record["skin"])
+    assert len(snd) == record["num_candidates"]
+    moved = s.positions + np.random.default_rng(1).normal(0, 0.03, s.positions.shape)
+    assert golden.digest(moved) == record["moved"]
+    cs, cr, cu, csh, count = nlo.compact(moved, s.cell, snd, rcv, u, record["cutoff"])
+    assert count == record["count"]
+    got = golden.large_digests(dict(candidate_index=np.stack([snd, rcv]), candidate_unit_shifts=u,
+                                    edge_index=np.stack([cs[:count], cr[:count]]), unit_shifts=cu[:count],
+                                    shifts=csh[:count]))
+    for name, value in got.items():
+        assert value == record[name], name
+
+
 def test_edge_set_is_symmetric():
     g = np.load(os.path.join(GOLDEN, "neighbours_nacl216.npz"))
     edges = nlo.edge_set(g["edge_sender"], g["edge_receiver"], g["edge_unit_shifts"])

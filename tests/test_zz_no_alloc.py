@@ -60,3 +60,7 @@ def test_static_scratch_refuses_lists_beyond_its_maximum():
     status = lib.fmb_nl_compact_static(ctypes.byref(big), x.data_ptr(), _lib.current_stream())
     assert status == 1
     assert b"FMB_STATIC_COMPACT_MAX_ATOMS" in lib.fmb_last_error()
+    empty = _lib.NlStruct()
+    empty.n_atoms = 0
+    assert lib.fmb_nl_compact_static(ctypes.byref(empty), x.data_ptr(), _lib.current_stream()) == 1
+    assert b"no atoms" in lib.fmb_last_error()

@@ -26,8 +26,10 @@ STATUS_NO_MIRROR = 32
 
 EXPORTS = ("fmb_version", "fmb_last_error", "fmb_sizeof", "fmb_launch_count", "fmb_nl_build", "fmb_nl_compact", "fmb_nl_compact_static",
            "fmb_nl_needs_rebuild",
-           "fmb_forces", "fmb_edge_features", "fmb_harmonics_probe", "fmb_forward", "fmb_backward", "fmb_gemm", "fmb_langevin_first_half",
-           "fmb_langevin_second_half", "fmb_langevin_device_noise", "fmb_commit_forces", "fmb_profile_enable", "fmb_profile_read")
+           "fmb_forces", "fmb_forces_phase", "fmb_halo_gather_rows", "fmb_halo_add_rows", "fmb_halo_local_positions",
+           "fmb_halo_owned_forces", "fmb_edge_features", "fmb_harmonics_probe", "fmb_forward", "fmb_backward", "fmb_gemm", "fmb_langevin_first_half",
+           "fmb_langevin_second_half", "fmb_langevin_device_noise", "fmb_langevin_device_noise_ids",
+           "fmb_langevin_noise_sums", "fmb_langevin_first_half_global", "fmb_commit_forces", "fmb_profile_enable", "fmb_profile_read")
 
 
 class Fmb200Error(RuntimeError):
@@ -80,7 +82,7 @@ class WorkStruct(ctypes.Structure):
         ("partial", c_void_p), ("energy", c_void_p), ("forces", c_void_p), ("stress", c_void_p), ("status", c_void_p),
         ("n_energy_atoms", c_int32), ("n_inner_atoms", c_int32),
         ("mirror", c_void_p), ("edge_q", c_void_p), ("edge_dx", c_void_p),
-        ("symcon_groups", c_void_p), ("n_symcon_groups", c_int32), ("pad_", c_int32),
+        ("symcon_groups", c_void_p), ("n_symcon_groups", c_int32), ("halo_exchange", c_int32),
     ]
 
 
@@ -123,6 +125,11 @@ def load() -> ctypes.CDLL:
     lib.fmb_nl_needs_rebuild.argtypes = [POINTER(NlStruct), P, c_double, P]
     lib.fmb_forces.argtypes = [POINTER(ModelStruct), POINTER(NlStruct), POINTER(WorkStruct), P, P]
     lib.fmb_edge_features.argtypes = [POINTER(ModelStruct), POINTER(NlStruct), POINTER(WorkStruct), P, P]
+    lib.fmb_forces_phase.argtypes = [POINTER(ModelStruct), POINTER(NlStruct), POINTER(WorkStruct), P, c_int, P]
+    lib.fmb_halo_gather_rows.argtypes = [P, P, P, c_int, c_int, P]
+    lib.fmb_halo_add_rows.argtypes = [P, P, P, P, P, c_int, c_int, P]
+    lib.fmb_halo_local_positions.argtypes = [P, c_int, P, P, c_int, POINTER(c_double * 3), P, P]
+    lib.fmb_halo_owned_forces.argtypes = [P, P, P, P, c_int, P, P]
     lib.fmb_harmonics_probe.argtypes = [P, P, P, P, c_int, P]
     lib.fmb_forward.argtypes = [POINTER(ModelStruct), POINTER(NlStruct), POINTER(WorkStruct), P]
     lib.fmb_backward.argtypes = [POINTER(ModelStruct), POINTER(NlStruct), POINTER(WorkStruct), P]
@@ -130,6 +137,9 @@ def load() -> ctypes.CDLL:
     lib.fmb_langevin_first_half.argtypes = [POINTER(LangevinStruct), P]
     lib.fmb_langevin_second_half.argtypes = [POINTER(LangevinStruct), P]
     lib.fmb_langevin_device_noise.argtypes = [P, c_int, ctypes.c_ulonglong, P, P]
+    lib.fmb_langevin_device_noise_ids.argtypes = [P, c_int, P, ctypes.c_ulonglong, P, P]
+    lib.fmb_langevin_noise_sums.argtypes = [POINTER(LangevinStruct), P, P]
+    lib.fmb_langevin_first_half_global.argtypes = [POINTER(LangevinStruct), P, ctypes.c_longlong, P]
     lib.fmb_commit_forces.argtypes = [POINTER(WorkStruct), P, P, P, P]
     lib.fmb_profile_enable.argtypes = [c_int]
     lib.fmb_profile_read.argtypes = [POINTER(c_float), POINTER(c_int), c_int]

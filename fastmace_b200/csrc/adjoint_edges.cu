@@ -290,25 +290,32 @@ k_first_adjoint_edges(int n_rows, int n_valid, int n_add, int n_species, const i
 }
 
 // F_a = -(sum_row qe[e] - qe[mirror e]), virial_a = sum_row v_e (x) qe[e]; one warp per atom, lanes over its edges,
-// folded with a fixed butterfly.
+// folded with a fixed butterfly. RESTRICT: only the edges into atoms below n_valid carry a gradient -- an atom at or
+// beyond it (a halo atom) has no row terms and no virial, and a mirror edge counts only if its receiver (this edge's
+// sender) is below n_valid; qe and edge_vec are never read elsewhere.
+template <bool RESTRICT>
 __global__ void __launch_bounds__(256)
-k_force_gather(int n_atoms, const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ mirror,
-               const float4* __restrict__ qe, const float* __restrict__ edge_vec, float* __restrict__ force_acc,
-               float* __restrict__ atom_virial) {
+k_force_gather(int n_atoms, int n_valid, const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ senders,
+               const int32_t* __restrict__ mirror, const float4* __restrict__ qe, const float* __restrict__ edge_vec,
+               float* __restrict__ force_acc, float* __restrict__ atom_virial) {
     const int a = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (a >= n_atoms) return;
     float f[3] = {0.f, 0.f, 0.f}, vir[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    const bool own = !RESTRICT || a < n_valid;
     for (long long e = row_ptr[a] + lane; e < row_ptr[a + 1]; e += 32) {
-        const float4 q = qe[e];
-        const int m = mirror[e];
+        const float4 q = own ? qe[e] : make_float4(0.f, 0.f, 0.f, 0.f);
+        int m = mirror[e];
+        if (RESTRICT && senders[e] >= n_valid) m = -1;
         const float4 qm = m >= 0 ? qe[m] : make_float4(0.f, 0.f, 0.f, 0.f);
         f[0] += q.x - qm.x; f[1] += q.y - qm.y; f[2] += q.z - qm.z;
-        const float4 uv = __ldg(reinterpret_cast<const float4*>(edge_vec) + e);
-        const float vx = uv.x * uv.w, vy = uv.y * uv.w, vz = uv.z * uv.w;
-        vir[0] += vx * q.x; vir[1] += vy * q.y; vir[2] += vz * q.z;
-        vir[3] += 0.5f * (vy * q.z + vz * q.y);
-        vir[4] += 0.5f * (vx * q.z + vz * q.x);
-        vir[5] += 0.5f * (vx * q.y + vy * q.x);
+        if (own) {
+            const float4 uv = __ldg(reinterpret_cast<const float4*>(edge_vec) + e);
+            const float vx = uv.x * uv.w, vy = uv.y * uv.w, vz = uv.z * uv.w;
+            vir[0] += vx * q.x; vir[1] += vy * q.y; vir[2] += vz * q.z;
+            vir[3] += 0.5f * (vy * q.z + vz * q.y);
+            vir[4] += 0.5f * (vx * q.z + vz * q.x);
+            vir[5] += 0.5f * (vx * q.y + vy * q.x);
+        }
     }
 #pragma unroll
     for (int q = 0; q < 3; ++q) f[q] = warp_sum(f[q]);
@@ -381,15 +388,16 @@ int tp_adjoint_edges(const EdgeAdjointArgs& t, cudaStream_t stream) {
 }
 
 int gather_sender_gradient(const EdgeAdjointArgs& t, cudaStream_t stream) {
-    if (t.n_rows <= 0) return FMB_OK;
+    const int rows = t.n_gather > 0 ? t.n_gather : t.n_rows;     // atoms that collect; the edges of [0, n_rows) hand over
+    if (rows <= 0) return FMB_OK;
     const int in_dim = (t.lin + 1) * (t.lin + 1);
-    const int grid = t.n_rows < 1184 ? t.n_rows : 1184;
+    const int grid = rows < 1184 ? rows : 1184;
     if (in_dim == 1) {
-        k_gather_dx<1><<<grid, kC, 0, stream>>>(t.n_rows, t.n_rows, t.row_ptr, t.senders, t.mirror, t.dxe, t.d_x);
+        k_gather_dx<1><<<grid, kC, 0, stream>>>(rows, t.n_rows, t.row_ptr, t.senders, t.mirror, t.dxe, t.d_x);
     } else if (in_dim == 4) {
-        k_gather_dx<4><<<grid, kC, 0, stream>>>(t.n_rows, t.n_rows, t.row_ptr, t.senders, t.mirror, t.dxe, t.d_x);
+        k_gather_dx<4><<<grid, kC, 0, stream>>>(rows, t.n_rows, t.row_ptr, t.senders, t.mirror, t.dxe, t.d_x);
     } else if (in_dim == 9) {
-        k_gather_dx<9><<<grid, kC, 0, stream>>>(t.n_rows, t.n_rows, t.row_ptr, t.senders, t.mirror, t.dxe, t.d_x);
+        k_gather_dx<9><<<grid, kC, 0, stream>>>(rows, t.n_rows, t.row_ptr, t.senders, t.mirror, t.dxe, t.d_x);
     } else {
         return FMB_ERR_UNSUPPORTED;
     }
@@ -409,11 +417,17 @@ int first_adjoint_edges(const FirstArgs& f, int n_add, float* qe, cudaStream_t s
     return FMB_OK;
 }
 
-int force_gather(int n_atoms, const int32_t* row_ptr, const int32_t* mirror, const float* qe, const float* edge_vec,
-                 float* force_acc, float* atom_virial, cudaStream_t stream) {
+int force_gather(int n_atoms, int n_valid, const int32_t* row_ptr, const int32_t* senders, const int32_t* mirror,
+                 const float* qe, const float* edge_vec, float* force_acc, float* atom_virial, cudaStream_t stream) {
     if (n_atoms <= 0) return FMB_OK;
-    k_force_gather<<<ceil_div(n_atoms, 8), 256, 0, stream>>>(n_atoms, row_ptr, mirror, reinterpret_cast<const float4*>(qe),
-                                                             edge_vec, force_acc, atom_virial);
+    if (n_valid < n_atoms)
+        k_force_gather<true><<<ceil_div(n_atoms, 8), 256, 0, stream>>>(n_atoms, n_valid, row_ptr, senders, mirror,
+                                                                       reinterpret_cast<const float4*>(qe), edge_vec,
+                                                                       force_acc, atom_virial);
+    else
+        k_force_gather<false><<<ceil_div(n_atoms, 8), 256, 0, stream>>>(n_atoms, n_valid, row_ptr, senders, mirror,
+                                                                        reinterpret_cast<const float4*>(qe), edge_vec,
+                                                                        force_acc, atom_virial);
     FMB_LAUNCH_CHECK();
     return FMB_OK;
 }

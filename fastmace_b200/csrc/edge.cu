@@ -434,7 +434,8 @@ __global__ void k_harmonics_probe(const float* __restrict__ vectors, const float
 }  // namespace
 
 int edge_features(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, const double* positions,
-                  cudaStream_t stream) {
+                  const long long* count, cudaStream_t stream) {
+    if (!count) count = (const long long*)nl->count;
     EdgeParams p;
     p.n_layers = model->n_layers;
     p.capacity = nl->capacity;
@@ -450,13 +451,13 @@ int edge_features(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t
         const size_t smem_mma = (size_t)kMmaSmemFloats * sizeof(float);
         FMB_CUDA_CHECK(opt_in_shared_memory((const void*)k_edge_features_mma, (int)smem_mma));
         k_edge_features_mma<<<blocks, kThreads, smem_mma, stream>>>(p, positions, nl->edge_index, nl->unit_shifts,
-                                                                    (const long long*)nl->count, work->edge_vec,
+                                                                    count, work->edge_vec,
                                                                     work->edge_sh, work->edge_hidden);
         FMB_LAUNCH_CHECK();
         return FMB_OK;
     }
     k_edge_features<<<blocks, kThreads, smem, stream>>>(p, positions, nl->edge_index, nl->unit_shifts,
-                                                        (const long long*)nl->count, work->edge_vec, work->edge_sh,
+                                                        count, work->edge_vec, work->edge_sh,
                                                         work->edge_hidden);
     FMB_LAUNCH_CHECK();
     return FMB_OK;

@@ -125,6 +125,7 @@ struct Ctx {
     int n_chunks;
     long long chunk;
     cudaEvent_t radial_ready = nullptr;   // set when the radial weights of this pass are being produced on the side stream
+    bool exchange = false;                // halo-exchange mode: rows [n0, n) of x arrive from other ranks between phases
 };
 
 // When the whole edge list is one chunk, the last interaction's radial weights written by the forward pass are still
@@ -262,7 +263,18 @@ long long lin_weight_offset(const MidLayout& ml, int l) {
         if (rc__) return rc__;   \
     } while (0)
 
-int forward_layer(const Ctx& c, int layer) {
+// x = linear_up(h_{layer-1}) for the rows this rank computes; in halo-exchange mode this closes the first phase, so that
+// the rows of the halo atoms can be fetched from their owners before the tensor product reads them
+void queue_linear_up(LinearBatch& lb, const Ctx& c, int layer) {
+    const fmb_layer_t& L = c.m->layer[layer];
+    const int in_dim = dim_of(L.l_in_max);
+    const float* h_in = h_of(c, layer - 1);
+    for (int l = 0; l <= L.l_in_max; ++l)
+        block_linear(lb, c, c.n0, h_in, (long long)c.hidden_dim * kC, (long long)l * l * kC, kC, L.w_up, L.tc[1], L.tc_img[1],
+                     (long long)l * kC * kC, c.w->x, (long long)in_dim * kC, (long long)l * l * kC, kC, l, 0);
+}
+
+int forward_layer(const Ctx& c, int layer, bool with_up = true) {
     const fmb_layer_t& L = c.m->layer[layer];
     const MidLayout ml = mid_layout(L.l_in_max);
     FMB_REQUIRE(ml.mid_dim == L.mid_dim, "forward: message layout mismatch");
@@ -283,9 +295,7 @@ int forward_layer(const Ctx& c, int layer) {
                 block_linear(lb, c, rows, h_in, (long long)h_in_dim * kC, (long long)l * l * kC, kC, L.w_skip, L.tc[3], L.tc_img[3],
                              ((long long)l * c.m->n_species + z) * kC * kC, h_out, (long long)out_dim * kC,
                              (long long)l * l * kC, kC, l, 0, c.w->species, z);
-        for (int l = 0; l <= L.l_in_max; ++l)
-            block_linear(lb, c, c.n0, h_in, (long long)h_in_dim * kC, (long long)l * l * kC, kC, L.w_up, L.tc[1], L.tc_img[1],
-                         (long long)l * kC * kC, c.w->x, (long long)in_dim * kC, (long long)l * l * kC, kC, l, 0);
+        if (with_up) queue_linear_up(lb, c, layer);
         FMB_TRY(run_linears(c, lb));
         x = c.w->x;
     }
@@ -357,11 +367,25 @@ int forward_layer(const Ctx& c, int layer) {
 
 // d_h_out: gradient of this layer's output features [n][out_dim][C]. Produces d_x (layer >= 1) and the force / virial
 // contributions; for layer >= 1 also adds the skip and linear_up terms into d_h_in.
-int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in, int first_layer_of_pass) {
+// The adjoint of linear_up: d_h_in += d_x W_up^T for the rows this rank computes (after the halo atoms' shares of d_x
+// have come back from the ranks that hold them as ghosts, in halo-exchange mode).
+int backward_linear_up(const Ctx& c, int layer, float* d_h_in) {
+    const fmb_layer_t& L = c.m->layer[layer];
+    const int in_dim = dim_of(L.l_in_max);
+    LinearBatch lb;
+    for (int l = 0; l <= L.l_in_max; ++l)
+        block_linear(lb, c, c.n0, c.w->d_x, (long long)in_dim * kC, (long long)l * l * kC, kC, L.w_up_t, L.tc[2], L.tc_img[2],
+                     (long long)l * kC * kC, d_h_in, (long long)c.hidden_dim * kC, (long long)l * l * kC, kC, l, 1);
+    return run_linears(c, lb);
+}
+
+int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in, int first_layer_of_pass,
+                   bool with_up = true) {
     const fmb_layer_t& L = c.m->layer[layer];
     const MidLayout ml = mid_layout(L.l_in_max);
     const int in_dim = dim_of(L.l_in_max), out_dim = dim_of(L.l_out_max);
     const int rows = layer == 0 ? c.n0 : c.n1;     // atoms whose outputs of this layer carry a gradient
+    (void)in_dim;
     LinearBatch lb;
     for (int l = 0; l <= L.l_out_max; ++l)
         block_linear(lb, c, rows, d_h_out, (long long)out_dim * kC, (long long)l * l * kC, kC, L.w_prod_t, L.tc[8], L.tc_img[8],
@@ -389,7 +413,8 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
                          nz * kRadial, l, 0);
         FMB_TRY(run_linears(c, lb));
         FirstArgs f{};
-        f.n_rows = c.n; f.n_valid = rows; f.fresh_from = c.n0; f.n_species = nz;
+        // halo-exchange mode: the halo rows' edges belong to other ranks and are skipped altogether
+        f.n_rows = c.exchange ? rows : c.n; f.n_valid = rows; f.fresh_from = c.n0; f.n_species = nz;
         f.count = (const long long*)c.nl->count; f.row_ptr = c.nl->edge_row_ptr; f.senders = c.nl->edge_index;
         f.species = c.w->species; f.edge_sh = c.w->edge_sh; f.edge_vec = c.w->edge_vec;
         f.hidden = hidden_of(c, 0, 0); f.hidden_tangent = hidden_of(c, 0, 1); f.d_s = c.w->d_mid;
@@ -399,8 +424,8 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
             // the later interaction has written the edge-vector gradients of the rows below n0; add this one's and
             // turn the per-edge gradients into forces and virials
             FMB_TRY(first_adjoint_edges(f, first_layer_of_pass ? 0 : c.n0, c.w->edge_q, c.stream));
-            FMB_TRY(force_gather(c.n, c.nl->edge_row_ptr, c.w->mirror, c.w->edge_q, c.w->edge_vec, c.w->force_acc,
-                                 c.w->atom_virial, c.stream));
+            FMB_TRY(force_gather(c.n, c.exchange ? rows : c.n, c.nl->edge_row_ptr, c.nl->edge_index, c.w->mirror,
+                                 c.w->edge_q, c.w->edge_vec, c.w->force_acc, c.w->atom_virial, c.stream));
             return FMB_OK;
         }
         FMB_TRY(first_backward_launch(f, c.stream));
@@ -414,6 +439,7 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
     if (layer > 0 && edge_local_adjoint(c)) {
         EdgeAdjointArgs t{};
         t.lin = L.l_in_max; t.n_atoms = c.n; t.n_rows = c.n0; t.n_valid = rows; t.count = (const long long*)c.nl->count;
+        t.n_gather = c.exchange ? c.n : c.n0;      // halo atoms collect their shares too: they go back to their owners
         t.row_ptr = c.nl->edge_row_ptr; t.senders = c.nl->edge_index; t.mirror = c.w->mirror; t.x = c.w->x;
         t.edge_sh = c.w->edge_sh; t.edge_vec = c.w->edge_vec; t.tp_w = c.w->tp_w;
         t.tangent_offset = c.chunk * L.n_paths * kC; t.d_mid = c.w->d_mid; t.dxe = c.w->edge_dx; t.qe = c.w->edge_q;
@@ -433,12 +459,10 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
             StageScope scope(c.stream, kStTpBwd1);
             FMB_TRY(gather_sender_gradient(t, c.stream));
         }
-        for (int l = 0; l <= L.l_in_max; ++l)
-            block_linear(lb, c, c.n0, c.w->d_x, (long long)in_dim * kC, (long long)l * l * kC, kC, L.w_up_t, L.tc[2], L.tc_img[2],
-                         (long long)l * kC * kC, d_h_in, (long long)c.hidden_dim * kC, (long long)l * l * kC, kC, l, 1);
-        FMB_TRY(run_linears(c, lb));
+        if (with_up) FMB_TRY(backward_linear_up(c, layer, d_h_in));
         return FMB_OK;
     }
+    FMB_REQUIRE(!c.exchange, "halo-exchange mode needs the per-edge hand-over buffers (mirror, edge_q, edge_dx)");
     bool fused = false;
     // The fused adjoint executes more instructions per edge than the edge-major kernels (one reduction over channels per
     // path) and measures slower on the 1,944-atom cell; FMB_FUSED_ADJOINT=1 selects it (it needs no weight buffer).
@@ -477,12 +501,7 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
         StageScope scope(c.stream, layer == 0 ? kStTpBwd0 : kStTpBwd1);
         FMB_TRY(tp_backward_launch(t, c.stream));
     }
-    if (layer > 0) {
-        for (int l = 0; l <= L.l_in_max; ++l)
-            block_linear(lb, c, c.n0, c.w->d_x, (long long)in_dim * kC, (long long)l * l * kC, kC, L.w_up_t, L.tc[2], L.tc_img[2],
-                         (long long)l * kC * kC, d_h_in, (long long)c.hidden_dim * kC, (long long)l * l * kC, kC, l, 1);
-        FMB_TRY(run_linears(c, lb));
-    }
+    if (layer > 0 && with_up) FMB_TRY(backward_linear_up(c, layer, d_h_in));
     return FMB_OK;
 }
 
@@ -496,9 +515,16 @@ int make_ctx(Ctx& c, const fmb_model_t* m, const fmb_nl_t* nl, const fmb_work_t*
     FMB_REQUIRE(w->chunk_edges > 0, "forces: chunk_edges must be positive");
     c.m = m; c.nl = nl; c.w = w; c.stream = stream;
     c.n = w->n_atoms;
-    c.n1 = w->n_energy_atoms > 0 ? w->n_energy_atoms : c.n;
-    c.n0 = w->n_inner_atoms > 0 ? w->n_inner_atoms : c.n;
+    c.n1 = w->n_energy_atoms < 0 ? c.n : w->n_energy_atoms;      // negative: not restricted
+    c.n0 = w->n_inner_atoms < 0 ? c.n : w->n_inner_atoms;
+    FMB_REQUIRE(c.n1 > 0, "forces: no owned atoms (a rank without owned atoms skips the call)");
     FMB_REQUIRE(c.n1 <= c.n0 && c.n0 <= c.n, "forces: owned <= inner <= all atoms");
+    c.exchange = w->halo_exchange != 0;
+    if (c.exchange) {
+        FMB_REQUIRE(c.n0 == c.n1, "halo-exchange mode: the rows of both interactions are the owned atoms");
+        FMB_REQUIRE(w->mirror && w->edge_q && w->edge_dx && m->layer[0].first[0] != nullptr,
+                    "halo-exchange mode needs the per-edge hand-over buffers and the reassociated first interaction");
+    }
     c.hidden_dim = dim_of(m->hidden_lmax);
     c.count_cap = nl->capacity;
     c.chunk = std::min<long long>(w->chunk_edges, nl->capacity);
@@ -522,7 +548,17 @@ extern "C" FMB_API int fmb_edge_features(const fmb_model_t* model, const fmb_nl_
                                  const double* positions, fmb_stream_t stream) {
     FMB_REQUIRE(model && nl && work && positions, "fmb_edge_features: null argument");
     StageScope scope((cudaStream_t)stream, kStEdge);
-    const int rc = edge_features(model, nl, work, positions, (cudaStream_t)stream);
+    // halo-exchange mode: only the edges into owned atoms are evaluated on this rank (a prefix of the receiver-sorted
+    // list, limits[0] = row_ptr[owned atoms])
+    const long long* limit = nullptr;
+    if (work->halo_exchange) {
+        Ctx c;
+        FMB_TRY(make_ctx(c, model, nl, work, (cudaStream_t)stream));
+        k_edge_limits<<<1, 1, 0, c.stream>>>(nl->edge_row_ptr, c.n0, c.n1, edge_limits(c));
+        FMB_LAUNCH_CHECK();
+        limit = edge_limits(c);
+    }
+    const int rc = edge_features(model, nl, work, positions, limit, (cudaStream_t)stream);
     if (rc) return rc;
     // opposite-edge map for the per-edge adjoint (the compaction reorders edges every step)
     if (work->mirror && work->edge_q && work->edge_dx)
@@ -579,8 +615,42 @@ extern "C" FMB_API int fmb_backward(const fmb_model_t* model, const fmb_nl_t* nl
     return FMB_OK;
 }
 
+extern "C" FMB_API int fmb_forces_phase(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work,
+                                        const double* positions, int phase, fmb_stream_t stream) {
+    FMB_REQUIRE(work && work->halo_exchange, "fmb_forces_phase: the workspace is not in halo-exchange mode");
+    FMB_REQUIRE(phase >= 0 && phase <= 2, "fmb_forces_phase: phase is 0, 1 or 2");
+    Ctx c;
+    if (phase == 0) {
+        FMB_REQUIRE(positions, "fmb_forces_phase: phase 0 needs the positions");
+        FMB_TRY(fmb_edge_features(model, nl, work, positions, stream));
+        FMB_TRY(make_ctx(c, model, nl, work, (cudaStream_t)stream));
+        FMB_TRY(forward_layer(c, 0));
+        LinearBatch lb;
+        queue_linear_up(lb, c, 1);
+        return run_linears(c, lb);
+    }
+    FMB_TRY(make_ctx(c, model, nl, work, (cudaStream_t)stream));
+    if (phase == 1) {
+        FMB_TRY(forward_layer(c, 1, false));
+        {
+            StageScope scope(c.stream, kStReadout);
+            FMB_TRY(readout(model, c.n0, c.n1, h_of(c, 0), h_of(c, 1), work->node_energy, work->d_h, work->basis, c.stream));
+        }
+        return backward_layer(c, 1, work->basis, work->d_h, 1, false);
+    }
+    FMB_TRY(backward_linear_up(c, 1, work->d_h));
+    FMB_TRY(backward_layer(c, 0, work->d_h, nullptr, 0));
+    StageScope scope(c.stream, kStReadout);
+    return reduce_outputs(model, work, c.n1, cell_volume(nl), c.stream);
+}
+
 extern "C" FMB_API int fmb_forces(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, const double* positions,
                           fmb_stream_t stream) {
+    if (work && work->halo_exchange) {
+        // no other rank: the three phases back to back (the halo rows of x and d_x are then the caller's business)
+        for (int phase = 0; phase < 3; ++phase) FMB_TRY(fmb_forces_phase(model, nl, work, positions, phase, stream));
+        return FMB_OK;
+    }
     FMB_TRY(fmb_edge_features(model, nl, work, positions, stream));
     FMB_TRY(fmb_forward(model, nl, work, stream));
     FMB_TRY(fmb_backward(model, nl, work, stream));

@@ -60,20 +60,32 @@ k_noise(fmb_langevin_t lv) {
     }
 }
 
-__global__ void __launch_bounds__(256)
-k_first_half(fmb_langevin_t lv, int blocks) {
-    __shared__ double tot[10];
+// the ten sums of k_noise over this rank's atoms, in block order (a spatially decomposed run adds the ranks' sums)
+__global__ void k_noise_sums(fmb_langevin_t lv, int blocks, double* __restrict__ sums) {
     if (threadIdx.x < 10) {
         double v = 0.0;
         for (int b = 0; b < blocks; ++b) v += lv.partial[b * 16 + threadIdx.x];
+        sums[threadIdx.x] = v;
+    }
+}
+
+// `global_sums` / `n_global`: the ten sums and the atom count of the whole system when this rank integrates a part
+// of it (null / 0: the block partials of this launch and lv.n_atoms)
+__global__ void __launch_bounds__(256)
+k_first_half(fmb_langevin_t lv, int blocks, const double* __restrict__ global_sums, long long n_global) {
+    __shared__ double tot[10];
+    if (threadIdx.x < 10) {
+        double v = 0.0;
+        if (global_sums) v = global_sums[threadIdx.x];
+        else for (int b = 0; b < blocks; ++b) v += lv.partial[b * 16 + threadIdx.x];
         tot[threadIdx.x] = v;
     }
     __syncthreads();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    const int n = lv.n_atoms;
-    if (i >= n) return;
+    if (i >= lv.n_atoms) return;
+    const double n = n_global > 0 ? (double)n_global : (double)lv.n_atoms;
     const double m = lv.masses[i];
-    const double factor = sqrt((double)n / ((double)n - 1.0));
+    const double factor = sqrt(n / (n - 1.0));
 #pragma unroll
     for (int a = 0; a < 3; ++a) {
         double rp = lv.rnd_pos[3 * i + a], rv = lv.rnd_vel[3 * i + a];
@@ -138,17 +150,21 @@ __device__ __forceinline__ void box_muller(uint32_t a, uint32_t b, uint32_t c, u
     z1 = r * sn;
 }
 
+// `ids`: the atom index the generator is keyed with (null = the position in the array), so that an atom draws the same
+// numbers whichever rank integrates it
 __global__ void __launch_bounds__(256)
-k_device_noise(int n, unsigned long long seed, const int32_t* __restrict__ step, double* __restrict__ row) {
+k_device_noise(int n, unsigned long long seed, const int32_t* __restrict__ step, const int32_t* __restrict__ ids,
+               double* __restrict__ row) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
+    const uint32_t key = ids ? (uint32_t)ids[i] : (uint32_t)i;
     const uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
     double z[8];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-        uint32_t c[4] = {(uint32_t)i, (uint32_t)*step, (uint32_t)h, 0x6d616365u};
+        uint32_t c[4] = {key, (uint32_t)*step, (uint32_t)h, 0x6d616365u};
         philox(c, k0, k1);
-        uint32_t e[4] = {(uint32_t)i, (uint32_t)*step, (uint32_t)(h + 2), 0x6d616365u};
+        uint32_t e[4] = {key, (uint32_t)*step, (uint32_t)(h + 2), 0x6d616365u};
         philox(e, k0, k1);
         box_muller(c[0], c[1], c[2], c[3], z[4 * h + 0], z[4 * h + 1]);
         box_muller(e[0], e[1], e[2], e[3], z[4 * h + 2], z[4 * h + 3]);
@@ -170,7 +186,35 @@ using namespace fmb;
 extern "C" FMB_API int fmb_langevin_device_noise(double* noise_row, int n_atoms, unsigned long long seed,
                                                  const int32_t* step_counter, fmb_stream_t stream_) {
     FMB_REQUIRE(noise_row && step_counter && n_atoms > 0, "fmb_langevin_device_noise: bad argument");
-    k_device_noise<<<ceil_div(n_atoms, 256), 256, 0, (cudaStream_t)stream_>>>(n_atoms, seed, step_counter, noise_row);
+    k_device_noise<<<ceil_div(n_atoms, 256), 256, 0, (cudaStream_t)stream_>>>(n_atoms, seed, step_counter, nullptr, noise_row);
+    FMB_LAUNCH_CHECK();
+    return FMB_OK;
+}
+
+extern "C" FMB_API int fmb_langevin_device_noise_ids(double* noise_row, int n_atoms, const int32_t* atom_ids,
+                                                     unsigned long long seed, const int32_t* step_counter,
+                                                     fmb_stream_t stream_) {
+    FMB_REQUIRE(noise_row && step_counter && atom_ids && n_atoms > 0, "fmb_langevin_device_noise_ids: bad argument");
+    k_device_noise<<<ceil_div(n_atoms, 256), 256, 0, (cudaStream_t)stream_>>>(n_atoms, seed, step_counter, atom_ids, noise_row);
+    FMB_LAUNCH_CHECK();
+    return FMB_OK;
+}
+
+extern "C" FMB_API int fmb_langevin_noise_sums(const fmb_langevin_t* lv, double* sums, fmb_stream_t stream_) {
+    FMB_REQUIRE(lv && sums && lv->n_atoms > 0, "fmb_langevin_noise_sums: bad argument");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const int blocks = std::min(kBlocks, ceil_div(lv->n_atoms, 256));
+    k_noise<<<blocks, 256, 0, stream>>>(*lv);
+    FMB_LAUNCH_CHECK();
+    k_noise_sums<<<1, 32, 0, stream>>>(*lv, blocks, sums);
+    FMB_LAUNCH_CHECK();
+    return FMB_OK;
+}
+
+extern "C" FMB_API int fmb_langevin_first_half_global(const fmb_langevin_t* lv, const double* global_sums,
+                                                      long long n_global, fmb_stream_t stream_) {
+    FMB_REQUIRE(lv && global_sums && lv->n_atoms > 0 && n_global > 1, "fmb_langevin_first_half_global: bad argument");
+    k_first_half<<<ceil_div(lv->n_atoms, 256), 256, 0, (cudaStream_t)stream_>>>(*lv, 0, global_sums, n_global);
     FMB_LAUNCH_CHECK();
     return FMB_OK;
 }
@@ -181,7 +225,7 @@ extern "C" FMB_API int fmb_langevin_first_half(const fmb_langevin_t* lv, fmb_str
     const int blocks = std::min(kBlocks, ceil_div(lv->n_atoms, 256));
     k_noise<<<blocks, 256, 0, stream>>>(*lv);
     FMB_LAUNCH_CHECK();
-    k_first_half<<<ceil_div(lv->n_atoms, 256), 256, 0, stream>>>(*lv, blocks);
+    k_first_half<<<ceil_div(lv->n_atoms, 256), 256, 0, stream>>>(*lv, blocks, nullptr, 0);
     FMB_LAUNCH_CHECK();
     return FMB_OK;
 }

@@ -5,8 +5,9 @@
 
 namespace fmb {
 
+// `count`: device edge count to featurise (null = the list's own count)
 int edge_features(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, const double* positions,
-                  cudaStream_t stream);
+                  const long long* count, cudaStream_t stream);
 
 struct TpArgs {
     int lin;
@@ -94,6 +95,7 @@ struct EdgeAdjointArgs {
     int n_atoms;           // atoms of the list
     int n_rows;            // receivers [0, n_rows)
     int n_valid;           // atoms [0, n_valid) have a message gradient
+    int n_gather;          // atoms [0, n_gather) collect the gradient of their own features (d_x rows)
     long long chunk_e0, chunk_edges;   // this launch covers the edges [chunk_e0, chunk_e0 + chunk_edges) below the count
     const long long* count;
     const int32_t* row_ptr;
@@ -116,9 +118,10 @@ int tp_adjoint_edges(const EdgeAdjointArgs& t, cudaStream_t stream);
 int gather_sender_gradient(const EdgeAdjointArgs& t, cudaStream_t stream);
 // first interaction: adds its edge-vector gradients to qe (rows below n_add) or stores them
 int first_adjoint_edges(const FirstArgs& f, int n_add, float* qe, cudaStream_t stream);
-// forces (as gradients) and per-atom virials from the per-edge gradients
-int force_gather(int n_atoms, const int32_t* row_ptr, const int32_t* mirror, const float* qe, const float* edge_vec,
-                 float* force_acc, float* atom_virial, cudaStream_t stream);
+// forces (as gradients) and per-atom virials from the per-edge gradients; only the edges into atoms [0, n_valid) carry
+// a gradient (the others are read as zero, whatever qe holds for them)
+int force_gather(int n_atoms, int n_valid, const int32_t* row_ptr, const int32_t* senders, const int32_t* mirror,
+                 const float* qe, const float* edge_vec, float* force_acc, float* atom_virial, cudaStream_t stream);
 
 int symcon_forward(int n_atoms, int n_terms, int out_dim, const int32_t* terms, const float* coef,
                    const int32_t* species, const float* msg, float* basis, const int32_t* groups, int n_groups,

@@ -306,13 +306,15 @@ class DomainForceField:
                                        chunk_edges=self.chunk_edges, packed=self.packed, n_owned=local.n_owned,
                                        n_inner=local.n_inner)
         self.local_box_volume = float(np.prod(np.diag(box)))
-        self.local_ff.rebuild(self._local_positions(positions))
+        if local.n_owned > 0:
+            self.local_ff.rebuild(self._local_positions(positions))
         self.neighbours.reference_positions.copy_(positions)
         self.neighbours.rebuilds += 1
         return True
 
     def compact(self, positions) -> None:
-        self.local_ff.compact(self._local_positions(positions))
+        if self.local.n_owned > 0:
+            self.local_ff.compact(self._local_positions(positions))
 
     def needs_rebuild(self, positions, fraction: float = 1.0):
         return self.neighbours.needs_rebuild(positions, fraction) != 0
@@ -323,8 +325,12 @@ class DomainForceField:
     # ------------------------------------------------------------------ force call
     def partial(self, positions):
         """This rank's contribution before the reduction: (energy+virial scalars [10], forces [N, 3])."""
-        out = self.local_ff(self._local_positions(positions))
         self.forces.zero_()
+        if self.local.n_owned == 0:
+            # an empty brick (vacuum slab, more ranks than occupied bricks): nothing to evaluate, zeros to the sums
+            self.scalars.zero_()
+            return self.scalars, self.forces
+        out = self.local_ff(self._local_positions(positions))
         self.forces.index_add_(0, self.local_index, out.forces)
         self.scalars[0:1].copy_(out.energy)
         self.scalars[1:10].copy_((out.stress.double() * self.local_box_volume).reshape(9))
@@ -358,7 +364,8 @@ class DomainForceField:
                 out.stress.double().cpu().numpy() if stress else None)
 
     def check_status(self) -> None:
-        self.local_ff.check_status()
+        if self.local.n_owned > 0:
+            self.local_ff.check_status()
 
     def buffers(self):
         return {f"neighbours.{k}": v for k, v in self.local_ff.neighbours.buffers().items()}

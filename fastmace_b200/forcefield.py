@@ -42,7 +42,8 @@ class B200ForceField:
 
     def __init__(self, spec: MaceSpec, weights, numbers, cell, *, compute_stress: bool = False, device="cuda",
                  neighbours: NeighbourConfig | None = None, chunk_edges: int = DEFAULT_CHUNK_EDGES,
-                 positions=None, packed: PackedModel | None = None, n_owned: int = 0, n_inner: int = 0):
+                 positions=None, packed: PackedModel | None = None, n_owned: int = -1, n_inner: int = -1,
+                 halo_exchange: bool = False, atom_capacity: int | None = None):
         if not torch.cuda.is_available():
             raise _lib.Fmb200Error("B200ForceField needs a CUDA device: there is no CPU path")
         self.lib = _lib.load()
@@ -53,16 +54,27 @@ class B200ForceField:
         self._compute_stress = bool(compute_stress)
         self.numbers = np.asarray(numbers, dtype=np.int64)
         self.natoms = len(self.numbers)
+        # ``atom_capacity``: rows every per-atom buffer is allocated for; ``set_atoms`` may then change the atoms (a
+        # re-partition of a spatially decomposed run) without moving a buffer as long as they fit
+        self.atom_capacity = max(self.natoms, int(atom_capacity or 0))
         self.cell = np.asarray(cell, dtype=np.float64).reshape(3, 3)
-        # ``packed``: a model already packed for a superset of these species (domain decomposition re-creates the
-        # local force field at every re-partition and reuses one packed model); ``n_owned`` / ``n_inner``: the atoms
-        # are ordered owned | inner halo | outer halo (0 = every atom is owned)
+        # ``packed``: a model already packed for a superset of these species (the ranks of a decomposed run share
+        # one); ``n_owned`` / ``n_inner``: the atoms are ordered owned | inner halo | outer halo (negative = every atom is
+        # owned, the default); ``halo_exchange``: the atoms beyond the owned ones belong to other ranks and the call runs in
+        # three phases (``phase``) between which the caller moves the halo rows of ``x`` and ``d_x``
         self.packed = packed if packed is not None else \
             PackedModel(spec, weights, sorted(set(int(z) for z in self.numbers)), self._device)
         self.n_owned, self.n_inner = int(n_owned), int(n_inner)
-        self.species = self.packed.species_index(self.numbers)
-        self.symcon_groups = self._species_groups(self.species.cpu().numpy(), 4).to(self._device)
-        self.neighbours = CellListNeighbours(self.cell, spec.r_cut, self._device, torch.float32, neighbours)
+        self.halo_exchange = bool(halo_exchange)
+        if self.halo_exchange and self.n_inner != self.n_owned:
+            raise ValueError("halo-exchange mode evaluates both interactions for the owned atoms: n_inner == n_owned")
+        self.species = torch.zeros(self.atom_capacity, dtype=torch.int32, device=self._device)
+        self.symcon_groups = torch.full((self.atom_capacity // 4 + len(self.packed.species_z) + 1, 4), -1,
+                                        dtype=torch.int32, device=self._device)
+        self.n_symcon_groups = 0
+        self._upload_atoms()
+        self.neighbours = CellListNeighbours(self.cell, spec.r_cut, self._device, torch.float32, neighbours,
+                                             atom_capacity=self.atom_capacity)
         # FMB_CHUNK_EDGES overrides the chunk size (a tuning knob: small chunks keep the per-edge weights in L2)
         self.chunk_edges = int(os.environ.get("FMB_CHUNK_EDGES", chunk_edges))
         self.num_edges = 0
@@ -90,6 +102,10 @@ class B200ForceField:
         return self._compute_stress
 
     @property
+    def forces(self) -> torch.Tensor:
+        return self._forces_all[:self.natoms]
+
+    @property
     def edge_count(self) -> torch.Tensor:
         return self.neighbours.count
 
@@ -110,16 +126,59 @@ class B200ForceField:
         groups = np.concatenate(rows) if rows else np.zeros((0, size), dtype=np.int32)
         return torch.from_numpy(np.ascontiguousarray(groups))
 
+    def _upload_atoms(self) -> None:
+        """Species indices and contraction groups of the current atoms into their (capacity-sized) device buffers."""
+        species = self.packed.species_index(self.numbers)
+        self.species[:self.natoms].copy_(species)
+        # only the rows the interactions are evaluated for need a group
+        rows = self.n_inner if self.n_inner >= 0 else self.natoms
+        groups = self._species_groups(species[:rows].cpu().numpy(), 4)
+        self.n_symcon_groups = int(groups.shape[0])
+        self.symcon_groups[:self.n_symcon_groups].copy_(groups)
+
+    def set_atoms(self, numbers, n_owned: int = -1, n_inner: int = -1) -> bool:
+        """Replace the atoms (a re-partition of a spatially decomposed run): same model, same box, another set of
+        atomic numbers and owned / halo counts. The per-atom buffers stay where they are while the new atoms fit the
+        capacity; returns True if they had to be reallocated (every buffer moved). The neighbour list must be rebuilt
+        (``rebuild``) before the next call."""
+        self.numbers = np.asarray(numbers, dtype=np.int64)
+        self.natoms = len(self.numbers)
+        self.n_owned, self.n_inner = int(n_owned), int(n_inner)
+        if self.halo_exchange and self.n_inner != self.n_owned:
+            raise ValueError("halo-exchange mode: n_inner == n_owned")
+        moved = False
+        if self.natoms > self.atom_capacity:
+            self.atom_capacity = int(self.natoms * 1.1) + 16
+            self.species = torch.zeros(self.atom_capacity, dtype=torch.int32, device=self._device)
+            self.symcon_groups = torch.full((self.atom_capacity // 4 + len(self.packed.species_z) + 1, 4), -1,
+                                            dtype=torch.int32, device=self._device)
+            self.neighbours.set_atom_capacity(self.atom_capacity)
+            self._outputs()
+            self.work, self.buf = None, None
+            moved = True
+        self._upload_atoms()
+        self.neighbours.set_natoms(self.natoms)
+        if self.work is not None:
+            self._fill_counts(self.work)
+        return moved
+
+    def _fill_counts(self, w) -> None:
+        w.n_atoms = self.natoms
+        w.n_energy_atoms, w.n_inner_atoms = self.n_owned, self.n_inner
+        w.halo_exchange = int(self.halo_exchange)
+        w.species = self.species.data_ptr()
+        w.symcon_groups, w.n_symcon_groups = self.symcon_groups.data_ptr(), self.n_symcon_groups
+
     # ------------------------------------------------------------------ buffers
     def _outputs(self):
         dev = self._device
         self.energy = torch.zeros(1, dtype=torch.float64, device=dev)
-        self.forces = torch.zeros(self.natoms, 3, dtype=torch.float32, device=dev)
+        self._forces_all = torch.zeros(self.atom_capacity, 3, dtype=torch.float32, device=dev)
         self.stress = torch.zeros(3, 3, dtype=torch.float32, device=dev)
         self.status = torch.zeros((), dtype=torch.int32, device=dev)
 
     def _allocate_work(self):
-        spec, n, cap, dev = self.spec, self.natoms, self.neighbours.capacity, self._device
+        spec, n, cap, dev = self.spec, self.atom_capacity, self.neighbours.capacity, self._device
         if getattr(self, "buf", None) is not None:
             # the edge capacity grew: give the old buffers back to the device before the new ones are sized, so that the
             # two sets never exist side by side (the per-edge buffers of a large brick are tens of GB each)
@@ -160,6 +219,9 @@ class B200ForceField:
         need = cap * (hid * c * 4 + 20)
         # FMB_EDGE_ADJOINT=0 keeps the mirror-evaluation kernels (A/B tests)
         self.edge_local = need <= free - total // 10 and os.environ.get("FMB_EDGE_ADJOINT", "1") != "0"
+        if self.halo_exchange and not self.edge_local:
+            raise _lib.Fmb200Error(f"halo-exchange mode needs {need / 2 ** 30:.1f} GiB for the per-edge hand-over "
+                                   f"buffers, {max(0, free - total // 10) / 2 ** 30:.1f} GiB are free: use more ranks")
         if self.edge_local:
             try:
                 buf["mirror"] = torch.zeros(cap, dtype=torch.int32, device=dev)
@@ -173,14 +235,12 @@ class B200ForceField:
                 self.edge_local = False
         self.buf = buf
         w = _lib.WorkStruct()
-        w.n_atoms, w.edge_capacity, w.chunk_edges, w.compute_stress = n, cap, chunk, int(self._compute_stress)
-        w.species = self.species.data_ptr()
+        w.edge_capacity, w.chunk_edges, w.compute_stress = cap, chunk, int(self._compute_stress)
         for name, tensor in buf.items():
             setattr(w, name, tensor.data_ptr())
-        w.energy, w.forces, w.stress = self.energy.data_ptr(), self.forces.data_ptr(), self.stress.data_ptr()
+        w.energy, w.forces, w.stress = self.energy.data_ptr(), self._forces_all.data_ptr(), self.stress.data_ptr()
         w.status = self.status.data_ptr()
-        w.n_energy_atoms, w.n_inner_atoms = self.n_owned, self.n_inner
-        w.symcon_groups, w.n_symcon_groups = self.symcon_groups.data_ptr(), int(self.symcon_groups.shape[0])
+        self._fill_counts(w)
         self.work = w
 
     # ------------------------------------------------------------------ protocol methods
@@ -215,6 +275,17 @@ class B200ForceField:
                                        positions.data_ptr(), _lib.current_stream()), "fmb_forces")
         return ForceOutput(self.energy, self.forces, self.stress if self._compute_stress else None)
 
+    def phase(self, index: int, positions: torch.Tensor | None = None) -> None:
+        """One of the three phases of a halo-exchange call (``fmb_forces_phase``): 0 reads ``positions`` and ends
+        with ``x`` of the owned atoms, 1 ends with ``d_x`` of every local atom, 2 ends with the outputs."""
+        if self.work is None:
+            raise _lib.Fmb200Error("call rebuild() and compact() before the first force call")
+        if index == 0:
+            self.calls += 1
+        _lib.check(self.lib.fmb_forces_phase(self.packed.pointer(), self.neighbours.pointer(), ctypes.byref(self.work),
+                                             positions.data_ptr() if positions is not None else None, int(index),
+                                             _lib.current_stream()), "fmb_forces_phase")
+
     def evaluate(self, atoms, stress: bool = False):
         """One-off evaluation (``ForceField.evaluate``): rebuilds the list, synchronises, returns host values:
         (energy float eV, forces (N, 3) float64 ndarray, stress (3, 3) ndarray or None)."""
@@ -241,7 +312,7 @@ class B200ForceField:
             raise _lib.Fmb200Error("a tensor-core kernel gave up waiting (FMB_STATUS_TENSOR_TIMEOUT)")
 
     def per_atom_energies(self):
-        return self.buf["node_energy"].double().cpu().numpy()
+        return self.buf["node_energy"][:self.natoms].double().cpu().numpy()
 
     def buffers(self):
         out = {f"neighbours.{name}": value for name, value in self.neighbours.buffers().items()}

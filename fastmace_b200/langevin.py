@@ -6,7 +6,9 @@ Same coefficients (``langevin.py:184-198``), same noise source and order: NumPy 
 ``standard_normal((k, 2, N, 3))`` per batch (per step ``xi`` then ``eta``), uploaded ``noise_batch`` steps at a time
 and capped at 64 MiB (``langevin.py:31-45``). The kernels pick the step's row through a device-side cursor, so a
 captured step needs no per-step host copy; the next batch is drawn on a background thread into pinned memory while
-the current one is consumed (``langevin.py:67-89``).
+the current one is consumed (``langevin.py:67-89``). The first batches are short (8, 16, 32 ... steps up to
+``noise_batch``) so that a run of a few steps does not wait for 256 steps of normals it never reads; NumPy fills the
+array in order, so the stream of numbers is the same for any split into batches.
 """
 
 from __future__ import annotations
@@ -24,6 +26,7 @@ from .state import SimulationState
 from .structures import FS, KB
 
 NOISE_BATCH_BYTES = 64 * 2 ** 20
+FIRST_NOISE_ROWS = 8
 
 
 @dataclasses.dataclass(frozen=True)
@@ -48,7 +51,8 @@ class Langevin:
     ``fastmace/integrators/langevin.py``), each half one CUDA kernel on float64 state that stays on the device."""
 
     def __init__(self, state: SimulationState, config: IntegratorConfig | None = None, *, temperature_K: float = 0.0,
-                 force_buffer: torch.Tensor | None = None, noise: str = "host", device_seed: int = 0):
+                 force_buffer: torch.Tensor | None = None, noise: str = "host", device_seed: int = 0,
+                 atom_ids: torch.Tensor | None = None, n_global: int = 0):
         """``noise="host"``: the reference's NumPy stream, uploaded in batches. ``noise="device"``: counter-based
         normals generated on the GPU per step (``fmb_langevin_device_noise``): not the reference's numbers, but
         identical on every rank of a domain-decomposed run and free of the host draw that limits large systems."""
@@ -62,6 +66,13 @@ class Langevin:
         if noise not in ("host", "device"):
             raise ValueError("noise is 'host' or 'device'")
         self.noise_mode, self.device_seed = noise, int(device_seed)
+        # a rank of a spatially decomposed run integrates ``state``'s atoms out of ``n_global``: the device noise is
+        # keyed by ``atom_ids`` (int32 indices in the whole system) and the centre-of-mass projection uses the sums
+        # over all ranks (``noise_sums`` / ``first_half_global``)
+        self.atom_ids = None if atom_ids is None else atom_ids.to(torch.int32).contiguous()
+        self.n_global = int(n_global)
+        if self.atom_ids is not None and noise != "device":
+            raise ValueError("atom_ids key the device noise generator: pass noise='device'")
         self.noise_batch = 1 if noise == "device" else noise_steps(config.noise_batch, 6 * self.natoms)
         dev = state.positions.device
         f64 = dict(dtype=torch.float64, device=dev)
@@ -83,7 +94,9 @@ class Langevin:
         self.cursor_dev = torch.zeros((), dtype=torch.int32, device=dev)
         shape = (self.noise_batch, 2, self.natoms, 3)
         state.rng.batch = torch.zeros(shape, **f64)
-        state.rng.cursor = self.noise_batch        # used up: the first step refills
+        self.rows = self.noise_batch               # steps the batch on the device holds
+        self._draw_rows = [min(FIRST_NOISE_ROWS, self.noise_batch)] * 2     # rows drawn into each staging buffer
+        state.rng.cursor = self.rows               # used up: the first step refills
         self.zero_cursor = torch.zeros((), dtype=torch.int32, device=dev)
         self._staging = [] if noise == "device" else \
             [torch.empty(shape, dtype=torch.float64).pin_memory() if dev.type == "cuda"
@@ -120,8 +133,8 @@ class Langevin:
 
     # ------------------------------------------------------------------ noise
     def _draw_into(self, generator: np.random.Generator, slot: int) -> None:
-        np.copyto(self._staging[slot].numpy(),
-                  generator.standard_normal(size=(self.noise_batch, 2, self.natoms, 3)))
+        rows = self._draw_rows[slot]
+        generator.standard_normal(out=self._staging[slot].numpy()[:rows])     # straight into the pinned buffer
 
     def _start_draw_ahead(self, state: SimulationState) -> None:
         slot = self._next
@@ -140,19 +153,22 @@ class Langevin:
         else:
             self._ahead.join()
         slot = self._next
-        rng.batch.copy_(self._staging[slot], non_blocking=True)
+        rows = self._draw_rows[slot]
+        rng.batch[:rows].copy_(self._staging[slot][:rows], non_blocking=True)
         if self._staging_events[slot] is not None:
             self._staging_events[slot].record()
         self.cursor_dev.zero_()
         rng.cursor = 0
+        self.rows = rows
         self._next = 1 - slot
+        self._draw_rows[self._next] = min(2 * rows, self.noise_batch)
         self._start_draw_ahead(state)
 
     def prepare_step(self, state: SimulationState) -> None:
         """Refill the noise batch when it is used up (host; between replays) and advance the host cursor."""
         if self.noise_mode == "device":
             return
-        if state.rng.cursor == self.noise_batch:
+        if state.rng.cursor >= self.rows:
             self.refill(state)
         state.rng.cursor += 1
 
@@ -163,15 +179,38 @@ class Langevin:
         state.rng.batch[:k].copy_(torch.from_numpy(np.ascontiguousarray(rows)))
         self.cursor_dev.zero_()
         state.rng.cursor = 0
+        self.rows = k
 
     # ------------------------------------------------------------------ stages (graph-capturable)
-    def first_half(self, state: SimulationState) -> None:
-        if self.noise_mode == "device":
+    def _device_noise(self, state: SimulationState) -> None:
+        if self.noise_mode != "device":
+            return
+        if self.atom_ids is not None:
+            _lib.check(self.lib.fmb_langevin_device_noise_ids(state.rng.batch.data_ptr(), self.natoms,
+                                                              self.atom_ids.data_ptr(), self.device_seed,
+                                                              self.cursor_dev.data_ptr(), _lib.current_stream()),
+                       "fmb_langevin_device_noise_ids")
+        else:
             _lib.check(self.lib.fmb_langevin_device_noise(state.rng.batch.data_ptr(), self.natoms, self.device_seed,
                                                           self.cursor_dev.data_ptr(), _lib.current_stream()),
                        "fmb_langevin_device_noise")
+
+    def first_half(self, state: SimulationState) -> None:
+        self._device_noise(state)
         _lib.check(self.lib.fmb_langevin_first_half(ctypes.byref(self.struct), _lib.current_stream()),
                    "fmb_langevin_first_half")
+
+    def noise_sums(self, state: SimulationState, sums: torch.Tensor) -> None:
+        """First part of the first half on a rank that integrates a part of the system: the random terms of its
+        atoms and, in ``sums`` (10 float64), its share of the sums the centre-of-mass projection needs."""
+        self._device_noise(state)
+        _lib.check(self.lib.fmb_langevin_noise_sums(ctypes.byref(self.struct), sums.data_ptr(), _lib.current_stream()),
+                   "fmb_langevin_noise_sums")
+
+    def first_half_global(self, state: SimulationState, sums: torch.Tensor) -> None:
+        """Second part: projection with the sums over all ranks, half kick, drift."""
+        _lib.check(self.lib.fmb_langevin_first_half_global(ctypes.byref(self.struct), sums.data_ptr(), self.n_global,
+                                                           _lib.current_stream()), "fmb_langevin_first_half_global")
 
     def second_half(self, state: SimulationState) -> None:
         _lib.check(self.lib.fmb_langevin_second_half(ctypes.byref(self.struct), _lib.current_stream()),

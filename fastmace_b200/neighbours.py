@@ -59,7 +59,8 @@ def cell_list_plan(cell: np.ndarray, reach: float):
 class CellListNeighbours:
     """Periodic pairs within cutoff + skin built on the device, compacted to the cutoff each step."""
 
-    def __init__(self, cell, cutoff: float, device, float_dtype=torch.float32, config: NeighbourConfig | None = None):
+    def __init__(self, cell, cutoff: float, device, float_dtype=torch.float32, config: NeighbourConfig | None = None,
+                 atom_capacity: int = 0):
         self.lib = _lib.load()
         self.config = config or NeighbourConfig()
         self.cell = np.asarray(cell, dtype=np.float64).reshape(3, 3).copy()
@@ -80,6 +81,7 @@ class CellListNeighbours:
         self.variable_cell = False
         self.reader_stream = None
         self.natoms = None
+        self.atom_capacity = int(atom_capacity)      # rows of the per-atom buffers (0: the atoms of the first build)
         self.struct = _lib.NlStruct()
         self._set_cell_constants()
         dev = self.device
@@ -89,7 +91,11 @@ class CellListNeighbours:
         self.rebuild_flag = torch.zeros((), dtype=torch.int32, device=dev)
         self.max_disp2 = torch.zeros((), dtype=torch.float64, device=dev)
         self.build_cell = torch.tensor(self.cell, dtype=torch.float64, device=dev)
-        self.reference_positions = None
+        self._reference_all = None
+
+    @property
+    def reference_positions(self):
+        return None if self._reference_all is None else self._reference_all[:self.natoms]
 
     # ------------------------------------------------------------------ set-up
     def _set_cell_constants(self):
@@ -112,9 +118,26 @@ class CellListNeighbours:
             s.reach_bins[a] = self.reach_bins[a]
             s.pad_unit_shift[a] = float(self._pad_unit_shift[a])
 
-    def _allocate_atoms(self, natoms: int):
+    def set_natoms(self, natoms: int) -> None:
+        """Another number of atoms in the same buffers (a re-partition); the list must be rebuilt afterwards."""
+        if self.natoms is None:
+            return
+        if natoms > self.atom_capacity:
+            raise ValueError(f"{natoms} atoms exceed the list's capacity of {self.atom_capacity}")
+        self.natoms = int(natoms)
+        self.struct.n_atoms = int(natoms)
+        self.num_candidates = 0
+
+    def set_atom_capacity(self, capacity: int) -> None:
+        self.atom_capacity = int(capacity)
+        if self.natoms is not None:
+            self._allocate_atoms(min(self.natoms, self.atom_capacity))
+
+    def _allocate_atoms(self, live: int):
         dev, i32, f64 = self.device, torch.int32, torch.float64
-        self.natoms = natoms
+        self.atom_capacity = max(self.atom_capacity, live)
+        natoms = self.atom_capacity
+        self.natoms = live
         total_bins = int(np.prod(self.nbins))
         self.wrapped = torch.zeros(natoms, 3, dtype=f64, device=dev)
         self.offsets = torch.zeros(natoms, 3, dtype=f64, device=dev)
@@ -128,13 +151,14 @@ class CellListNeighbours:
         self.edge_row_count = torch.zeros(natoms + 1, dtype=i32, device=dev)
         self.edge_row_ptr = torch.zeros(natoms + 1, dtype=i32, device=dev)
         self.scan_scratch = torch.zeros(2 * (max(natoms, total_bins) // 4096 + 2) + 8, dtype=i32, device=dev)
-        self.reference_positions = torch.zeros(natoms, 3, dtype=f64, device=dev)
+        self._reference_all = torch.zeros(natoms, 3, dtype=f64, device=dev)
         s = self.struct
-        s.n_atoms = natoms
+        s.n_atoms = live
         for name in ("wrapped", "offsets", "atom_bin", "bin_count", "bin_start", "bin_fill", "bin_atoms",
                      "cand_row_count", "cand_row_ptr", "edge_row_count", "edge_row_ptr", "scan_scratch",
-                     "reference_positions", "build_cell", "count", "status", "rebuild_flag"):
+                     "build_cell", "count", "status", "rebuild_flag"):
             setattr(s, name, getattr(self, name).data_ptr())
+        s.reference_positions = self._reference_all.data_ptr()
         s.num_candidates = self.num_candidates_dev.data_ptr()
         s.max_disp2_bits = self.max_disp2.data_ptr()
 

@@ -210,7 +210,8 @@ typedef struct {
     float* forces;                    /* [n_atoms][3] */
     float* stress;                    /* [9] */
     uint32_t* status;                 /* [1] */
-    /* Domain decomposition (0 = every atom): the atoms are ordered owned | inner halo | outer halo. Atoms
+    /* Domain decomposition (negative = every atom; 0 owned atoms is refused: such a rank has nothing to evaluate and
+     * skips the call): the atoms are ordered owned | inner halo | outer halo. Atoms
      * [0, n_energy_atoms) are owned: only they contribute energy and get the last layer's rows; atoms
      * [0, n_inner_atoms) get the first layer's rows (they are senders of owned receivers); the rest only act as
      * species-only senders of the first layer. Forces come out for every atom (partial sums for halo atoms). */
@@ -228,7 +229,13 @@ typedef struct {
      * CTA. */
     const int32_t* symcon_groups;
     int32_t n_symcon_groups;
-    int32_t pad_;
+    /* Halo-exchange mode of a spatially decomposed run (nonzero; needs n_energy_atoms == n_inner_atoms = the owned
+     * atoms and the hand-over buffers): the atoms beyond the owned ones are halo atoms that belong to other ranks.
+     * Both interactions are evaluated for the owned atoms only; the halo rows of x are written by the caller
+     * between phase 0 and phase 1 (fetched from their owners), the halo rows of d_x are read by the caller after
+     * phase 1 (returned to their owners, whose rows receive them before phase 2), and forces come out as partial sums
+     * for every local atom (the halo atoms' shares go back to their owners). */
+    int32_t halo_exchange;
 } fmb_work_t;
 
 /* MACEForceField.__call__ (fastmace/model/forces.py:1127-1136,1220-1240): energy (float64), forces and stress of the
@@ -237,6 +244,34 @@ typedef struct {
  * edge count from the device. */
 FMB_API int fmb_forces(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, const double* positions,
                fmb_stream_t stream);
+
+/* fmb_forces in three phases for a workspace in halo-exchange mode; no counterpart in the reference, which runs one
+ * structure on one GPU (SPEC.md:70-74; structural precedent: the halo senders of a tile, fastmace/model/tiled.py:1-26).
+ * phase 0: edge features of the edges into owned atoms, first interaction, x = linear_up(h1) of the owned atoms;
+ * phase 1: second interaction, readouts, its adjoint down to d_x of every local atom;
+ * phase 2: adjoint of linear_up and of the first interaction, forces (partial sums), energy and virial of the owned
+ *          atoms' edges.
+ * `positions` is read by phase 0 only. Each phase is stream-ordered and graph-capturable like fmb_forces. */
+FMB_API int fmb_forces_phase(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, const double* positions,
+                             int phase, fmb_stream_t stream);
+
+/* Halo-exchange helpers (no counterpart in the reference): out[i] = rows[index[i]] for rows of row_bytes bytes (a
+ * multiple of 4): the rows a peer holds as halo atoms, gathered into the send buffer. */
+FMB_API int fmb_halo_gather_rows(const void* rows, const int32_t* index, void* out, int n, int row_bytes,
+                                 fmb_stream_t stream);
+/* dst[target[t]] += sum_{k in [ptr[t], ptr[t+1])} received[source[k]], rows of row_floats floats, summed in the order
+ * of k (no atomics): what the peers computed for atoms this rank owns, added into the owners' rows. target null =
+ * row t itself. */
+FMB_API int fmb_halo_add_rows(const float* received, const int32_t* ptr, const int32_t* source, const int32_t* target,
+                              float* dst, int n_targets, int row_floats, fmb_stream_t stream);
+/* out [n_owned + n_halo][3] = (owned | received) + shift - origin, float64: the rank's atoms in its own frame (shift
+ * [n_owned + n_halo][3]: whole cell vectors that bring an owned atom into the brick and a halo atom to its image). */
+FMB_API int fmb_halo_local_positions(const double* owned, int n_owned, const double* received, const double* shift,
+                                     int n_halo, const double* origin, double* out, fmb_stream_t stream);
+/* forces64[i] = local_forces[i] + sum_{k in [ptr[i], ptr[i+1])} received[source[k]] for the owned atoms (ptr null = no
+ * peers): the reverse force accumulation, cast to the float64 state (fastmace/engine/graph.py:1125-1131). */
+FMB_API int fmb_halo_owned_forces(const float* local_forces, const float* received, const int32_t* ptr,
+                                  const int32_t* source, int n_owned, double* forces64, fmb_stream_t stream);
 
 /* Individual stages, exported for kernel-level parity tests (same arguments as inside fmb_forces). */
 FMB_API int fmb_edge_features(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, const double* positions,
@@ -302,6 +337,18 @@ FMB_API int fmb_langevin_second_half(const fmb_langevin_t* lv, fmb_stream_t stre
  * sizes where the host draw of 6 N normals per step would limit the step. */
 FMB_API int fmb_langevin_device_noise(double* noise_row, int n_atoms, unsigned long long seed,
                                       const int32_t* step_counter, fmb_stream_t stream);
+/* The same generator keyed by atom_ids[i] instead of i: in a spatially decomposed run an atom draws the same numbers
+ * whichever rank integrates it (atom_ids = the atoms' indices in the whole system). */
+FMB_API int fmb_langevin_device_noise_ids(double* noise_row, int n_atoms, const int32_t* atom_ids, unsigned long long seed,
+                                          const int32_t* step_counter, fmb_stream_t stream);
+/* fmb_langevin_first_half in two parts for a rank that integrates a part of the system (no counterpart in the
+ * reference): fmb_langevin_noise_sums computes the random terms of this rank's atoms and writes the ten sums the
+ * centre-of-mass projection needs (sum rnd_pos [3], sum m rnd_pos [3], sum m rnd_vel [3], sum m) to `sums`; the caller
+ * adds the ranks' sums; fmb_langevin_first_half_global applies the projection with the system's sums and atom count,
+ * then the half kick and the drift (fastmace/integrators/langevin.py:233-257). */
+FMB_API int fmb_langevin_noise_sums(const fmb_langevin_t* lv, double* sums, fmb_stream_t stream);
+FMB_API int fmb_langevin_first_half_global(const fmb_langevin_t* lv, const double* global_sums, long long n_global,
+                                           fmb_stream_t stream);
 /* state.forces/energy/stress <- ForceOutput (fastmace/engine/graph.py:1125-1131): fp32 -> float64 copies. */
 FMB_API int fmb_commit_forces(const fmb_work_t* work, double* forces64, double* energy64, double* stress64,
                       fmb_stream_t stream);

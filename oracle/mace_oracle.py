@@ -160,8 +160,13 @@ def symmetric_contraction(spec, weights, layer, message, species, chunk=128):
                 x = message[idx]                                             # [n, 16, C]
                 acc = None
                 for nu in range(spec.correlation, 0, -1):
-                    acc = uws[nu][None] if acc is None else acc + uws[nu][None]
-                    acc = torch.einsum("n...ic,nic->n...c", acc.expand(len(idx), *acc.shape[1:]), x)
+                    u = uws[nu]                                              # [M, 16 (nu times), C]
+                    if acc is None:
+                        # the weighted coupling tensor has no atom axis yet: one GEMM per channel over all atoms
+                        flat = u.reshape(-1, u.shape[-2], c)
+                        acc = torch.einsum("kic,nic->nkc", flat, x).reshape(len(idx), *u.shape[:-2], c)
+                    else:
+                        acc = torch.einsum("n...ic,nic->n...c", acc + u[None], x)
                 out[idx, big_l * big_l:(big_l + 1) ** 2, :] = acc
     return out
 

@@ -315,7 +315,14 @@ class B200ForceField:
         return self.buf["node_energy"][:self.natoms].double().cpu().numpy()
 
     def buffers(self):
+        """Persistent device buffers under the names the reference's registry has policies for
+        (``fastmace/engine/registry.py:91-139``): everything a rebuild makes as ``neighbours.*`` (the status words
+        included: they are sticky until a rebuild clears them) and the cell. The work buffers of a force call are
+        written before they are read in every call and carry nothing across steps."""
         out = {f"neighbours.{name}": value for name, value in self.neighbours.buffers().items()}
+        out["neighbours.status"] = self.neighbours.status
+        out["neighbours.force_status"] = self.status
+        out["cell"] = self.neighbours.build_cell
         return out
 
     def info(self):

@@ -52,7 +52,7 @@ class Langevin:
 
     def __init__(self, state: SimulationState, config: IntegratorConfig | None = None, *, temperature_K: float = 0.0,
                  force_buffer: torch.Tensor | None = None, noise: str = "host", device_seed: int = 0,
-                 atom_ids: torch.Tensor | None = None, n_global: int = 0):
+                 atom_ids: torch.Tensor | None = None, n_global: int = 0, cursor: str = "device"):
         """``noise="host"``: the reference's NumPy stream, uploaded in batches. ``noise="device"``: counter-based
         normals generated on the GPU per step (``fmb_langevin_device_noise``): not the reference's numbers, but
         identical on every rank of a domain-decomposed run and free of the host draw that limits large systems."""
@@ -66,6 +66,14 @@ class Langevin:
         if noise not in ("host", "device"):
             raise ValueError("noise is 'host' or 'device'")
         self.noise_mode, self.device_seed = noise, int(device_seed)
+        # ``cursor="device"``: the second half advances the row counter on the device, so a captured whole step needs
+        # no host write (B200Engine). ``cursor="host"``: ``prepare_step`` writes the row index before every step and
+        # the kernels leave it alone -- for engines that replay a stage several times while they capture it (the
+        # reference's GraphEngine warms a stage up three times, fastmace/engine/graph.py:1328-1397) and would
+        # otherwise run the counter ahead
+        if cursor not in ("device", "host"):
+            raise ValueError("cursor is 'device' or 'host'")
+        self.cursor_mode = cursor
         # a rank of a spatially decomposed run integrates ``state``'s atoms out of ``n_global``: the device noise is
         # keyed by ``atom_ids`` (int32 indices in the whole system) and the centre-of-mass projection uses the sums
         # over all ranks (``noise_sums`` / ``first_half_global``)
@@ -119,7 +127,8 @@ class Langevin:
         # device noise: the batch holds the current step only (row 0) and the counter the second half advances is
         # the step index the generator is keyed with
         s.noise_cursor = (self.zero_cursor if noise == "device" else self.cursor_dev).data_ptr()
-        s.noise_cursor_rw = self.cursor_dev.data_ptr()
+        self._idle_cursor = torch.zeros((), dtype=torch.int32, device=dev)
+        s.noise_cursor_rw = (self.cursor_dev if cursor == "device" else self._idle_cursor).data_ptr()
         s.x_old, s.rnd_pos, s.rnd_vel = self.x_old.data_ptr(), self.rnd_pos.data_ptr(), self.rnd_vel.data_ptr()
         s.partial = self.partial.data_ptr()
 
@@ -170,6 +179,8 @@ class Langevin:
             return
         if state.rng.cursor >= self.rows:
             self.refill(state)
+        if self.cursor_mode == "host":
+            self.cursor_dev.fill_(int(state.rng.cursor))
         state.rng.cursor += 1
 
     def upload_noise(self, state: SimulationState, rows: np.ndarray) -> None:
@@ -219,6 +230,9 @@ class Langevin:
     def start(self, state: SimulationState) -> None:
         """Called once after the initial force evaluation; Langevin has nothing to prepare
         (``integrators/base.py:123-128``)."""
+
+    def register_derived(self, registry, state: SimulationState) -> None:
+        """Nothing here is derived from state an event may change (``integrators/base.py``: default none)."""
 
     def mid_step_tensors(self, state: SimulationState):
         return (state.velocities,)

@@ -569,7 +569,7 @@ def main():
         getattr(state, name).copy_(value_)
     state.rng = RandomStream(np.random.default_rng(WORKLOADS[args.workload]["seed"] + 1))
     user_integrator = Langevin(state, IntegratorConfig(timestep_fs=1.0), temperature_K=WORKLOADS[args.workload]["temperature"])
-    user_engine = B200Engine(ff, user_integrator, state, mode="graph", check_every=0)
+    user_engine = B200Engine(ff, user_integrator, state, mode="graph")      # the defaults, check points included
     user_engine.step()                 # untimed: captures the step graph (warm-ups restore the state)
     user_engine.flush()
     barrier()

@@ -262,7 +262,16 @@ class B200ForceField:
         self.data["edge_index"] = self.neighbours.edge_index[:, :self.num_edges]
 
     def set_cell(self, cell: torch.Tensor) -> None:
-        raise NotImplementedError("variable-cell runs are outside this force field's scope (fixed cell only)")
+        """The current float64 cell of a variable-cell run (``fastmace/model/forces.py:1351-1356``): the neighbour
+        list's shifts, the edge vectors and the volume the stress is divided by follow it from the next call on; the
+        candidates are rebuilt when the deformation-aware test fires (``needs_rebuild``). Needs ``compute_stress``
+        like the reference's. Host-side (the kernels take the cell by value): not for use inside a captured step."""
+        if not self._compute_stress:
+            raise RuntimeError("set_cell needs a force field built with compute_stress=True")
+        self.neighbours.set_cell(cell)
+        self.cell = self.neighbours.cell.copy()
+
+    reset_cell = set_cell
 
     def __call__(self, positions: torch.Tensor) -> ForceOutput:
         """Energy, forces (and stress) at float64 ``positions`` (N, 3) on the compacted edges. Graph-capturable."""

@@ -112,6 +112,7 @@ class Langevin:
         self._staging_events = [torch.cuda.Event() if dev.type == "cuda" else None for _ in range(2)]
         self._next = 0
         self._ahead: threading.Thread | None = None
+        self._queued: np.ndarray | None = None     # drawn rows that come before the generator's next draw (a resume)
         self.set_temperature(temperature_K)
         self.struct = _lib.LangevinStruct()
         s = self.struct
@@ -143,7 +144,14 @@ class Langevin:
     # ------------------------------------------------------------------ noise
     def _draw_into(self, generator: np.random.Generator, slot: int) -> None:
         rows = self._draw_rows[slot]
-        generator.standard_normal(out=self._staging[slot].numpy()[:rows])     # straight into the pinned buffer
+        out = self._staging[slot].numpy()[:rows]
+        taken = 0
+        if self._queued is not None:
+            taken = min(rows, len(self._queued))
+            out[:taken] = self._queued[:taken]
+            self._queued = self._queued[taken:] if taken < len(self._queued) else None
+        if taken < rows:
+            generator.standard_normal(out=out[taken:])        # straight into the pinned buffer
 
     def _start_draw_ahead(self, state: SimulationState) -> None:
         slot = self._next
@@ -182,6 +190,44 @@ class Langevin:
         if self.cursor_mode == "host":
             self.cursor_dev.fill_(int(state.rng.cursor))
         state.rng.cursor += 1
+
+    def noise_record(self, state: SimulationState) -> dict:
+        """The noise stream for a restart file (``fastmace/io/restart.py:1-20``: ``rng_state``, ``noise``,
+        ``noise_next``): every drawn row that no step has used yet -- the rest of the batch on the device, then the
+        batch drawn ahead on the host -- and the generator's state behind them, so that a resumed run reads the same
+        numbers in the same order. Device noise has no stream: the step counter is its whole state."""
+        if self.noise_mode == "device":
+            return dict(noise=np.zeros((0, 2, self.natoms, 3)), noise_next=0, rng_state="{}",
+                        noise_step=int(self.cursor_dev.item()))
+        import json
+        rows = [state.rng.batch[state.rng.cursor:self.rows].cpu().numpy()]
+        if self._ahead is not None:
+            self._ahead.join()
+            rows.append(self._staging[self._next].numpy()[:self._draw_rows[self._next]].copy())
+        if self._queued is not None:
+            rows.append(self._queued)
+        bit_state = state.rng.generator.bit_generator.state
+        return dict(noise=np.concatenate(rows), noise_next=0, rng_state=json.dumps(bit_state, default=int),
+                    noise_step=int(self.cursor_dev.item()))
+
+    def load_noise_record(self, state: SimulationState, record) -> None:
+        """Resume the stream of ``noise_record``: its rows are served first, then the generator continues."""
+        if self.noise_mode == "device":
+            self.cursor_dev.fill_(int(record["noise_step"]))
+            return
+        import json
+        if self._ahead is not None:
+            self._ahead.join()
+            self._ahead = None
+        bit_state = json.loads(str(record["rng_state"]))
+        generator = np.random.Generator(getattr(np.random, bit_state["bit_generator"])())
+        generator.bit_generator.state = bit_state
+        state.rng.generator = generator
+        rows = np.asarray(record["noise"], dtype=np.float64)[int(record["noise_next"]):]
+        self._queued = rows if len(rows) else None
+        self.rows = 0
+        state.rng.cursor = 0                         # used up: the next step refills, queued rows first
+        self._draw_rows = [min(FIRST_NOISE_ROWS, self.noise_batch)] * 2
 
     def upload_noise(self, state: SimulationState, rows: np.ndarray) -> None:
         """Replace the batch by ``rows`` (k <= noise_batch steps) and rewind the cursor: for tests and for

@@ -139,6 +139,7 @@ class CellListNeighbours:
         natoms = self.atom_capacity
         self.natoms = live
         total_bins = int(np.prod(self.nbins))
+        self._bins_allocated = total_bins
         self.wrapped = torch.zeros(natoms, 3, dtype=f64, device=dev)
         self.offsets = torch.zeros(natoms, 3, dtype=f64, device=dev)
         self.atom_bin = torch.zeros(natoms, dtype=i32, device=dev)
@@ -202,6 +203,11 @@ class CellListNeighbours:
 
         Synchronises once to read the candidate count (the reference's build does too, skin.py:466)."""
         positions = torch.as_tensor(positions, dtype=torch.float64, device=self.device).contiguous()
+        if self.variable_cell:
+            self._set_cell_constants()                # bins and padding pair of the cell as it is now
+            self.build_cell.copy_(self._cell_t.reshape(self.build_cell.shape))
+            if self.natoms is not None and int(np.prod(self.nbins)) > self._bins_allocated:
+                self._allocate_atoms(self.natoms)     # the cell grew by a bin
         if self.natoms is None:
             self._allocate_atoms(positions.shape[0])
         elif positions.shape[0] != self.natoms:
@@ -247,8 +253,38 @@ class CellListNeighbours:
         _lib.check(self.lib.fmb_nl_compact(ctypes.byref(self.struct), positions.data_ptr(), _lib.current_stream()),
                    "fmb_nl_compact")
 
+    def set_cell(self, cell) -> None:
+        """The current cell of a variable-cell run (``skin.py:679-683``): compaction, shifts and edge vectors follow
+        it at once, the candidates stay those of the build cell until the deformation-aware test asks for a rebuild.
+        Host-side here: the kernels take the cell by value, so a captured graph keeps the cell it was captured with
+        and an engine that captures must drop its graphs when the cell changes."""
+        cell = torch.as_tensor(cell, dtype=torch.float64).detach().cpu().numpy().reshape(3, 3)
+        self.variable_cell = True
+        self.cell = cell.copy()
+        inverse = np.linalg.inv(self.cell)
+        for k in range(9):
+            self.struct.cell[k] = float(self.cell.reshape(-1)[k])
+            self.struct.inverse[k] = float(inverse.reshape(-1)[k])
+        self._cell_t = torch.as_tensor(self.cell, dtype=torch.float64, device=self.device)
+
+    def _needs_rebuild_deformed(self, positions: torch.Tensor, fraction: float) -> torch.Tensor:
+        """The deformation-aware test (``skin.py:694-700``): displacements are measured in the build cell's
+        coordinates and the allowance shrinks with the smallest singular value of the deformation."""
+        build = self.build_cell.reshape(3, 3)
+        to_build = torch.linalg.solve(self._cell_t, build)                   # inverse(cell) @ build_cell
+        squared = ((positions @ to_build - self.reference_positions) ** 2).sum(dim=1)
+        strain = torch.linalg.solve(build, self._cell_t) - torch.eye(3, dtype=torch.float64, device=self.device)
+        lower = 1.0 - torch.sqrt((strain * strain).sum())
+        allowed = self.cutoff + self.skin - self.cutoff / torch.clamp(lower, min=1e-6)
+        flag = (2 * torch.sqrt(squared.max()) > fraction * allowed) | (lower <= 0)
+        self.rebuild_flag.copy_(flag.to(torch.int32))
+        return self.rebuild_flag
+
     def needs_rebuild(self, positions: torch.Tensor, fraction: float = 1.0) -> torch.Tensor:
-        """Device flag (int32 scalar, nonzero = rebuild): has any atom moved more than fraction * skin / 2?"""
+        """Device flag (int32 scalar, nonzero = rebuild): has any atom moved more than fraction * skin / 2?
+        After ``set_cell`` the deformation-aware form of the test applies."""
+        if self.variable_cell:
+            return self._needs_rebuild_deformed(positions, fraction)
         _lib.check(self.lib.fmb_nl_needs_rebuild(ctypes.byref(self.struct), positions.data_ptr(), float(fraction),
                                                  _lib.current_stream()), "fmb_nl_needs_rebuild")
         return self.rebuild_flag

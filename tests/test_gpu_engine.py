@@ -93,3 +93,79 @@ def test_captured_step_equals_checked_step_bitwise():
     for k in range(4):
         assert torch.equal(a[k], b[k]), k
     assert b[4]["captures"] == 1
+
+
+def test_overflow_in_graph_mode_is_restored_grown_and_redone():
+    """The candidate buffers are sized with no headroom at all, so a later rebuild of the hot crystal finds more
+    pairs than they hold. The captured step can only raise the device flag; the engine goes back to its last check
+    point, rebuilds host-driven, redoes the lost steps and captures again. The result equals the stage-by-stage
+    engine, whose rebuilds grow the buffers on the spot (reference: overflow before commit with redo,
+    fastmace/engine/graph.py:605-660,921-966; tested there by shrinking capacities on the host,
+    tests/cpu/test_overflow_commit.py:10-13)."""
+    from fastmace_b200.engine import B200Engine
+    from fastmace_b200.forcefield import B200ForceField
+    from fastmace_b200.langevin import IntegratorConfig, Langevin
+    from fastmace_b200.model import SMALL, init_weights
+    from fastmace_b200.neighbours import NeighbourConfig
+    from fastmace_b200.state import SimulationState
+    from fastmace_b200.structures import nacl
+    tight = NeighbourConfig(skin=0.2, capacity_headroom=1.0, edge_multiple=1)
+    weights = init_weights(SMALL, 0)
+
+    def run(mode):
+        s = nacl((3, 3, 3), 0.02, 3).with_velocities(2500.0, 4)
+        ff = B200ForceField(SMALL, weights, s.numbers, s.cell, compute_stress=True, neighbours=tight)
+        state = SimulationState.from_structure(s, ff.device, seed=5, compute_stress=True)
+        engine = B200Engine(ff, Langevin(state, IntegratorConfig(), temperature_K=2500.0), state, mode=mode,
+                            check_every=16)
+        engine.run(160)
+        return engine, state, ff
+
+    graph_engine, graph_state, graph_ff = run("graph")
+    checked_engine, checked_state, checked_ff = run("checked")
+    info = graph_engine.info()
+    print(f"overflows redone {info['overflows_redone']}, log {info['overflow_log'][:3]}, captures {info['captures']}, "
+          f"capacity {graph_ff.edge_capacity} vs {checked_ff.edge_capacity}, rebuilds {graph_ff.neighbours.rebuilds}")
+    assert info["overflows_redone"] >= 1 and info["captures"] >= 2
+    assert graph_state.step == checked_state.step == 160
+    assert torch.equal(graph_state.positions, checked_state.positions)
+    assert torch.equal(graph_state.velocities, checked_state.velocities)
+    assert torch.equal(graph_state.energy, checked_state.energy)
+
+
+def test_status_words_are_cleared_once_reported():
+    from fastmace_b200 import _lib
+    spec, weights, s, ff, state, it = _setup()
+    from fastmace_b200.engine import B200Engine
+    engine = B200Engine(ff, it, state, mode="graph", check_every=4)
+    engine.run(2)
+    ff.status.fill_(_lib.STATUS_NONFINITE)
+    engine.step()
+    with pytest.raises(_lib.Fmb200Error):
+        engine.flush()
+    assert int(ff.status.item()) == 0
+    engine.run(3)                                   # the run goes on and the next check is clean
+
+
+@pytest.mark.parametrize("mode", ["graph", "checked"])
+def test_resumed_run_continues_bit_for_bit(mode, tmp_path):
+    """Restart at a canonical point (fastmace/engine/graph.py:739-782, fastmace/io/restart.py:1-20): 30 steps, a
+    restart file, 40 more steps -- against a fresh engine that loads the file and runs the 40 steps."""
+    from fastmace_b200.engine import B200Engine
+    spec, weights, s, ff, state, it = _setup("small", temperature=1200.0, seed=6)
+    engine = B200Engine(ff, it, state, mode=mode, check_every=16)
+    engine.run(30)
+    path = str(tmp_path / "restart.npz")
+    engine.save_restart(path)
+    engine.run(40)
+    spec2, weights2, s2, ff2, state2, it2 = _setup("small", temperature=1200.0, seed=6)
+    resumed = B200Engine(ff2, it2, state2, mode=mode, check_every=16)
+    resumed.load_restart(path)
+    assert state2.step == 30
+    resumed.run(40)
+    assert state2.step == state.step == 70
+    assert torch.equal(state.positions, state2.positions) and torch.equal(state.velocities, state2.velocities)
+    assert torch.equal(state.energy, state2.energy) and torch.equal(state.forces, state2.forces)
+    record = dict(np.load(path))
+    assert {"positions", "momenta", "velocities", "cell", "rng_state", "noise", "noise_next", "forces", "energy",
+            "step", "masses", "species", "fastmace_restart", "plan"} <= set(record)

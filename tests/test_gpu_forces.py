@@ -258,3 +258,72 @@ def test_kernel_variants_in_subprocess(env, name, chunk):
                                  s_ref, s.natoms)
     assert de <= TOL_E and df <= TOL_F and ds <= TOL_S
     assert df <= 2e-4 * fscale + 1e-7
+
+
+def test_set_cell_follows_a_strained_cell():
+    """Variable cell (``ForceField.set_cell``, fastmace/model/forces.py:1351-1356): after a homogeneous strain of
+    cell and positions the force field gives what a force field built for the strained cell gives, first on the
+    candidates of the old cell (small strain, inside the skin), then after the rebuild the deformation-aware test
+    (fastmace/neighbors/skin.py:694-700) asks for."""
+    from fastmace_b200.forcefield import B200ForceField
+    spec, weights, s = _case("medium")
+    ff = B200ForceField(spec, weights, s.numbers, s.cell, compute_stress=True)
+    x0 = torch.tensor(s.positions, device="cuda")
+    ff.rebuild(x0); ff.compact(x0)
+    rebuilds = ff.neighbours.rebuilds
+    for scale, expect_rebuild in ((1.004, False), (1.03, True)):
+        strain = np.eye(3) * scale + np.array([[0, 0.002, 0], [0.002, 0, 0], [0, 0, 0]]) * (scale - 1) * 10
+        cell = s.cell @ strain
+        x = torch.tensor(s.positions @ strain, device="cuda")
+        ff.set_cell(torch.tensor(cell, device="cuda"))
+        flag = bool(ff.needs_rebuild(x).item())
+        # the reference's formula in NumPy
+        f_map = np.linalg.solve(cell, s.cell)
+        disp = np.sqrt((((s.positions @ strain) @ f_map - s.positions) ** 2).sum(1).max())
+        eps = np.linalg.solve(s.cell, cell) - np.eye(3)
+        lower = 1.0 - np.sqrt((eps * eps).sum())
+        allowed = spec.r_cut + 0.3 - spec.r_cut / max(lower, 1e-6)
+        assert flag == bool(2 * disp > allowed or lower <= 0) == expect_rebuild
+        if flag:
+            ff.rebuild(x)
+        ff.compact(x)
+        out = ff(x)
+        torch.cuda.synchronize()
+        ff.check_status()
+        fresh = B200ForceField(spec, weights, s.numbers, cell, compute_stress=True)
+        import dataclasses
+        e, f, st = fresh.evaluate(dataclasses.replace(s, positions=s.positions @ strain, cell=cell), stress=True)
+        assert abs(float(out.energy.item()) - e) / s.natoms <= TOL_E
+        assert np.abs(out.forces.double().cpu().numpy() - f).max() <= 2e-4 * np.abs(f).max() + 1e-7
+        assert np.abs(out.stress.double().cpu().numpy() - st).max() <= 2e-4 * np.abs(st).max() + 1e-9
+    assert ff.neighbours.rebuilds == rebuilds + 1
+
+
+def test_accuracy_gate_on_rattled_and_strained_copies():
+    """The reference's acceptance rule for a production path (SPEC.md:2038,2051-2066; planner/selfcheck.py:242-274):
+    error against float64 at most 3 x the float32 calculator's error, with floors. Production = the CUDA path; float64
+    reference and float32 yardstick = the CPU oracle in the two precisions."""
+    from fastmace_b200 import gate
+    from fastmace_b200.forcefield import B200ForceField
+    spec, weights, s = _case("medium")
+    fields = {}
+
+    def field_for(cell):
+        key = cell.tobytes()
+        if key not in fields:
+            fields[key] = B200ForceField(spec, weights, s.numbers, cell, compute_stress=True)
+        return fields[key]
+
+    def oracle(dtype):
+        def evaluate(positions, cell):
+            snd, rcv, u = nlo.build(positions, cell, spec.r_cut, 0.0)
+            e, f, st = mo.evaluate(spec, weights, positions, cell, s.numbers, snd, rcv, u, dtype=dtype)
+            return float(e), f.numpy(), st.numpy()
+        return evaluate
+
+    record = gate.run_gate(gate.force_field_evaluator(field_for, s.numbers), oracle(torch.float64), oracle(torch.float32),
+                           s.positions, s.cell, s.natoms, seed=3, stress=True)
+    for name, q in record["verdict"]["quantities"].items():
+        print(f"gate {name}: production {q['production']:.3e}  float32 yardstick {q['yardstick']:.3e}  "
+              f"ratio {q['ratio']}  limit {q['limit']:.3e}  {'passed' if q['passed'] else 'FAILED'}")
+    assert record["status"] == "passed" and len(record["rows"]) == 4

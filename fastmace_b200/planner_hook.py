@@ -81,12 +81,36 @@ def _numbers_cell(atoms):
     return numbers, cell
 
 
+def state_from_atoms(atoms, device, seed: int, compute_stress: bool):
+    """FastMACE's ``SimulationState`` for ``atoms``: ``SimulationState.from_atoms`` (``fastmace/state.py:340-378``)
+    where ASE is installed (it reads the constraints through ``ase.constraints``); without ASE the same fields from the
+    same accessors, for atoms objects without constraints."""
+    import numpy as np
+    import torch
+    from fastmace.state import RandomStream, SimulationState
+    try:
+        return SimulationState.from_atoms(atoms, device, seed, compute_stress=compute_stress)
+    except ModuleNotFoundError as error:
+        if error.name != "ase" and not str(error.name).startswith("ase."):
+            raise
+    if getattr(atoms, "constraints", None):
+        raise ValueError("constraints need ASE (SimulationState.from_atoms reads them through ase.constraints)")
+    f64 = dict(dtype=torch.float64, device=device)
+    positions = torch.tensor(np.asarray(atoms.get_positions()), **f64)
+    numbers, cell = _numbers_cell(atoms)
+    return SimulationState(
+        positions=positions, velocities=torch.tensor(np.asarray(atoms.get_velocities()), **f64),
+        masses=torch.tensor(np.asarray(atoms.get_masses())[:, None], **f64), cell=torch.tensor(cell, **f64),
+        species=torch.tensor(numbers, dtype=torch.int64, device=device), forces=torch.zeros_like(positions),
+        energy=torch.zeros(1, **f64), stress=torch.zeros((3, 3), **f64) if compute_stress else None,
+        rng=RandomStream(np.random.default_rng(seed)), pbc=tuple(bool(p) for p in getattr(atoms, "pbc", (True,) * 3)))
+
+
 def build_b200(planner, plan, force_field, atoms, *, temperature_K=None):
     """The engine of a ``tier="b200"`` plan, modelled on ``MinimalPlanner.build_reference``
     (``planner/minimal.py:1260-1286``): the CUDA force field and Langevin stages of this package on FastMACE's own
     ``SimulationState`` and ``GraphEngine``."""
     from fastmace.engine.graph import GraphEngine
-    from fastmace.state import SimulationState
 
     from .forcefield import B200ForceField
     from .langevin import IntegratorConfig, Langevin
@@ -109,7 +133,7 @@ def build_b200(planner, plan, force_field, atoms, *, temperature_K=None):
     field = B200ForceField(spec, weights, numbers, cell, compute_stress=stress, device=plan.engine.device,
                            neighbours=neighbours)
     seed = int(getattr(plan.integrator, "seed", 0) or 0)
-    state = SimulationState.from_atoms(atoms, field.device, seed, compute_stress=stress)
+    state = state_from_atoms(atoms, field.device, seed, stress)
     field.rebuild(state.positions)
     it = plan.integrator
     config = IntegratorConfig() if it is None else IntegratorConfig(
@@ -189,5 +213,5 @@ def unregister() -> None:
         _registered.clear()
 
 
-__all__ = ["TIER", "MODE", "register", "unregister", "build_b200", "extend_literals", "spec_of", "weights_of",
+__all__ = ["TIER", "MODE", "register", "unregister", "build_b200", "state_from_atoms", "extend_literals", "spec_of", "weights_of",
            "make_planner_class"]

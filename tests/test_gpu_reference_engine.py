@@ -27,12 +27,12 @@ def test_reference_graph_engine_steps_the_drop_in():
     from fastmace.config import EngineConfig
     from fastmace.engine.constraints import ProcessRecord
     from fastmace.engine.graph import GraphEngine
-    from fastmace.state import SimulationState
     from fastmace_b200.engine import B200Engine
+    from fastmace_b200.planner_hook import state_from_atoms
     from fastmace_b200.state import SimulationState as OwnState
 
     s, ff, IntegratorConfig, Langevin, temperature, cursor = _parts()
-    state = SimulationState.from_atoms(AtomsView(s), ff.device, 11, compute_stress=True)
+    state = state_from_atoms(AtomsView(s), ff.device, 11, True)
     ff.rebuild(state.positions)
     integrator = Langevin(state, IntegratorConfig(), temperature_K=temperature, cursor=cursor)
     config = EngineConfig(device=str(ff.device), pipelined="off", async_output="off", compile_mode="none",

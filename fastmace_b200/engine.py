@@ -56,6 +56,7 @@ class B200Engine:
         self.overflows_redone = 0
         self.overflow_log = []
         self._committed = None
+        self._commit_pending = False
         self.stream = torch.cuda.Stream(device=force_field.device)
         ff = force_field
         x = state.positions
@@ -68,7 +69,9 @@ class B200Engine:
 
     # ------------------------------------------------------------------ committed point, overflow redo
     def _commit(self) -> None:
-        """The state as it is now becomes the point an overflow goes back to (device copies, stream-ordered)."""
+        """The state as it is now becomes the point an overflow goes back to (device copies, stream-ordered). Taken
+        after ``prepare_step`` of the step about to run, so that a noise refill at this step is part of the point: the
+        redo finds the rows of the stretch still in the batch and the cursors where they were."""
         st, it = self.state, self.integrator
         tensors = dict(x=st.positions, v=st.velocities, f=st.forces, e=st.energy, cursor=it.cursor_dev)
         if st.stress is not None:
@@ -78,8 +81,9 @@ class B200Engine:
         else:
             for k, v in tensors.items():
                 self._committed[k].copy_(v)
-        self._committed_host = (st.step, st.rng.cursor)
+        self._committed_host = (st.step, st.rng.cursor - 1)      # prepare_step has counted the step about to run
         self.steps_since_check = 0
+        self._commit_pending = False
 
     def _check(self) -> None:
         """Check point of graph mode: synchronise, read the status words, commit or redo."""
@@ -95,7 +99,8 @@ class B200Engine:
         finally:
             ff.status.zero_()                # reported once: a later check reads what happened after this one
             ff.neighbours.status.zero_()
-        self._commit()
+        self.steps_since_check = 0
+        self._commit_pending = True          # the next step commits, behind its prepare_step
 
     def _redo_from_committed(self) -> None:
         st, it, ff = self.state, self.integrator, self.force_field
@@ -120,7 +125,8 @@ class B200Engine:
             self._checked_step()
         torch.cuda.synchronize(ff.device)
         ff.check_status()
-        self._commit()
+        self.steps_since_check = 0
+        self._commit_pending = True
 
     # ------------------------------------------------------------------ stages
     def _force_stage(self) -> None:
@@ -193,9 +199,9 @@ class B200Engine:
             self._check()                    # before the rows of the stretch since the last check point are replaced
         if self.graph is None:
             self._capture()
-            if self.check_every and self._committed is None:
-                self._commit()
         it.prepare_step(st)
+        if self.check_every and (self._commit_pending or self._committed is None):
+            self._commit()
         self.graph.replay()
         self.steps_since_check += 1
         st.step += 1
@@ -231,8 +237,7 @@ class B200Engine:
             self._force_stage()
             self.integrator.start(st)
         torch.cuda.synchronize(ff.device)
-        if self.mode == "graph" and self.check_every and self.graph is not None:
-            self._commit()
+        self._commit_pending = True
         self.canonical_points = getattr(self, "canonical_points", 0) + 1
 
     def restart_record(self) -> dict:

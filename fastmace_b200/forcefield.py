@@ -326,12 +326,11 @@ class B200ForceField:
     def buffers(self):
         """Persistent device buffers under the names the reference's registry has policies for
         (``fastmace/engine/registry.py:91-139``): everything a rebuild makes as ``neighbours.*`` (the status words
-        included: they are sticky until a rebuild clears them) and the cell. The work buffers of a force call are
-        written before they are read in every call and carry nothing across steps."""
+        included: they are sticky until a rebuild clears them; the cell is ``neighbours.build_cell``). The work buffers
+        of a force call are written before they are read in every call and carry nothing across steps."""
         out = {f"neighbours.{name}": value for name, value in self.neighbours.buffers().items()}
         out["neighbours.status"] = self.neighbours.status
         out["neighbours.force_status"] = self.status
-        out["cell"] = self.neighbours.build_cell
         return out
 
     def info(self):

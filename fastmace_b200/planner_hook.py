@@ -141,8 +141,12 @@ def build_b200(planner, plan, force_field, atoms, *, temperature_K=None):
         fixcm_projection=str(getattr(it, "fixcm_projection", "mass_weighted") or "mass_weighted"),
         noise_batch=int(it.noise_batch))
     integrator = Langevin(state, config, temperature_K=float(temperature_K), cursor="host")
-    engine = GraphEngine(plan.engine, field, integrator, state, neighbours=plan.neighbours,
-                         constraints=planner.process if planner is not None else None)
+    # GraphEngine's capture path prepares mace-torch's modules for capture (fastmace/_patches.py, from graph.py:1331);
+    # in an installation without that package the stages run uncaptured on padded edge counts
+    import importlib.util
+    capture = None if importlib.util.find_spec("mace") is not None else False
+    engine = GraphEngine(plan.engine, field, integrator, state, neighbours=plan.neighbours, capture=capture,
+                         pad_edges=True, constraints=planner.process if planner is not None else None)
     engine.plan = plan
     return engine
 

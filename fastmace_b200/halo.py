@@ -457,6 +457,7 @@ class DomainSimulation:
         self.ranks = [HaloRank(self, r) for r in self.rank_ids]
         self.step_count = 0
         self.repartitions = 0
+        self.repartition_seconds = 0.0
         self.energy = torch.zeros(1, **f64)
         self.stress = torch.zeros(3, 3, **f64)
         positions = torch.tensor(np.asarray(structure.positions), **f64)
@@ -482,12 +483,17 @@ class DomainSimulation:
         return rows[:, 0:3].contiguous(), rows[:, 3:6].contiguous(), rows[:, 6:9].contiguous()
 
     def _repartition(self, positions: torch.Tensor, velocities: torch.Tensor, random_kick=None) -> None:
+        import time
+        torch.cuda.synchronize(self.device)
+        t0 = time.perf_counter()
         geometry = _Geometry(self.plan, positions)
         for r in self.ranks:
             part = partition(self.plan, positions, r.rank, geometry)
             if isinstance(self.transport, DistributedTransport):
                 self.transport.check_counts(part.send_counts, part.recv_counts, self.device)
             r.set_partition(part, positions, velocities, random_kick)
+        torch.cuda.synchronize(self.device)
+        self.repartition_seconds += time.perf_counter() - t0
         self.repartitions += 1
 
     # ------------------------------------------------------------------ exchanges
@@ -583,7 +589,8 @@ class DomainSimulation:
         r = self.ranks[0]
         return {"engine": "fmb200-halo", "ranks": self.plan.n_ranks, "bricks": self.plan.grid, "rank": r.rank,
                 "owned_atoms": r.part.n_owned, "local_atoms": r.part.n_local, "halo_rows_sent": len(r.part.send_index),
-                "repartitions": self.repartitions, "steps": self.step_count,
+                "repartitions": self.repartitions, "repartition_seconds": round(self.repartition_seconds, 4),
+                "steps": self.step_count,
                 "local_edges": int(r.ff.edge_count.item()) if r.active else 0,
                 "streaming_interactions": self.spec.num_interactions, "sort_receivers": True,
                 "owned_all": [x.part.n_owned for x in self.ranks], "local_all": [x.part.n_local for x in self.ranks]}

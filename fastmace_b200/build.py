@@ -41,9 +41,7 @@ def _compile(source: str, verbose: bool) -> str:
     obj = os.path.join(BUILD, os.path.basename(source)[:-3] + ".o")
     if os.path.exists(obj) and os.path.getmtime(obj) > max(os.path.getmtime(source), _newest_header()):
         return obj
-    # FMB_NVCC_FLAGS: extra compiler flags for experiments (e.g. -DFMB_FUSED_PROFILE)
-    extra = os.environ.get("FMB_NVCC_FLAGS", "").split()
-    cmd = [_nvcc(), *ARCH, *FLAGS, *extra, "-c", source, "-o", obj]
+    cmd = [_nvcc(), *ARCH, *FLAGS, "-c", source, "-o", obj]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     result = subprocess.run(cmd, capture_output=True, text=True)

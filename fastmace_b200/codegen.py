@@ -290,8 +290,8 @@ PATHS_OUT = os.path.join(HERE, "csrc", "generated", "tp_paths_generated.cuh")
 
 
 def _emit_paths(lin: int) -> str:
-    """One ``TpPath<LIN, P>`` per path: shape constants and the forward / adjoint of that path alone, for the kernels
-    that take the radial weights of one path at a time from tensor memory."""
+    """One ``TpPath<LIN, P>`` per path: shape constants and the forward of that path alone, for the kernel that takes
+    the radial weights of one path at a time from tensor memory."""
     paths = so3.tp_paths(lin)
     slots, blocks = message_slots(paths)
     out = [f"// ---- node l_max = {lin}"]
@@ -303,7 +303,6 @@ def _emit_paths(lin: int) -> str:
         seg = slots[(p, 0)] - base
         first_for_in = l_in not in seen_in
         seen_in.add(l_in)
-        sign = -1.0 if l_edge % 2 else 1.0
         out += [f"template <> struct TpPath<{lin}, {p}> {{  // {l_in} x {l_edge} -> {l_out}",
                 f"    static constexpr int kNin = {n_in}, kNe = {n_e}, kNo = {n_o};",
                 f"    static constexpr int kInOff = {path['in_off']}, kEdgeOff = {path['edge_off']};",
@@ -312,38 +311,11 @@ def _emit_paths(lin: int) -> str:
                 f"    static __device__ __forceinline__ void forward(const float (&x)[{n_in}], const float (&Y)[{n_e}], "
                 f"float w, float (&acc)[{n_o}]) {{"]
         by_out: dict[int, list] = {}
-        by_edge: dict[int, list] = {}
-        by_in: dict[int, list] = {}
         for mi, me, mo, c in path["terms"]:
             by_out.setdefault(mo, []).append((mi, me, c))
-            by_edge.setdefault(me, []).append((mi, mo, c))
-            by_in.setdefault(mi, []).append((me, mo, c))
         for mo, terms in sorted(by_out.items()):
             expr = " + ".join(f"{_lit(c)} * x[{mi}] * Y[{me}]" for mi, me, c in terms)
             out.append(f"        acc[{mo}] = fmaf(w, {expr}, acc[{mo}]);")
-        out += ["    }",
-                "    // edge as stored (sender features xj, receiver gradient ga) plus its mirror (own features xa, the",
-                "    // sender's gradient gj, harmonics with (-1)^l): part[0 .. kNe) = dE/dY of this path, part[kNe] = dE/dr",
-                f"    static __device__ __forceinline__ void backward(const float (&xj)[{n_in}], const float (&ga)[{n_o}], "
-                f"const float (&xa)[{n_in}], const float (&gj)[{n_o}], const float (&Y)[{n_e}], float w, float wp, "
-                f"float (&part)[{n_e + 1}], float (&dx)[{n_in}]) {{",
-                f"        constexpr float sg = {_lit(sign)};",
-                "        float dw = 0.0f;"]
-        for me in range(n_e):
-            terms = by_edge.get(me, [])
-            if not terms:
-                out.append(f"        part[{me}] = 0.0f;")
-                continue
-            e1 = " + ".join(f"{_lit(c)} * xj[{mi}] * ga[{mo}]" for mi, mo, c in terms)
-            e2 = " + ".join(f"{_lit(c)} * xa[{mi}] * gj[{mo}]" for mi, mo, c in terms)
-            out.append(f"        {{ const float s = ({e1}) + sg * ({e2}); dw = fmaf(s, Y[{me}], dw); part[{me}] = w * s; }}")
-        out.append(f"        part[{n_e}] = wp * dw;")
-        for mi in range(n_in):
-            terms = by_in.get(mi, [])
-            if not terms:
-                continue
-            expr = " + ".join(f"{_lit(c)} * Y[{me}] * gj[{mo}]" for me, mo, c in terms)
-            out.append(f"        dx[{mi}] = fmaf(w * sg, {expr}, dx[{mi}]);")
         out += ["    }", "};"]
     out.append(f"#define FMB_FOR_EACH_PATH_{lin}(X) " + " ".join(f"X({p})" for p in range(len(paths))))
     out.append("")

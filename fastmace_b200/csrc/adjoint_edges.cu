@@ -356,24 +356,11 @@ int tp_adjoint_edges(const EdgeAdjointArgs& t, cudaStream_t stream) {
             t.tp_w, t.tangent_offset, t.d_mid, t.dxe,
             reinterpret_cast<float4*>(t.qe));
     } else if (t.lin == 1) {
-        static const int occupancy = [] {
-            const char* env = std::getenv("FMB_ADJOINT_OCCUPANCY");      // CTAs per SM the compiler targets (tuning knob)
-            return env ? std::atoi(env) : 4;
-        }();
-#define FMB_ADJ1(MINB_)                                                                                                \
-    {                                                                                                                  \
-        static const int grid_cap = grid_for((const void*)k_tp_adjoint_edges<1, MINB_>, 1 << 30, kC, 0);               \
-        k_tp_adjoint_edges<1, MINB_><<<t.n_rows < grid_cap ? t.n_rows : grid_cap, kC, 0, stream>>>(                    \
-            t.n_atoms, t.n_rows, t.n_valid, t.chunk_e0, t.chunk_edges, t.count, t.row_ptr, t.senders, t.x, t.edge_sh,   \
-            t.edge_vec, t.tp_w, t.tangent_offset, t.d_mid, t.dxe,                                                       \
-            reinterpret_cast<float4*>(t.qe));                                                                          \
-    }
-        if (occupancy >= 6) FMB_ADJ1(6)
-        else if (occupancy == 5) FMB_ADJ1(5)
-        else if (occupancy == 4) FMB_ADJ1(4)
-        else if (occupancy == 3) FMB_ADJ1(3)
-        else FMB_ADJ1(2)
-#undef FMB_ADJ1
+        // four CTAs per SM (127 registers): measured best on the 1,944-atom cell among 2 .. 6
+        static const int grid_cap = grid_for((const void*)k_tp_adjoint_edges<1, 4>, 1 << 30, kC, 0);
+        k_tp_adjoint_edges<1, 4><<<t.n_rows < grid_cap ? t.n_rows : grid_cap, kC, 0, stream>>>(
+            t.n_atoms, t.n_rows, t.n_valid, t.chunk_e0, t.chunk_edges, t.count, t.row_ptr, t.senders, t.x, t.edge_sh,
+            t.edge_vec, t.tp_w, t.tangent_offset, t.d_mid, t.dxe, reinterpret_cast<float4*>(t.qe));
     } else if (t.lin == 2) {
         static const int grid_cap = grid_for((const void*)k_tp_adjoint_edges<2, 2>, 1 << 30, kC, 0);
         k_tp_adjoint_edges<2, 2><<<t.n_rows < grid_cap ? t.n_rows : grid_cap, kC, 0, stream>>>(

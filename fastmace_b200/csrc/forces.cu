@@ -77,13 +77,7 @@ SideStream* side_stream(cudaStream_t main) {
     return &s;
 }
 
-bool overlap_enabled() {
-    static const bool on = [] {
-        const char* env = std::getenv("FMB_OVERLAP");        // FMB_OVERLAP=0: everything on the caller's stream
-        return !(env && env[0] == '0');
-    }();
-    return on && !g_timer.on;       // the stage timers attribute time on one stream
-}
+bool overlap_enabled() { return !g_timer.on; }       // the stage timers attribute time on one stream
 
 inline int dim_of(int lmax) { return (lmax + 1) * (lmax + 1); }
 
@@ -139,16 +133,8 @@ bool keeps_forward_weights(const Ctx& c, int layer) {
 
 // Per-edge hand-over adjoint (adjoint_edges.cu) instead of the mirror evaluation: the buffers exist and the first
 // interaction is in its reassociated form (its per-edge kernel closes the chain).
-bool fused_adjoint_selected() {
-    static const bool on = [] {
-        const char* env = std::getenv("FMB_FUSED_ADJOINT");
-        return env && env[0] == '1';
-    }();
-    return on;
-}
-
 bool edge_local_adjoint(const Ctx& c) {
-    return !fused_adjoint_selected() && c.w->mirror && c.w->edge_q && c.w->edge_dx && c.m->n_layers == 2 && c.m->layer[0].first[0] != nullptr;
+    return c.w->mirror && c.w->edge_q && c.w->edge_dx && c.m->n_layers == 2 && c.m->layer[0].first[0] != nullptr;
 }
 
 float* h_of(const Ctx& c, int layer) {
@@ -463,24 +449,7 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
         return FMB_OK;
     }
     FMB_REQUIRE(!c.exchange, "halo-exchange mode needs the per-edge hand-over buffers (mirror, edge_q, edge_dx)");
-    bool fused = false;
-    // The fused adjoint executes more instructions per edge than the edge-major kernels (one reduction over channels per
-    // path) and measures slower on the 1,944-atom cell; FMB_FUSED_ADJOINT=1 selects it (it needs no weight buffer).
-    if (fused_adjoint_selected() && layer > 0 && L.rad_img && tensor_cores_enabled()) {
-        FusedArgs f{};
-        f.lin = L.l_in_max; f.n_rows = c.n0; f.n_valid = rows; f.fresh_from = 0; f.first_layer_of_pass = first_layer_of_pass;
-        f.row_ptr = c.nl->edge_row_ptr; f.senders = c.nl->edge_index; f.x = c.w->x; f.edge_sh = c.w->edge_sh;
-        f.edge_vec = c.w->edge_vec; f.hidden = hidden_of(c, layer, 0); f.hidden_tangent = hidden_of(c, layer, 1);
-        f.image = L.rad_img; f.d_mid = c.w->d_mid; f.d_x = c.w->d_x; f.force_acc = c.w->force_acc;
-        f.atom_virial = c.w->atom_virial; f.error_word = c.w->status;
-        StageScope scope(c.stream, kStTpBwd1);
-        const int rc = tp_fused_backward(f, c.stream);
-        if (rc != FMB_ERR_UNSUPPORTED) {
-            if (rc) return rc;
-            fused = true;
-        }
-    }
-    for (int k = 0; k < c.n_chunks && !fused; ++k) {
+    for (int k = 0; k < c.n_chunks; ++k) {
         const long long e0 = (long long)k * c.chunk;
         if (c.radial_ready && layer > 0) {
             FMB_CUDA_CHECK(cudaStreamWaitEvent(c.stream, c.radial_ready, 0));
@@ -573,13 +542,9 @@ int fork_radial(Ctx& c, int which) {
     const int layer = c.m->n_layers - 1;
     if (!overlap_enabled() || !keeps_forward_weights(c, layer) || !c.m->layer[layer].rad_img || !tensor_cores_enabled())
         return FMB_OK;
-    if (fused_adjoint_selected()) return FMB_OK;
     SideStream* side = side_stream(c.stream);
     if (!side) return FMB_OK;
-    static const int side_ctas = [] {
-        const char* env = std::getenv("FMB_SIDE_CTAS");
-        return env ? std::atoi(env) : 120;
-    }();
+    constexpr int side_ctas = 120;      // the SMs it leaves free serve the node kernels beside it (measured best of 64 .. 148)
     FMB_CUDA_CHECK(cudaEventRecord(side->fork, c.stream));
     FMB_CUDA_CHECK(cudaStreamWaitEvent(side->stream, side->fork, 0));
     FMB_TRY(radial_weights(c, layer, 0, which, which, edge_limits(c) + (which == 0 ? 1 : 0), side->stream, side_ctas));

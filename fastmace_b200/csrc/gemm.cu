@@ -111,26 +111,15 @@ int gemm_simt(const GemmArgs& g, cudaStream_t stream) {
     return FMB_OK;
 }
 
-static int gemm_mode() {
-    static const int mode = [] {
-        const char* env = std::getenv("FMB_GEMM");
-        return (env && std::strcmp(env, "simt") == 0) ? 0 : 1;
-    }();
-    return mode;
-}
-
-bool tensor_cores_enabled() { return gemm_mode() == 1; }
+bool tensor_cores_enabled() { return true; }
 
 int gemm_batch(const GemmArgs* list, int count, cudaStream_t stream) {
     int done = 0;
     while (done < count) {
         const int take = count - done < 8 ? count - done : 8;
-        int rc = FMB_ERR_UNSUPPORTED;
-        if (gemm_mode() == 1) {
-            rc = gemm_ws_batch(list + done, take, stream);
-            if (rc == FMB_ERR_UNSUPPORTED) rc = gemm_tc_batch(list + done, take, stream);
-        }
-        if (rc == FMB_ERR_UNSUPPORTED) {
+        int rc = gemm_ws_batch(list + done, take, stream);
+        if (rc == FMB_ERR_UNSUPPORTED) rc = gemm_tc_batch(list + done, take, stream);
+        if (rc == FMB_ERR_UNSUPPORTED) {      // a shape neither tensor-core kernel takes
             for (int q = 0; q < take; ++q) {
                 rc = gemm_simt(list[done + q], stream);
                 if (rc) return rc;
@@ -144,11 +133,8 @@ int gemm_batch(const GemmArgs* list, int count, cudaStream_t stream) {
 }
 
 int gemm(const GemmArgs& g, cudaStream_t stream) {
-    const int mode = gemm_mode();
-    if (mode == 1) {
-        const int rc = gemm_tc(g, stream);
-        if (rc != FMB_ERR_UNSUPPORTED) return rc;
-    }
+    const int rc = gemm_tc(g, stream);
+    if (rc != FMB_ERR_UNSUPPORTED) return rc;
     return gemm_simt(g, stream);
 }
 

@@ -493,11 +493,6 @@ int gemm_tc_batch(const GemmArgs* list, int count, cudaStream_t stream) {
         if (wants_swap(list[q]) != swap) return FMB_ERR_UNSUPPORTED;
         if (list[q].n % 128 != 0) wide = false;
     }
-    static const int forced_tn = [] {
-        const char* env = std::getenv("FMB_GEMM_TN");      // 64: narrow tiles, two CTAs per SM (tuning knob)
-        return env ? std::atoi(env) : 0;
-    }();
-    if (forced_tn == 64) wide = false;
     const int tn = swap ? 256 : (wide ? 128 : 64);
     long long row_tiles_total = 0;
     for (int q = 0; q < count; ++q) row_tiles_total += ceil_div(std::max(list[q].m, 0), TM);

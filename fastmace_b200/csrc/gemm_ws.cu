@@ -301,13 +301,10 @@ int gemm_ws_batch(const GemmArgs* list, int count, cudaStream_t stream) {
         if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
         return sms;
     }();
-    static const int wide_mode = [] {
-        const char* env = std::getenv("FMB_GEMM_WIDE");        // 0: never pair column tiles, 2: always (tuning knob)
-        return env ? std::atoi(env) : 1;
-    }();
+    // launches of more than one wave pair adjacent column tiles (128 x 256): half the CTAs and half the A traffic
     int narrow_tiles = 0;
     for (int q = 0; q < count; ++q) narrow_tiles += ceil_div(std::max(list[q].m, 0), 128) * (list[q].n / 128);
-    batch.wide = wide_mode == 2 || (wide_mode == 1 && narrow_tiles > sm_count) ? 1 : 0;
+    batch.wide = narrow_tiles > sm_count ? 1 : 0;
     int tiles = 0;
     for (int q = 0; q < count; ++q) {
         const GemmArgs& g = list[q];

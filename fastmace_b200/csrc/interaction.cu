@@ -490,13 +490,6 @@ int persistent_grid(const void* kernel, int n_atoms) {
 }  // namespace
 
 // FMB_TP_STREAM=0 keeps the direct-load forward kernel (A/B tests)
-static bool stream_weights() {
-    static const bool on = [] {
-        const char* env = std::getenv("FMB_TP_STREAM");
-        return !(env && env[0] == '0');
-    }();
-    return on;
-}
 
 int tp_forward_launch(const TpArgs& t, cudaStream_t stream) {
     if (t.n_rows <= 0) return FMB_OK;
@@ -529,7 +522,7 @@ int tp_forward_launch(const TpArgs& t, cudaStream_t stream) {
         FMB_FWD(0, true)
     } else if (t.lin == 0) {
         FMB_FWD(0, false)
-    } else if (t.whole_list && (t.lin == 1 || t.lin == 2) && stream_weights()) {
+    } else if (t.whole_list && (t.lin == 1 || t.lin == 2)) {
         if (t.lin == 1) FMB_FWD_STREAM(1) else FMB_FWD_STREAM(2)
     } else if (t.lin == 1) {
         FMB_FWD(1, false)
@@ -565,13 +558,7 @@ int tp_backward_launch(const TpArgs& t, cudaStream_t stream) {
         // CTAs per SM the compiler targets (FMB_TP_OCCUPANCY = 2, 3 or 4; 168 / 128 registers at 3 / 4). Measured on
         // the 1,944-atom cell: 0.47 / 0.51 / 0.56 ms -- the kernel is bound by the 37 KB per edge it pulls through L2
         // (the mirror receiver's 20 KB gradient row, 10 KB of radial weights), not by issue slots, so 2 stays.
-        static const int occupancy = [] {
-            const char* env = std::getenv("FMB_TP_OCCUPANCY");
-            return env ? std::atoi(env) : 2;
-        }();
-        if (occupancy >= 4) FMB_BWD_OCC(1, false, true, 4)
-        else if (occupancy == 3) FMB_BWD_OCC(1, false, true, 3)
-        else FMB_BWD_OCC(1, false, true, 2)
+        FMB_BWD_OCC(1, false, true, 2)
     } else if (t.lin == 2) {
         FMB_BWD(2, false, true)
     } else {

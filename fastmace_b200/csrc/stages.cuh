@@ -62,7 +62,6 @@ struct FusedArgs {
 };
 // FMB_ERR_UNSUPPORTED when the fused kernels do not apply (no weight image, lin outside 1..2)
 int tp_fused_forward(const FusedArgs& f, cudaStream_t stream);
-int tp_fused_backward(const FusedArgs& f, cudaStream_t stream);
 
 // Per-edge radial weights (or their d/dr) [rows][n_paths * 128] = hidden [rows][64] x last radial layer, through the
 // fused kernels' tensor-core pipeline (tp_fused.cu); FMB_ERR_UNSUPPORTED without the weight image.

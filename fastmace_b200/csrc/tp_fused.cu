@@ -2,7 +2,9 @@
 // per-edge weights W[e, path, channel] = hidden[e, :] . W4[:, path, channel] are produced by the tensor cores straight
 // into tensor memory and consumed from there, so the [edges][paths * 128] weight matrix (5 KB per edge for ten paths)
 // never exists in HBM. Replaces conv_tp + scatter_sum and the last radial linear (fastmace/rewrites/generic/
-// modules.py:485-486) and, for the adjoint, autograd through both.
+// modules.py:485-486). Forward only: the adjoint of these interactions is the per-edge hand-over kernel
+// (adjoint_edges.cu) or, for lists too large for its buffers, the mirror evaluation (interaction.cu); a fused
+// adjoint of this shape needs one channel reduction per path and measured three times slower than the former.
 //
 // One persistent CTA per SM: 8 consumer warps (two groups of 128 threads, thread = channel = TMEM lane) and one warp
 // that feeds the tensor cores. A work item is a pair of receivers, one per consumer group; a round covers up to 64
@@ -10,14 +12,12 @@
 // them as the N-side operand (K-major, 128-byte swizzle); then, path by path,
 //   * bulk copies bring the path's 128 x 64 block of W4 (pre-split and pre-swizzled at packing time, 16 KB pieces)
 //     through a ring of shared-memory stages,
-//   * one thread issues the 3xTF32 MMAs (M = 128 channels, N = 128 edge columns, or 256 with the d/dr columns for the
-//     adjoint, K = 64) into one of two TMEM accumulators and commits to mbarriers,
+//   * one thread issues the 3xTF32 MMAs (M = 128 channels, N = 128 edge columns, K = 64) into one of two TMEM
+//     accumulators and commits to mbarriers,
 //   * each consumer thread reads its lane (channel) four edge columns at a time and applies the path's coupling
 //     (generated bodies, tp_paths_generated.cuh) while the tensor cores work on the next path.
-// Forward: the message row of a receiver is accumulated in registers per path and stored once per round. Adjoint:
-// every edge is evaluated together with its mirror (same radial weights, harmonics with (-1)^l), the per-edge
-// dE/dY and dE/dr are reduced over channels per path (transpose-reduce) into shared memory and turned into the
-// force / virial of the CTA's own atoms; nothing is scattered and there are no atomics.
+// The message row of a receiver is accumulated in registers per path and stored once per round; nothing is scattered
+// and there are no atomics.
 //
 // Every wait is bounded (tc::mbar_wait): if one gives up, the CTA raises FMB_STATUS_TENSOR_TIMEOUT, stops waiting
 // everywhere, runs to its end and frees its tensor memory.
@@ -36,35 +36,27 @@ namespace {
 
 using namespace tc;
 
-// -DFMB_FUSED_PROFILE: CTA 0 prints where its tensor-core thread and its first consumer thread spent their cycles
-#ifdef FMB_FUSED_PROFILE
-#define FMB_T0() const long long t0__ = clock64()
-#define FMB_T1(slot) prof[slot] += clock64() - t0__
-#else
-#define FMB_T0()
-#define FMB_T1(slot)
-#endif
 
 constexpr int kFusedThreads = 288;        // 8 consumer warps + the tensor-core warp
 constexpr int kStageBytes = 16384;        // one (hi or lo) x (K half) piece of a path's weight block: 128 rows x 32
 constexpr int kRoundEdges = 64;           // edge columns per consumer group and round
 constexpr unsigned kSpin = 1u << 20;
 
-template <bool BWD> struct FusedShape {
-    static constexpr int kTN = BWD ? 256 : 128;              // MMA N: edge columns (+ their d/dr twins)
+struct FusedShape {
+    static constexpr int kTN = 128;              // MMA N: edge columns (+ their d/dr twins)
     static constexpr int kBTile = kTN * 256;                  // bytes of the hi (or lo) N-side operand
-    static constexpr int kStages = BWD ? 3 : 8;
+    static constexpr int kStages = 8;
     static constexpr int kRing = 2 * kBTile;
     static constexpr int kYsh = kRing + kStages * kStageBytes;           // harmonics of the round's edges [128][16]
     static constexpr int kVec = kYsh + 128 * 64;                         // unit vector and length [128] float4
     static constexpr int kSnd = kVec + 128 * 16;                         // senders [128]
     static constexpr int kRed = kSnd + 128 * 4;                          // adjoint: [128 edges][4 warps][17]
-    static constexpr int kScratch = kRed + (BWD ? 128 * 4 * 17 * 4 : 0); // force / virial hand-over between warps
+    static constexpr int kScratch = kRed + 0; // force / virial hand-over between warps
     static constexpr int kBars = kScratch + 256;
     static constexpr int kMisc = kBars + 256;
     static constexpr int kBytes = kMisc + 16 + 1024;                     // + slack to align the base to 1024 bytes
 };
-static_assert(FusedShape<true>::kBytes <= 232448 && FusedShape<false>::kBytes <= 232448, "shared memory budget");
+static_assert(FusedShape::kBytes <= 232448, "shared memory budget");
 
 // barrier slots
 constexpr int kBarFull = 0, kBarEmpty = 8, kBarTFull = 16, kBarTEmpty = 18, kBarB = 20;
@@ -179,19 +171,6 @@ __device__ __forceinline__ void gather_x(const float* __restrict__ x, const int*
     }
 }
 
-template <typename TP, int MID, int EB>
-__device__ __forceinline__ void gather_g(const float* __restrict__ d_mid, const int* __restrict__ snd_col, int c,
-                                         int n_valid, float (&gn)[EB][TP::kNo]) {
-#pragma unroll
-    for (int q = 0; q < EB; ++q) {
-        const long long j = snd_col[q];
-        const bool has = j < n_valid;
-#pragma unroll
-        for (int m = 0; m < TP::kNo; ++m)
-            gn[q][m] = has ? __ldg(d_mid + ((j * MID + TP::kSlotBase + m * TP::kSlotStride) * kC + c)) : 0.0f;
-    }
-}
-
 // rows and rounds of work item `item` (receivers 2 item and 2 item + 1)
 struct ItemRows {
     int rb[2], deg[2], rounds;
@@ -214,10 +193,10 @@ __device__ __forceinline__ ItemRows item_rows(const int32_t* __restrict__ row_pt
     return r;
 }
 
-template <int LIN, bool BWD>
+template <int LIN>
 __global__ void __launch_bounds__(kFusedThreads, 1)
 k_tp_fused(const __grid_constant__ FusedArgs a) {
-    using S = FusedShape<BWD>;
+    using S = FusedShape;
     constexpr int P = TpShape<LIN>::kPaths, IN = TpShape<LIN>::kInDim, MID = TpShape<LIN>::kMidDim;
     constexpr int TN = S::kTN, NST = S::kStages;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -226,10 +205,7 @@ k_tp_fused(const __grid_constant__ FusedArgs a) {
     uint8_t* b_lo = smem + S::kBTile;
     uint8_t* ring = smem + S::kRing;
     float* ysh = reinterpret_cast<float*>(smem + S::kYsh);
-    float4* vsh = reinterpret_cast<float4*>(smem + S::kVec);
     int* snd = reinterpret_cast<int*>(smem + S::kSnd);
-    float* red = reinterpret_cast<float*>(smem + S::kRed);
-    float* scratch = reinterpret_cast<float*>(smem + S::kScratch);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kBars);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + S::kMisc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + S::kMisc + 4);
@@ -237,10 +213,6 @@ k_tp_fused(const __grid_constant__ FusedArgs a) {
     auto bar = [&](int slot) { return bar0 + 8u * (uint32_t)slot; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-#ifdef FMB_FUSED_PROFILE
-    long long prof[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-    const long long kernel_t0 = clock64();
-#endif
     if (tid == 0) {
         for (int s = 0; s < NST; ++s) {
             mbar_init(bar(kBarFull + s), 1);
@@ -295,19 +267,14 @@ k_tp_fused(const __grid_constant__ FusedArgs a) {
             const ItemRows rows = item_rows(row_ptr, a.n_rows, item);
             const int i = 2 * item + wg;
             const bool row_ok = i < a.n_rows;
-            float fsum[3] = {0.f, 0.f, 0.f}, vir[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             for (int r = 0; r < rows.rounds; ++r) {
                 const int n_g = min(max(rows.deg[wg] - r * kRoundEdges, 0), kRoundEdges);
-#ifdef FMB_FUSED_PROFILE
-                const long long stage_t0 = clock64();
-#endif
                 named_barrier(1, 256);              // every consumer is done with the previous round's tables
                 if (tid < 128) {
                     const int g = tid >> 6, idx = tid & 63;
                     const bool ok = idx < rows.deg[g] - r * kRoundEdges;
                     const long long e = (long long)rows.rb[g] + r * kRoundEdges + idx;
                     snd[tid] = ok ? a.senders[e] : 0;
-                    if (BWD) vsh[tid] = ok ? __ldg(reinterpret_cast<const float4*>(a.edge_vec) + e) : zero4;
                 }
                 for (int q = tid; q < 512; q += 256) {
                     const int col = q >> 2, g = col >> 6, idx = col & 63;
@@ -316,16 +283,14 @@ k_tp_fused(const __grid_constant__ FusedArgs a) {
                     reinterpret_cast<float4*>(ysh)[q] =
                         ok ? __ldg(reinterpret_cast<const float4*>(a.edge_sh + 16 * e) + (q & 3)) : zero4;
                 }
-                if (BWD) {
-                    for (int q = tid; q < 128 * 4 * 17; q += 256) red[q] = 0.0f;
-                }
+
 #pragma unroll
                 for (int sweep = 0; sweep < TN / 64; ++sweep) {
                     const int row = ld_row + 64 * sweep;          // operand row: edge column, + 128 for its d/dr twin
                     const int col = row & 127, g = col >> 6, idx = col & 63;
                     const bool ok = idx < rows.deg[g] - r * kRoundEdges;
                     const long long e = (long long)rows.rb[g] + r * kRoundEdges + idx;
-                    const float* src = ((BWD && row >= 128) ? a.hidden_tangent : a.hidden) + e * kRadial;
+                    const float* src = a.hidden + e * kRadial;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const float4 v = ok ? __ldg(reinterpret_cast<const float4*>(src) + ld_q + 4 * j) : zero4;
@@ -341,10 +306,6 @@ k_tp_fused(const __grid_constant__ FusedArgs a) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(kBarB));
                 named_barrier(1, 256);              // tables visible to every consumer
-#ifdef FMB_FUSED_PROFILE
-                prof[5] += clock64() - stage_t0;
-                const long long paths_t0 = clock64();
-#endif
 
                 auto path_fn = [&](auto tag) {
                     constexpr int p = decltype(tag)::value;
@@ -352,7 +313,7 @@ k_tp_fused(const __grid_constant__ FusedArgs a) {
                     constexpr int NI = TP::kNin, NE = TP::kNe, NO = TP::kNo;
                     const uint32_t buf = gpath & 1u;
                     const uint32_t t0 = tmem_base + lane_base + buf * TN + (uint32_t)col0;
-                    if constexpr (!BWD) {
+{
                         // EB edges per batch; the next batch's sender rows are requested before this one is used, the
                         // first one before the accumulator is waited for
                         constexpr int EB = LIN == 1 ? 16 : 8;
@@ -361,7 +322,7 @@ k_tp_fused(const __grid_constant__ FusedArgs a) {
                         for (int m = 0; m < NO; ++m) acc[m] = 0.0f;
                         float xn[EB][NI];
                         gather_x<TP, IN, EB>(x, snd + col0, c, xn);
-                        { FMB_T0(); mbar_wait(bar(kBarTFull + buf), (gpath >> 1) & 1u, abort_flag, kSpin); FMB_T1(6); }
+                        mbar_wait(bar(kBarTFull + buf), (gpath >> 1) & 1u, abort_flag, kSpin);
                         fence_after_sync();
 #pragma unroll 1
                         for (int sb = 0; sb < n_g; sb += EB) {
@@ -390,66 +351,6 @@ k_tp_fused(const __grid_constant__ FusedArgs a) {
                                 *out = r == 0 ? acc[m] : *out + acc[m];
                             }
                         }
-                    } else {
-                        constexpr int NV = NE + 1, NP = pow2_at_least(NV), SH = 5 - log2_of(NP);
-                        float ga[NO], xa[NI], dx[NI];
-                        const bool own_gradient = row_ok && i < a.n_valid;
-#pragma unroll
-                        for (int m = 0; m < NO; ++m)
-                            ga[m] = own_gradient ? __ldg(a.d_mid + (((long long)i * MID + TP::kSlotBase + m * TP::kSlotStride) * kC + c))
-                                                 : 0.0f;
-#pragma unroll
-                        for (int m = 0; m < NI; ++m) {
-                            xa[m] = row_ok ? __ldg(x + (((long long)i * IN + TP::kInOff + m) * kC + c)) : 0.0f;
-                            dx[m] = 0.0f;
-                        }
-                        float xn[4][NI], gn[4][NO];
-                        gather_x<TP, IN, 4>(x, snd + col0, c, xn);
-                        gather_g<TP, MID, 4>(a.d_mid, snd + col0, c, a.n_valid, gn);
-                        { FMB_T0(); mbar_wait(bar(kBarTFull + buf), (gpath >> 1) & 1u, abort_flag, kSpin); FMB_T1(6); }
-                        fence_after_sync();
-#pragma unroll 1
-                        for (int sb = 0; sb < n_g; sb += 4) {
-                            float w[4], wp[4];
-                            float xj[4][NI], gj[4][NO];
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-#pragma unroll
-                                for (int m = 0; m < NO; ++m) gj[q][m] = gn[q][m];
-#pragma unroll
-                                for (int m = 0; m < NI; ++m) xj[q][m] = xn[q][m];
-                            }
-                            if (sb + 4 < n_g) {
-                                gather_x<TP, IN, 4>(x, snd + col0 + sb + 4, c, xn);
-                                gather_g<TP, MID, 4>(a.d_mid, snd + col0 + sb + 4, c, a.n_valid, gn);
-                            }
-                            tmem_load_4x2(t0 + sb, t0 + 128 + sb, w, wp);
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                float Y[NE], pv[NV], part[NP];
-#pragma unroll
-                                for (int m = 0; m < NE; ++m) Y[m] = ysh[(col0 + sb + q) * 16 + TP::kEdgeOff + m];
-                                TP::backward(xj[q], ga, xa, gj[q], Y, w[q], wp[q], pv, dx);
-#pragma unroll
-                                for (int m = 0; m < NP; ++m) part[m] = m < NV ? pv[m] : 0.0f;
-                                warp_reduce_t<NP>(part);
-                                const int v = lane >> SH;
-                                if ((lane & ((1 << SH) - 1)) == 0 && v < NV) {
-                                    const int slot = v < NE ? TP::kEdgeOff + v : 16;
-                                    red[((col0 + sb + q) * 4 + quadrant) * 17 + slot] += part[0];
-                                }
-                            }
-                        }
-                        fence_before_sync();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(bar(kBarTEmpty + buf));
-                        if (row_ok) {
-#pragma unroll
-                            for (int m = 0; m < NI; ++m) {
-                                float* dst = a.d_x + (((long long)i * IN + TP::kInOff + m) * kC + c);
-                                *dst = (r == 0 && TP::kFirstForIn) ? dx[m] : *dst + dx[m];
-                            }
-                        }
                     }
                     ++gpath;
                 };
@@ -460,67 +361,12 @@ k_tp_fused(const __grid_constant__ FusedArgs a) {
                     FMB_FOR_EACH_PATH_2(FMB_PATH_CALL)
                 }
 #undef FMB_PATH_CALL
-#ifdef FMB_FUSED_PROFILE
-                prof[7] += clock64() - paths_t0;
-#endif
 
-                if constexpr (BWD) {
-                    named_barrier(2 + wg, 128);     // the group's four warps have added their sums
-                    if (c < n_g) {
-                        const int col = col0 + c;
-                        float g[16];
-#pragma unroll
-                        for (int q = 0; q < 16; ++q)
-                            g[q] = red[(col * 4 + 0) * 17 + q] + red[(col * 4 + 1) * 17 + q] + red[(col * 4 + 2) * 17 + q] +
-                                   red[(col * 4 + 3) * 17 + q];
-                        const float drt = red[(col * 4 + 0) * 17 + 16] + red[(col * 4 + 1) * 17 + 16] +
-                                          red[(col * 4 + 2) * 17 + 16] + red[(col * 4 + 3) * 17 + 16];
-                        const float4 uv = vsh[col];
-                        float q3[3];
-                        edge_vector_gradient(g, drt, uv.x, uv.y, uv.z, uv.w, q3);
-                        fsum[0] += q3[0]; fsum[1] += q3[1]; fsum[2] += q3[2];
-                        const float vx = uv.x * uv.w, vy = uv.y * uv.w, vz = uv.z * uv.w;
-                        vir[0] += vx * q3[0]; vir[1] += vy * q3[1]; vir[2] += vz * q3[2];
-                        vir[3] += 0.5f * (vy * q3[2] + vz * q3[1]);
-                        vir[4] += 0.5f * (vx * q3[2] + vz * q3[0]);
-                        vir[5] += 0.5f * (vx * q3[1] + vy * q3[0]);
-                    }
-                }
+
             }
-            if constexpr (BWD) {
-                // the first two warps of the group hold the per-edge terms of its row: fold them in a fixed order
-                if (quadrant < 2) {
-#pragma unroll
-                    for (int q = 0; q < 3; ++q) fsum[q] = warp_sum(fsum[q]);
-#pragma unroll
-                    for (int q = 0; q < 6; ++q) vir[q] = warp_sum(vir[q]);
-                    if (quadrant == 1 && lane == 0) {
-#pragma unroll
-                        for (int q = 0; q < 3; ++q) scratch[wg * 16 + q] = fsum[q];
-#pragma unroll
-                        for (int q = 0; q < 6; ++q) scratch[wg * 16 + 3 + q] = vir[q];
-                    }
-                }
-                named_barrier(2 + wg, 128);
-                if (row_ok && quadrant == 0 && lane == 0) {
-                    const bool fresh = a.first_layer_of_pass || i >= a.fresh_from;
-#pragma unroll
-                    for (int q = 0; q < 3; ++q)
-                        a.force_acc[3 * (long long)i + q] =
-                            (fresh ? 0.0f : a.force_acc[3 * (long long)i + q]) + (fsum[q] + scratch[wg * 16 + q]);
-#pragma unroll
-                    for (int q = 0; q < 6; ++q)
-                        a.atom_virial[6 * (long long)i + q] =
-                            (fresh ? 0.0f : a.atom_virial[6 * (long long)i + q]) + 0.5f * (vir[q] + scratch[wg * 16 + 3 + q]);
-                }
-            }
+
         }
     }
-#ifdef FMB_FUSED_PROFILE
-    if (blockIdx.x == 0 && (tid == 0 || tid == 256))
-        printf("fused<%d,%d> tid %d total %lld | empty %lld B %lld tempty %lld full %lld | staging %lld wait_tfull %lld paths %lld\n",
-               LIN, (int)BWD, tid, clock64() - kernel_t0, prof[0], prof[1], prof[2], prof[3], prof[5], prof[6], prof[7]);
-#endif
     fence_before_sync();
     __syncthreads();
     if (warp == 8) {
@@ -664,10 +510,10 @@ k_radial_weights(const __grid_constant__ WeightArgs a) {
     }
 }
 
-template <int LIN, bool BWD>
+template <int LIN>
 int launch_fused(const FusedArgs& f, cudaStream_t stream) {
     static int sms = 0;
-    FMB_CUDA_CHECK(opt_in_shared_memory((const void*)k_tp_fused<LIN, BWD>, FusedShape<BWD>::kBytes));
+    FMB_CUDA_CHECK(opt_in_shared_memory((const void*)k_tp_fused<LIN>, FusedShape::kBytes));
     if (sms == 0) {
         int dev = 0, count = 148;
         FMB_CUDA_CHECK(cudaGetDevice(&dev));
@@ -676,7 +522,7 @@ int launch_fused(const FusedArgs& f, cudaStream_t stream) {
     }
     const int items = (f.n_rows + 1) / 2;
     const int grid = items < sms ? items : sms;       // one persistent CTA per SM
-    k_tp_fused<LIN, BWD><<<grid, kFusedThreads, FusedShape<BWD>::kBytes, stream>>>(f);
+    k_tp_fused<LIN><<<grid, kFusedThreads, FusedShape::kBytes, stream>>>(f);
     FMB_LAUNCH_CHECK();
     return FMB_OK;
 }
@@ -706,13 +552,8 @@ int radial_weights_tc(const float* hidden, const float* image, float* out, int r
 int tp_fused_forward(const FusedArgs& f, cudaStream_t stream) {
     if (!f.image || f.lin < 1 || f.lin > 2) return FMB_ERR_UNSUPPORTED;
     if (f.n_rows <= 0) return FMB_OK;
-    return f.lin == 1 ? launch_fused<1, false>(f, stream) : launch_fused<2, false>(f, stream);
+    return f.lin == 1 ? launch_fused<1>(f, stream) : launch_fused<2>(f, stream);
 }
 
-int tp_fused_backward(const FusedArgs& f, cudaStream_t stream) {
-    if (!f.image || f.lin < 1 || f.lin > 2) return FMB_ERR_UNSUPPORTED;
-    if (f.n_rows <= 0) return FMB_OK;
-    return f.lin == 1 ? launch_fused<1, true>(f, stream) : launch_fused<2, true>(f, stream);
-}
 
 }  // namespace fmb

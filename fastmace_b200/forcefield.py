@@ -13,7 +13,6 @@ are simply never read), and forces come from analytic backward kernels, not auto
 from __future__ import annotations
 
 import ctypes
-import os
 from typing import NamedTuple
 
 import numpy as np
@@ -43,7 +42,7 @@ class B200ForceField:
     def __init__(self, spec: MaceSpec, weights, numbers, cell, *, compute_stress: bool = False, device="cuda",
                  neighbours: NeighbourConfig | None = None, chunk_edges: int = DEFAULT_CHUNK_EDGES,
                  positions=None, packed: PackedModel | None = None, n_owned: int = -1, n_inner: int = -1,
-                 halo_exchange: bool = False, atom_capacity: int | None = None):
+                 halo_exchange: bool = False, atom_capacity: int | None = None, edge_adjoint: bool | None = None):
         if not torch.cuda.is_available():
             raise _lib.Fmb200Error("B200ForceField needs a CUDA device: there is no CPU path")
         self.lib = _lib.load()
@@ -75,8 +74,11 @@ class B200ForceField:
         self._upload_atoms()
         self.neighbours = CellListNeighbours(self.cell, spec.r_cut, self._device, torch.float32, neighbours,
                                              atom_capacity=self.atom_capacity)
-        # FMB_CHUNK_EDGES overrides the chunk size (a tuning knob: small chunks keep the per-edge weights in L2)
-        self.chunk_edges = int(os.environ.get("FMB_CHUNK_EDGES", chunk_edges))
+        self.chunk_edges = int(chunk_edges)
+        # ``edge_adjoint``: None = the per-edge hand-over adjoint whenever its buffers fit in the free device memory,
+        # else the mirror evaluation; False = the mirror evaluation regardless (the path of lists too large for the
+        # buffers, selectable so that tests reach it on small cells); True = refuse to fall back
+        self.edge_adjoint = edge_adjoint
         self.num_edges = 0
         self.calls = 0
         self.data = {}
@@ -217,9 +219,8 @@ class B200ForceField:
         free, total = torch.cuda.mem_get_info(dev)
         free += torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)   # blocks torch holds but does not use
         need = cap * (hid * c * 4 + 20)
-        # FMB_EDGE_ADJOINT=0 keeps the mirror-evaluation kernels (A/B tests)
-        self.edge_local = need <= free - total // 10 and os.environ.get("FMB_EDGE_ADJOINT", "1") != "0"
-        if self.halo_exchange and not self.edge_local:
+        self.edge_local = need <= free - total // 10 and self.edge_adjoint is not False
+        if (self.halo_exchange or self.edge_adjoint) and not self.edge_local:
             raise _lib.Fmb200Error(f"halo-exchange mode needs {need / 2 ** 30:.1f} GiB for the per-edge hand-over "
                                    f"buffers, {max(0, free - total // 10) / 2 ** 30:.1f} GiB are free: use more ranks")
         if self.edge_local:

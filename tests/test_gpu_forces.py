@@ -214,48 +214,24 @@ def test_warp_specialised_gemm_against_torch():
     assert int(status.item()) == 0
 
 
-_VARIANT_SCRIPT = r"""
-import json, sys
-import numpy as np
-sys.path.insert(0, {root!r})
-from tests.test_gpu_forces import _case
-from fastmace_b200.forcefield import B200ForceField
-spec, weights, s = _case({name!r})
-ff = B200ForceField(spec, weights, s.numbers, s.cell, compute_stress=True, chunk_edges={chunk})
-e, f, st = ff.evaluate(s, stress=True)
-print("RESULT " + json.dumps(dict(e=e, f=f.tolist(), s=st.tolist())))
-"""
-
-
-@pytest.mark.parametrize("env,name,chunk", [
-    ({"FMB_FUSED_ADJOINT": "1"}, "medium", 1 << 19),      # fused forward and adjoint (weights only in tensor memory)
-    ({"FMB_FUSED_ADJOINT": "1"}, "large", 4096),          # the same over several chunks, node l_max 2
-    ({"FMB_GEMM": "simt"}, "medium", 1 << 19),            # every contraction on the FP32 pipes
-    ({"FMB_EDGE_ADJOINT": "0"}, "medium", 1 << 19),       # mirror-evaluation adjoint (the path of lists too large for
-    ({"FMB_EDGE_ADJOINT": "0"}, "large", 4096),           # the per-edge hand-over buffers), one chunk and several
-    ({"FMB_TP_STREAM": "0"}, "medium", 1 << 19),          # direct-load forward kernel
-    ({"FMB_OVERLAP": "0"}, "medium", 1 << 19),            # radial-weight producer on the caller's stream
-    ({"FMB_GEMM_WIDE": "2"}, "medium", 1 << 19),          # 128 x 256 tiles in every node linear that has two column
-    ({"FMB_GEMM_WIDE": "2"}, "large", 4096),              # tiles (by default only launches of more than one wave)
+@pytest.mark.parametrize("name,chunk,edge_adjoint", [
+    ("medium", 1 << 19, False),      # mirror-evaluation adjoint (the path of lists too large for the per-edge
+    ("large", 4096, False),          # hand-over buffers), one chunk and several, node l_max 1 and 2
+    ("large", 4096, None),           # several chunks: fused forward (weights only in tensor memory), per-edge adjoint
+    ("silica", 2048, None),          # the same on the amorphous cell's long rows
 ])
-def test_kernel_variants_in_subprocess(env, name, chunk):
-    """The kernel variants are selected once per process by environment variables, so each runs in a child process
-    and is compared with the oracle like the default path."""
-    import json
-    import os
-    import subprocess
-    import sys
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    script = _VARIANT_SCRIPT.format(root=root, name=name, chunk=chunk)
-    out = subprocess.run([sys.executable, "-c", script], env={**os.environ, **env}, capture_output=True, text=True,
-                         timeout=600)
-    assert out.returncode == 0, out.stderr[-2000:]
-    line = [l for l in out.stdout.splitlines() if l.startswith("RESULT ")][-1]
-    got = json.loads(line[len("RESULT "):])
+def test_paths_of_other_size_regimes_against_oracle(name, chunk, edge_adjoint):
+    """The kernels that large systems select by themselves (chunked edge lists, the mirror adjoint), reached here on
+    small cells through the constructor arguments that size them, against the oracle like the default path."""
+    from fastmace_b200.forcefield import B200ForceField
     spec, weights, s = _case(name)
+    ff = B200ForceField(spec, weights, s.numbers, s.cell, compute_stress=True, chunk_edges=chunk,
+                        edge_adjoint=edge_adjoint)
+    e, f, st = ff.evaluate(s, stress=True)
+    assert ff.edge_local == (edge_adjoint is None)
     e_ref, f_ref, s_ref = _oracle(spec, weights, s)
-    de, df, ds, fscale = _report(f"{name} {env}", got["e"], np.asarray(got["f"]), np.asarray(got["s"]), e_ref, f_ref,
-                                 s_ref, s.natoms)
+    de, df, ds, fscale = _report(f"{name} chunk {chunk} edge_adjoint {edge_adjoint}", e, f, st, e_ref, f_ref, s_ref,
+                                 s.natoms)
     assert de <= TOL_E and df <= TOL_F and ds <= TOL_S
     assert df <= 2e-4 * fscale + 1e-7
 

@@ -11,7 +11,8 @@
 //     current one (two shared-memory stages), so the loads of chunk k + 1 are in flight during chunk k;
 //   * the same thread that issues the bulk copies issues the MMAs (M = 128 rows, N = 128, K = 8 each; 12 per chunk)
 //     and commits them to the stage's `empty` barrier; after the last chunk it commits to the accumulator barrier and
-//     the loader warps turn into the epilogue (lane = row; strided rows, accumulate, species mask).
+//     the loader warps turn into the epilogue (strided rows, accumulate, species mask): the accumulator rows are
+//     turned through shared memory so that every store instruction writes one whole row.
 // One CTA computes one 128 x 128 tile of C; up to eight problems share a launch. Waits are bounded (tc::mbar_wait).
 // A launch with more narrow tiles than the GPU has SMs pairs adjacent column tiles instead (128 x 256 per CTA: two
 // weight pieces per stage, N = 256 per MMA): the MMA issue rate, not their width, bounds the K loop, and the activation
@@ -77,6 +78,10 @@ __device__ __forceinline__ void ws_fetch(const float* const (&src)[4], const boo
         for (int j = 0; j < 2; ++j)
             out[i][j] = ok[i] ? __ldg(reinterpret_cast<const float4*>(src[i] + kc * kWsTK) + ld_q + 4 * j)
                               : make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
+__device__ __forceinline__ void add_to_global(float* dst, const float4& v) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" :: "l"(dst), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 
 // barrier slots: b_full[2], a_full[2], empty[2], acc
@@ -223,56 +228,49 @@ k_gemm_ws(const __grid_constant__ WsBatch batch) {
 #ifdef FMB_GEMM_PROFILE
         t_loop = clock64();
 #endif
-        // ------------------------------------------------------------------ epilogue: lane = row
-        const int row = row0 + warp * 32 + lane;
-        const bool write = row < m && !(batch_species && batch_species[row / cmap.nm] != select);
-        float* dst_row = c_out + (row < m ? cmap(row) : 0) + nt * 128;
-        if (accumulate) {
-            // the old values of 128 columns of the row are requested before the accumulator is waited for: one memory
-            // round trip instead of one per 16 columns (measured 18,000 -> 4,000 cycles for this epilogue)
+        // ------------------------------------------------------------------ epilogue
+        // A lane reads its row of the accumulator (lane = row in TMEM), but a row written by its lane alone makes every
+        // store instruction touch 32 lines with 16 bytes each (measured 4,500 cycles for 64 KB). The warp's 32 rows go
+        // through its own 16 KB of the operand stages instead (free once the accumulator barrier has completed) and
+        // leave as whole 512-byte rows, one per instruction.
+        const int row_base = row0 + warp * 32;
+        const bool mine = row_base + lane < m && !(batch_species && batch_species[(row_base + lane) / cmap.nm] != select);
+        const unsigned live = __ballot_sync(0xffffffffu, mine);             // bit rr: row rr of this warp is written
+        float4* const turn = reinterpret_cast<float4*>(smem + warp * 16384);      // [32 rows][32 float4], XOR-swizzled
+        float* const c_tile = c_out + nt * 128 + 4 * lane;
+        const int q0 = row_base / cmap.nm, rem0 = row_base % cmap.nm;
 #pragma unroll 1
-            for (int c0 = 0; c0 < tn; c0 += 128) {
-                float4 old[32];
-#pragma unroll
-                for (int q = 0; q < 32; ++q)
-                    old[q] = write ? *(reinterpret_cast<const float4*>(dst_row + c0) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
-                if (c0 == 0) {
-                    mbar_wait(bar(kWsAcc), 0, abort_flag, kWsSpin);
+        for (int c0 = 0; c0 < tn; c0 += 128) {
+            if (c0 == 0) {
+                mbar_wait(bar(kWsAcc), 0, abort_flag, kWsSpin);
 #ifdef FMB_GEMM_PROFILE
-                    t_acc = clock64();
+                t_acc = clock64();
 #endif
-                    fence_after_sync();
-                }
-#pragma unroll
-                for (int col = 0; col < 128; col += 16) {
-                    float v[16];
-                    tmem_load<16>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c0 + col), v);
-                    if (write) {
-                        float4* dst = reinterpret_cast<float4*>(dst_row + c0 + col);
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const float4 o = old[col / 4 + q];
-                            dst[q] = make_float4(v[4 * q] + o.x, v[4 * q + 1] + o.y, v[4 * q + 2] + o.z, v[4 * q + 3] + o.w);
-                        }
-                    }
-                }
+                fence_after_sync();
             }
-        } else {
-            mbar_wait(bar(kWsAcc), 0, abort_flag, kWsSpin);
-#ifdef FMB_GEMM_PROFILE
-            t_acc = clock64();
-#endif
-            fence_after_sync();
-#pragma unroll 1
-            for (int col = 0; col < tn; col += 16) {
+#pragma unroll
+            for (int col = 0; col < 128; col += 16) {
                 float v[16];
-                tmem_load<16>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col, v);
-                if (write) {
-                    float4* dst = reinterpret_cast<float4*>(dst_row + col);
+                tmem_load<16>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c0 + col), v);
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                }
+                for (int q = 0; q < 4; ++q)
+                    turn[lane * 32 + (((col >> 2) + q) ^ lane)] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
             }
+            __syncwarp();
+            int q = q0, rem = rem0;
+#pragma unroll 8
+            for (int rr = 0; rr < 32; ++rr) {
+                const float4 v = turn[rr * 32 + (lane ^ rr)];
+                if ((live >> rr) & 1u) {
+                    float* dst = c_tile + c0 + (long long)q * cmap.bs + (long long)rem * cmap.rs;
+                    // accumulate: the add happens at the memory side (every element has one writer, so the sum is the
+                    // same old + new as a load and a store would give, without the round trip for the old values)
+                    if (accumulate) add_to_global(dst, v);
+                    else *reinterpret_cast<float4*>(dst) = v;
+                }
+                if (++rem == cmap.nm) { rem = 0; ++q; }
+            }
+            __syncwarp();
         }
     }
 #ifdef FMB_GEMM_PROFILE

@@ -60,6 +60,7 @@ class LayerStruct(ctypes.Structure):
         ("w_lin_t", c_void_p), ("w_prod", c_void_p), ("w_prod_t", c_void_p), ("sc_terms", c_void_p),
         ("sc_coef", c_void_p), ("w_readout", c_void_p), ("tc", c_void_p * 9), ("first", c_void_p * 4),
         ("rad_img", c_void_p), ("tc_img", c_void_p * 9), ("first_img", c_void_p * 2),
+        ("mlp_img", c_void_p),
     ]
 
 

@@ -15,6 +15,7 @@
 #include "edge_gradient.cuh"
 #include "gemm.cuh"
 #include "stages.cuh"
+#include "tc_common.cuh"
 
 namespace fmb {
 
@@ -45,59 +46,6 @@ __device__ __forceinline__ void sh16(float x, float y, float z, float* Y) {
     Y[15] = C3 * (S56 * (s24 * z - s20 * x));
 }
 
-// act: [2][64][128] value rows then tangent rows, k-major (edge contiguous). w: [K][64] in shared memory.
-// Each thread owns 8 edges x 8 outputs (te = tid / 8 edge group, tj = tid % 8 output group).
-template <int K>
-__device__ __forceinline__ void mlp_layer(float* __restrict__ act, const float* __restrict__ w, float silu_norm,
-                                          float (&val)[8][8], float (&tan)[8][8]) {
-    const int te = threadIdx.x >> 3, tj = threadIdx.x & 7;
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) { val[i][j] = 0.0f; tan[i][j] = 0.0f; }
-#pragma unroll 4
-    for (int k = 0; k < K; ++k) {
-        const float4 v0 = *reinterpret_cast<const float4*>(&act[k * 128 + te * 8]);
-        const float4 v1 = *reinterpret_cast<const float4*>(&act[k * 128 + te * 8 + 4]);
-        const float4 t0 = *reinterpret_cast<const float4*>(&act[(64 + k) * 128 + te * 8]);
-        const float4 t1 = *reinterpret_cast<const float4*>(&act[(64 + k) * 128 + te * 8 + 4]);
-        const float4 w0 = *reinterpret_cast<const float4*>(&w[k * 64 + tj * 8]);
-        const float4 w1 = *reinterpret_cast<const float4*>(&w[k * 64 + tj * 8 + 4]);
-        const float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-        const float tt[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
-        const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                val[i][j] = fmaf(vv[i], ww[j], val[i][j]);
-                tan[i][j] = fmaf(tt[i], ww[j], tan[i][j]);
-            }
-    }
-    // normalised SiLU and its derivative
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const float a = val[i][j];
-            const float sig = 1.0f / (1.0f + expf(-a));
-            val[i][j] = silu_norm * a * sig;
-            tan[i][j] = silu_norm * sig * (1.0f + a * (1.0f - sig)) * tan[i][j];
-        }
-}
-
-__device__ __forceinline__ void store_act(float* __restrict__ act, const float (&val)[8][8], const float (&tan)[8][8]) {
-    const int te = threadIdx.x >> 3, tj = threadIdx.x & 7;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const int k = tj * 8 + j;
-        *reinterpret_cast<float4*>(&act[k * 128 + te * 8]) = make_float4(val[0][j], val[1][j], val[2][j], val[3][j]);
-        *reinterpret_cast<float4*>(&act[k * 128 + te * 8 + 4]) = make_float4(val[4][j], val[5][j], val[6][j], val[7][j]);
-        *reinterpret_cast<float4*>(&act[(64 + k) * 128 + te * 8]) = make_float4(tan[0][j], tan[1][j], tan[2][j], tan[3][j]);
-        *reinterpret_cast<float4*>(&act[(64 + k) * 128 + te * 8 + 4]) = make_float4(tan[4][j], tan[5][j], tan[6][j], tan[7][j]);
-    }
-}
-
 struct EdgeParams {
     int n_layers;
     int capacity;
@@ -105,111 +53,92 @@ struct EdgeParams {
     float silu_norm;
     double cell[9];
     const float* rad_w[FMB_MAX_LAYERS][3];
+    const float* mlp_img[FMB_MAX_LAYERS];     // the same three layers as tensor-core operand images (or null)
+    uint32_t* error_word;
 };
 
-__global__ void __launch_bounds__(kThreads)
-k_edge_features(EdgeParams p, const double* __restrict__ x, const int32_t* __restrict__ edge_index,
-                const float* __restrict__ unit_shifts, const long long* __restrict__ count_ptr,
-                float* __restrict__ edge_vec, float* __restrict__ edge_sh, float* __restrict__ edge_hidden) {
-    extern __shared__ __align__(16) float smem[];
-    float* act = smem;                       // [2][64][128]
-    float* w_s = smem + 2 * 64 * 128;        // [64][64] (first layer uses [8][64])
-    float* feat = w_s + 64 * 64;             // [2][8][128] Bessel x cutoff and its derivative
-    const long long count = *count_ptr;
-    const long long e0 = (long long)blockIdx.x * kEdgesPerBlock;
-    if (e0 >= count) return;
-    const int tid = threadIdx.x;
-    const long long e = e0 + tid;
-    const bool live = e < count;
-    {
-        float ef[8], def[8];
+// Edge vector, length and the Bessel x envelope features with their d/dr (zero at and beyond the cutoff).
+struct EdgeGeometry {
+    float ux, uy, uz, len;
+};
+
+__device__ __forceinline__ EdgeGeometry edge_geometry(const EdgeParams& p, const double* __restrict__ x,
+                                                      const int32_t* __restrict__ edge_index,
+                                                      const float* __restrict__ unit_shifts, long long e) {
+    const int s = edge_index[e], r = edge_index[p.capacity + e];
+    const double u0 = unit_shifts[3 * e], u1 = unit_shifts[3 * e + 1], u2 = unit_shifts[3 * e + 2];
+    double v[3];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) { ef[k] = 0.0f; def[k] = 0.0f; }
-        if (live) {
-            const int s = edge_index[e], r = edge_index[p.capacity + e];
-            const double u0 = unit_shifts[3 * e], u1 = unit_shifts[3 * e + 1], u2 = unit_shifts[3 * e + 2];
-            double v[3];
+    for (int a = 0; a < 3; ++a) {
+        const double shift = u0 * p.cell[a] + u1 * p.cell[3 + a] + u2 * p.cell[6 + a];
+        v[a] = (x[3 * r + a] - x[3 * s + a]) + shift;
+    }
+    const float vx = (float)v[0], vy = (float)v[1], vz = (float)v[2];
+    EdgeGeometry g;
+    g.len = sqrtf(vx * vx + vy * vy + vz * vz);
+    const float inv = 1.0f / fmaxf(g.len, 1e-12f);
+    g.ux = vx * inv; g.uy = vy * inv; g.uz = vz * inv;
+    return g;
+}
+
+__device__ __forceinline__ void bessel_features(float len, float rc, float (&ef)[8], float (&def)[8]) {
 #pragma unroll
-            for (int a = 0; a < 3; ++a) {
-                const double shift = u0 * p.cell[a] + u1 * p.cell[3 + a] + u2 * p.cell[6 + a];
-                v[a] = (x[3 * r + a] - x[3 * s + a]) + shift;
-            }
-            const float vx = (float)v[0], vy = (float)v[1], vz = (float)v[2];
-            const float len = sqrtf(vx * vx + vy * vy + vz * vz);
-            const float inv = 1.0f / fmaxf(len, 1e-12f);
-            const float ux = vx * inv, uy = vy * inv, uz = vz * inv;
-            reinterpret_cast<float4*>(edge_vec)[e] = make_float4(ux, uy, uz, len);
-            float Y[16];
-            sh16(ux, uy, uz, Y);
-            float4* ysh = reinterpret_cast<float4*>(edge_sh + 16 * e);
-            ysh[0] = make_float4(Y[0], Y[1], Y[2], Y[3]);
-            ysh[1] = make_float4(Y[4], Y[5], Y[6], Y[7]);
-            ysh[2] = make_float4(Y[8], Y[9], Y[10], Y[11]);
-            ysh[3] = make_float4(Y[12], Y[13], Y[14], Y[15]);
-            if (len < p.r_cut) {
-                const float rc = p.r_cut;
-                const float xr = len / rc;
-                const float x2 = xr * xr, x4 = x2 * x2, x5 = x4 * xr;
-                // p = 5: 1 - 21 x^5 + 35 x^6 - 15 x^7 and its derivative
-                const float env = 1.0f - 21.0f * x5 + 35.0f * x5 * xr - 15.0f * x5 * x2;
-                const float denv = (-105.0f * x4 + 210.0f * x5 - 105.0f * x5 * xr) / rc;
-                const float pref = sqrtf(2.0f / rc);
-                const float inv_r = 1.0f / len;
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const float wk = (float)(k + 1) * 3.14159265358979323846f / rc;
-                    float sn, cs;
-                    sincosf(wk * len, &sn, &cs);
-                    const float bes = pref * sn * inv_r;
-                    const float dbes = pref * (wk * cs * inv_r - sn * inv_r * inv_r);
-                    ef[k] = bes * env;
-                    def[k] = dbes * env + bes * denv;
-                }
-            }
-        }
+    for (int k = 0; k < 8; ++k) { ef[k] = 0.0f; def[k] = 0.0f; }
+    if (len < rc) {
+        const float xr = len / rc;
+        const float x2 = xr * xr, x4 = x2 * x2, x5 = x4 * xr;
+        // p = 5: 1 - 21 x^5 + 35 x^6 - 15 x^7 and its derivative
+        const float env = 1.0f - 21.0f * x5 + 35.0f * x5 * xr - 15.0f * x5 * x2;
+        const float denv = (-105.0f * x4 + 210.0f * x5 - 105.0f * x5 * xr) / rc;
+        const float pref = sqrtf(2.0f / rc);
+        const float inv_r = 1.0f / len;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-            feat[k * 128 + tid] = ef[k];
-            feat[(8 + k) * 128 + tid] = def[k];
+            const float wk = (float)(k + 1) * 3.14159265358979323846f / rc;
+            float sn, cs;
+            sincosf(wk * len, &sn, &cs);
+            const float bes = pref * sn * inv_r;
+            const float dbes = pref * (wk * cs * inv_r - sn * inv_r * inv_r);
+            ef[k] = bes * env;
+            def[k] = dbes * env + bes * denv;
         }
     }
-    float val[8][8], tan[8][8];
-    const int te = tid >> 3, tj = tid & 7;
-    for (int layer = 0; layer < p.n_layers; ++layer) {
-        __syncthreads();
-        // first layer: 8 -> 64
-        for (int k = tid; k < 8 * 64; k += kThreads) w_s[k] = p.rad_w[layer][0][k];
-        for (int k = tid; k < 8 * 128; k += kThreads) {
-            act[k] = feat[k];
-            act[64 * 128 + k] = feat[8 * 128 + k];
-        }
-        __syncthreads();
-        mlp_layer<8>(act, w_s, p.silu_norm, val, tan);
-        __syncthreads();
-        store_act(act, val, tan);
-        for (int hidden = 1; hidden < 3; ++hidden) {
-            for (int k = tid; k < 64 * 64; k += kThreads) w_s[k] = p.rad_w[layer][hidden][k];
-            __syncthreads();
-            mlp_layer<64>(act, w_s, p.silu_norm, val, tan);
-            __syncthreads();
-            if (hidden < 2) store_act(act, val, tan);
-        }
-        // the third hidden layer goes to global memory: [layer][0 value / 1 tangent][edge][64]
-        float* hv = edge_hidden + ((long long)(2 * layer) * p.capacity) * 64;
-        float* ht = edge_hidden + ((long long)(2 * layer + 1) * p.capacity) * 64;
+}
+
+// four of the eight (first = 0 or 4), for kernels that spread an edge's basis functions over two threads
+__device__ __forceinline__ void bessel_features(float len, float rc, int first, float (&ef)[4], float (&def)[4]) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const long long ee = e0 + te * 8 + i;
-            if (ee < count) {
-                float4* dv = reinterpret_cast<float4*>(hv + ee * 64 + tj * 8);
-                float4* dt = reinterpret_cast<float4*>(ht + ee * 64 + tj * 8);
-                dv[0] = make_float4(val[i][0], val[i][1], val[i][2], val[i][3]);
-                dv[1] = make_float4(val[i][4], val[i][5], val[i][6], val[i][7]);
-                dt[0] = make_float4(tan[i][0], tan[i][1], tan[i][2], tan[i][3]);
-                dt[1] = make_float4(tan[i][4], tan[i][5], tan[i][6], tan[i][7]);
-            }
+    for (int k = 0; k < 4; ++k) { ef[k] = 0.0f; def[k] = 0.0f; }
+    if (len < rc) {
+        const float xr = len / rc;
+        const float x2 = xr * xr, x4 = x2 * x2, x5 = x4 * xr;
+        const float env = 1.0f - 21.0f * x5 + 35.0f * x5 * xr - 15.0f * x5 * x2;
+        const float denv = (-105.0f * x4 + 210.0f * x5 - 105.0f * x5 * xr) / rc;
+        const float pref = sqrtf(2.0f / rc);
+        const float inv_r = 1.0f / len;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float wk = (float)(first + k + 1) * 3.14159265358979323846f / rc;
+            float sn, cs;
+            sincosf(wk * len, &sn, &cs);
+            const float bes = pref * sn * inv_r;
+            const float dbes = pref * (wk * cs * inv_r - sn * inv_r * inv_r);
+            ef[k] = bes * env;
+            def[k] = dbes * env + bes * denv;
         }
     }
+}
+
+__device__ __forceinline__ void store_harmonics(const EdgeGeometry& g, float* __restrict__ edge_vec,
+                                                float* __restrict__ edge_sh, long long e) {
+    reinterpret_cast<float4*>(edge_vec)[e] = make_float4(g.ux, g.uy, g.uz, g.len);
+    float Y[16];
+    sh16(g.ux, g.uy, g.uz, Y);
+    float4* ysh = reinterpret_cast<float4*>(edge_sh + 16 * e);
+    ysh[0] = make_float4(Y[0], Y[1], Y[2], Y[3]);
+    ysh[1] = make_float4(Y[4], Y[5], Y[6], Y[7]);
+    ysh[2] = make_float4(Y[8], Y[9], Y[10], Y[11]);
+    ysh[3] = make_float4(Y[12], Y[13], Y[14], Y[15]);
 }
 
 // ------------------------------------------------------------------------------------------------ tensor-core MLP
@@ -297,45 +226,9 @@ k_edge_features_mma(EdgeParams p, const double* __restrict__ x, const int32_t* _
 #pragma unroll
     for (int k = 0; k < 8; ++k) { ef[k] = 0.0f; def[k] = 0.0f; }
     if (live) {
-        const int s = edge_index[e], r = edge_index[p.capacity + e];
-        const double u0 = unit_shifts[3 * e], u1 = unit_shifts[3 * e + 1], u2 = unit_shifts[3 * e + 2];
-        double v[3];
-#pragma unroll
-        for (int a = 0; a < 3; ++a) {
-            const double shift = u0 * p.cell[a] + u1 * p.cell[3 + a] + u2 * p.cell[6 + a];
-            v[a] = (x[3 * r + a] - x[3 * s + a]) + shift;
-        }
-        const float vx = (float)v[0], vy = (float)v[1], vz = (float)v[2];
-        const float len = sqrtf(vx * vx + vy * vy + vz * vz);
-        const float inv = 1.0f / fmaxf(len, 1e-12f);
-        const float ux = vx * inv, uy = vy * inv, uz = vz * inv;
-        reinterpret_cast<float4*>(edge_vec)[e] = make_float4(ux, uy, uz, len);
-        float Y[16];
-        sh16(ux, uy, uz, Y);
-        float4* ysh = reinterpret_cast<float4*>(edge_sh + 16 * e);
-        ysh[0] = make_float4(Y[0], Y[1], Y[2], Y[3]);
-        ysh[1] = make_float4(Y[4], Y[5], Y[6], Y[7]);
-        ysh[2] = make_float4(Y[8], Y[9], Y[10], Y[11]);
-        ysh[3] = make_float4(Y[12], Y[13], Y[14], Y[15]);
-        if (len < p.r_cut) {
-            const float rc = p.r_cut;
-            const float xr = len / rc;
-            const float x2 = xr * xr, x4 = x2 * x2, x5 = x4 * xr;
-            const float env = 1.0f - 21.0f * x5 + 35.0f * x5 * xr - 15.0f * x5 * x2;
-            const float denv = (-105.0f * x4 + 210.0f * x5 - 105.0f * x5 * xr) / rc;
-            const float pref = sqrtf(2.0f / rc);
-            const float inv_r = 1.0f / len;
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const float wk = (float)(k + 1) * 3.14159265358979323846f / rc;
-                float sn, cs;
-                sincosf(wk * len, &sn, &cs);
-                const float bes = pref * sn * inv_r;
-                const float dbes = pref * (wk * cs * inv_r - sn * inv_r * inv_r);
-                ef[k] = bes * env;
-                def[k] = dbes * env + bes * denv;
-            }
-        }
+        const EdgeGeometry g = edge_geometry(p, x, edge_index, unit_shifts, e);
+        store_harmonics(g, edge_vec, edge_sh, e);
+        bessel_features(g.len, p.r_cut, ef, def);
     }
     float cv[2][8][4], ct[2][8][4];
     for (int layer = 0; layer < p.n_layers; ++layer) {
@@ -411,6 +304,238 @@ k_edge_features_mma(EdgeParams p, const double* __restrict__ x, const int32_t* _
     }
 }
 
+// ------------------------------------------------------------------------------------------------ tcgen05 MLP
+// The three hidden layers on the tcgen05 path (the warp-level mma.sync instructions above run at a fraction of the
+// tensor pipe's rate on this architecture: 124 us for 62 k edges, with the pipe 46 % busy).
+//
+// One CTA = 64 edges = one M = 128 accumulator tile: the values and the d/dr tangents of an edge are two rows of the
+// same tile, so one chain of MMAs (N = 64, 3xTF32) serves both. Rows are ordered so that a quarter of the accumulator
+// lanes (the 32 lanes one warp can read) holds 16 edges' values (lanes 0-15) and the same edges' tangents (lanes
+// 16-31): the SiLU needs both, and the two lanes of an edge trade halves of what they read with shuffles, so that every
+// lane does the same amount of exp / reciprocal work and nothing crosses warps. Eight warps: warps w and w + 4 read
+// the same lane quarter and take 32 of the 64 columns each, i.e. a thread finishes 16 columns of one edge, values
+// and tangents. The activated rows go back to shared memory as the next layer's operand (tf32 value and remainder
+// parts, K-major with the 128-byte swizzle); the third layer's rows leave through the same memory as whole 256-byte
+// rows. The weights arrive as ready-made operand images by bulk copy while the SiLU of the layer before runs. One
+// thread issues the MMAs. Every wait is bounded.
+constexpr int kTcEdges = 64;
+constexpr int kTcThreads = 256;
+constexpr int kTcATile = 128 * 64 * 4;                 // 32 KB: [128 rows][64 k], one of the two tf32 parts
+constexpr int kTcWTile = 64 * 64 * 4;                  // 16 KB: [64 outputs][64 k]
+constexpr int kTcBytes = 2 * kTcATile + 2 * kTcWTile + 64 + 1024;
+constexpr unsigned kTcSpin = 1u << 20;
+// float offsets of the layers' images inside mlp_img: [8 -> 64] value / remainder (one K half each), then the two
+// [64 -> 64] layers, value (two K halves) then remainder
+constexpr int kImgFirstLo = 2048, kImgHidden = 4096, kImgHiddenStride = 8192;
+
+__device__ __forceinline__ void store_split(uint8_t* hi_tile, uint8_t* lo_tile, int row, int k, const float4& v) {
+    const float4 hi = make_float4(tc::tf32_rna(v.x), tc::tf32_rna(v.y), tc::tf32_rna(v.z), tc::tf32_rna(v.w));
+    const float4 lo = make_float4(tc::tf32_rna(v.x - hi.x), tc::tf32_rna(v.y - hi.y), tc::tf32_rna(v.z - hi.z),
+                                  tc::tf32_rna(v.w - hi.w));
+    const uint32_t off = tc::tile_offset<128>(row, k);
+    *reinterpret_cast<float4*>(hi_tile + off) = hi;
+    *reinterpret_cast<float4*>(lo_tile + off) = lo;
+}
+
+#ifdef FMB_EDGE_PROFILE
+#define FMB_ESTAMP() do { if (n_stamp < 40) stamp[n_stamp++] = clock64() - t_begin; } while (0)
+#else
+#define FMB_ESTAMP() do {} while (0)
+#endif
+
+__global__ void __launch_bounds__(kTcThreads, 2)
+k_edge_features_tc(const __grid_constant__ EdgeParams p, const double* __restrict__ x,
+                   const int32_t* __restrict__ edge_index, const float* __restrict__ unit_shifts,
+                   const long long* __restrict__ count_ptr, float* __restrict__ edge_vec, float* __restrict__ edge_sh,
+                   float* __restrict__ edge_hidden) {
+    using namespace tc;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t* a_hi = smem;
+    uint8_t* a_lo = smem + kTcATile;
+    uint8_t* w_buf = smem + 2 * kTcATile;                // value image, then remainder image 16 KB further
+    uint64_t* bars = reinterpret_cast<uint64_t*>(w_buf + 2 * kTcWTile);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const uint32_t bar_w = smem_u32(bars), bar_mma = bar_w + 8;
+
+    const long long count = *count_ptr;
+    const long long e0 = (long long)blockIdx.x * kTcEdges;
+    if (e0 >= count) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int quarter = warp & 3;                        // the 32 accumulator lanes this warp reads
+    const int half = warp >> 2;                          // and the 32 columns of them it takes
+    const int upper = lane >> 4;                         // 0: this lane's accumulator row holds values, 1: tangents
+    const int row_v = quarter * 32 + (lane & 15), row_t = row_v + 16;
+    const long long e = e0 + quarter * 16 + (lane & 15);
+    const bool live = e < count;
+#ifdef FMB_EDGE_PROFILE
+    long long stamp[40]; int n_stamp = 0;
+    const long long t_begin = clock64();
+#endif
+
+    auto request_weights = [&](int layer, int hidden) {
+        const float* img = p.mlp_img[layer];
+        const uint32_t dst = smem_u32(w_buf);
+        if (hidden == 0) {
+            mbar_expect_tx(bar_w, 2 * 8192);
+            bulk_load(dst, img, 8192, bar_w);
+            bulk_load(dst + kTcWTile, img + kImgFirstLo, 8192, bar_w);
+        } else {
+            mbar_expect_tx(bar_w, 2 * kTcWTile);
+            bulk_load(dst, img + kImgHidden + (hidden - 1) * kImgHiddenStride, 2 * kTcWTile, bar_w);
+        }
+    };
+    if (tid == 0) {
+        mbar_init(bar_w, 1);
+        mbar_init(bar_mma, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        request_weights(0, 0);
+    }
+    if (warp == 0) {
+        __syncwarp();
+        tmem_alloc(smem_u32(tmem_slot), 64);
+    }
+
+    // geometry: the four threads of an edge share its vector; the two lower ones evaluate four radial basis
+    // functions each, one of the upper ones the harmonics
+    float ef[4] = {0.f, 0.f, 0.f, 0.f}, def[4] = {0.f, 0.f, 0.f, 0.f};
+    if (live && !(upper && half)) {
+        const EdgeGeometry g = edge_geometry(p, x, edge_index, unit_shifts, e);
+        if (upper) store_harmonics(g, edge_vec, edge_sh, e);
+        else bessel_features(g.len, p.r_cut, 4 * half, ef, def);
+    }
+
+    uint32_t w_parity = 0, mma_parity = 0;
+    uint32_t tmem_base = 0;
+    for (int layer = 0; layer < p.n_layers; ++layer) {
+        for (int hidden = 0; hidden < 3; ++hidden) {
+            if (hidden == 0 && !upper) {
+                // the 8 radial features and their d/dr: K = 8, the first 32 bytes of the two rows of this edge
+                store_split(a_hi, a_lo, row_v, 4 * half, make_float4(ef[0], ef[1], ef[2], ef[3]));
+                store_split(a_hi, a_lo, row_t, 4 * half, make_float4(def[0], def[1], def[2], def[3]));
+            }
+            FMB_ESTAMP();      // 0: operands written
+            fence_async_smem();
+            fence_before_sync();
+            __syncthreads();
+            fence_after_sync();
+            FMB_ESTAMP();      // 1: CTA synchronised
+            if (layer == 0 && hidden == 0) tmem_base = *tmem_slot;
+            if (tid == 0) {
+                mbar_wait(bar_w, w_parity, abort_flag, kTcSpin);
+                FMB_ESTAMP();  // 2: weights there
+                const uint32_t idesc = make_idesc<64>();
+                const uint64_t da_hi = make_desc(smem_u32(a_hi)), da_lo = make_desc(smem_u32(a_lo));
+                const uint64_t dw_hi = make_desc(smem_u32(w_buf)), dw_lo = make_desc(smem_u32(w_buf) + kTcWTile);
+                if (hidden == 0) {
+                    mma_tf32(tmem_base, da_lo, dw_hi, idesc, 0);
+                    mma_tf32(tmem_base, da_hi, dw_lo, idesc, 1);
+                    mma_tf32(tmem_base, da_hi, dw_hi, idesc, 1);
+                } else {
+#pragma unroll
+                    for (int k8 = 0; k8 < 8; ++k8)
+                        mma_tf32(tmem_base, da_lo + k_step<128>(k8), dw_hi + k_step<64>(k8), idesc, k8 > 0 ? 1 : 0);
+#pragma unroll
+                    for (int k8 = 0; k8 < 8; ++k8) mma_tf32(tmem_base, da_hi + k_step<128>(k8), dw_lo + k_step<64>(k8), idesc, 1);
+#pragma unroll
+                    for (int k8 = 0; k8 < 8; ++k8) mma_tf32(tmem_base, da_hi + k_step<128>(k8), dw_hi + k_step<64>(k8), idesc, 1);
+                }
+                mma_commit(bar_mma);
+                FMB_ESTAMP();  // 3: issued
+            }
+            w_parity ^= 1u;
+            mbar_wait(bar_mma, mma_parity, abort_flag, kTcSpin);
+            mma_parity ^= 1u;
+            fence_after_sync();
+            FMB_ESTAMP();      // 4: MMAs complete
+            if (tid == 0) {
+                // the weight buffer is free: the next layer's image travels while this layer's SiLU runs
+                if (hidden < 2) request_weights(layer, hidden + 1);
+                else if (layer + 1 < p.n_layers) request_weights(layer + 1, 0);
+            }
+            // 32 columns of this lane's accumulator row: pre-activations (lower lanes) or raw tangents (upper lanes)
+            float own[32];
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(32 * half);
+            {
+                float v0[16], v1[16];
+                tmem_load_16x2(taddr, taddr + 16, v0, v1);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) { own[i] = v0[i]; own[16 + i] = v1[i]; }
+            }
+            FMB_ESTAMP();      // 5: accumulator row loaded
+            // the lower lane finishes the first 16 of these columns, the upper lane the other 16
+            float act[16], tng[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float send = upper ? own[i] : own[16 + i];
+                const float recv = __shfl_xor_sync(0xffffffffu, send, 16);
+                act[i] = upper ? recv : own[i];
+                tng[i] = upper ? own[16 + i] : recv;
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float a = act[i];
+                // ex2.approx + rcp.approx: relative error of a few 1e-7 on the sigmoid, far inside the fp32
+                // tolerance of the forces
+                const float sig = __fdividef(1.0f, 1.0f + __expf(-a));
+                act[i] = p.silu_norm * a * sig;
+                tng[i] = p.silu_norm * sig * (1.0f + a * (1.0f - sig)) * tng[i];
+            }
+            const int col0 = 32 * half + 16 * upper;
+            if (hidden < 2) {
+#pragma unroll
+                for (int i4 = 0; i4 < 4; ++i4) {
+                    store_split(a_hi, a_lo, row_v, col0 + 4 * i4, make_float4(act[4 * i4], act[4 * i4 + 1], act[4 * i4 + 2], act[4 * i4 + 3]));
+                    store_split(a_hi, a_lo, row_t, col0 + 4 * i4, make_float4(tng[4 * i4], tng[4 * i4 + 1], tng[4 * i4 + 2], tng[4 * i4 + 3]));
+                }
+            } else {
+                // the third hidden layer goes to global memory, [layer][0 value / 1 tangent][edge][64]: staged in
+                // the (now free) operand tile as plain rows [128][64] with the 16-byte slot XORed with the row, then
+                // written as whole rows -- a quarter's 16 value rows are 4 KB contiguous, and so are its tangent rows
+                float4* stage = reinterpret_cast<float4*>(a_hi);
+#pragma unroll
+                for (int i4 = 0; i4 < 4; ++i4) {
+                    const int slot = (col0 >> 2) + i4;
+                    stage[row_v * 16 + (slot ^ (row_v & 15))] = make_float4(act[4 * i4], act[4 * i4 + 1], act[4 * i4 + 2], act[4 * i4 + 3]);
+                    stage[row_t * 16 + (slot ^ (row_t & 15))] = make_float4(tng[4 * i4], tng[4 * i4 + 1], tng[4 * i4 + 2], tng[4 * i4 + 3]);
+                }
+                __syncthreads();
+                float* hv = edge_hidden + ((long long)(2 * layer) * p.capacity) * 64;
+                float* ht = edge_hidden + ((long long)(2 * layer + 1) * p.capacity) * 64;
+                // 2,048 float4 in all; a warp instruction moves two rows
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                    const int row = it * 16 + (tid >> 4), slot = tid & 15;
+                    const int q = row >> 5, j = row & 31;                 // quarter and lane of the row
+                    const long long edge = e0 + q * 16 + (j & 15);
+                    if (edge < count) {
+                        float* dst = (j < 16 ? hv : ht) + edge * 64 + 4 * slot;
+                        *reinterpret_cast<float4*>(dst) = stage[row * 16 + (slot ^ (row & 15))];
+                    }
+                }
+                if (layer + 1 < p.n_layers) __syncthreads();      // the next interaction's operands go to the same tile
+            }
+        }
+    }
+#ifdef FMB_EDGE_PROFILE
+    FMB_ESTAMP();
+    if (blockIdx.x == 0 && tid == 0) {
+        printf("edge_tc stamps:");
+        for (int i = 0; i < n_stamp; ++i) printf(" %lld", stamp[i]);
+        printf("\n");
+    }
+#endif
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 0) {
+        if (lane == 0 && *abort_flag && p.error_word) atomicOr(p.error_word, FMB_STATUS_TENSOR_TIMEOUT);
+        __syncwarp();
+        tmem_free(tmem_base, 64);
+    }
+}
+
 // The harmonics and their gradient exactly as the edge and adjoint kernels evaluate them, on plain vectors.
 __global__ void k_harmonics_probe(const float* __restrict__ vectors, const float* __restrict__ grad_sh,
                                   float* __restrict__ sh, float* __restrict__ grad_vectors, int n) {
@@ -444,21 +569,24 @@ int edge_features(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t
     for (int k = 0; k < 9; ++k) p.cell[k] = nl->cell[k];
     for (int t = 0; t < model->n_layers; ++t)
         for (int k = 0; k < 3; ++k) p.rad_w[t][k] = model->layer[t].rad_w[k];
-    const size_t smem = (size_t)(2 * 64 * 128 + 64 * 64 + 2 * 8 * 128) * sizeof(float);
-    FMB_CUDA_CHECK(opt_in_shared_memory((const void*)k_edge_features, (int)smem));
-    const int blocks = ceil_div(nl->capacity, kEdgesPerBlock);
-    if (tensor_cores_enabled()) {
-        const size_t smem_mma = (size_t)kMmaSmemFloats * sizeof(float);
-        FMB_CUDA_CHECK(opt_in_shared_memory((const void*)k_edge_features_mma, (int)smem_mma));
-        k_edge_features_mma<<<blocks, kThreads, smem_mma, stream>>>(p, positions, nl->edge_index, nl->unit_shifts,
-                                                                    count, work->edge_vec,
-                                                                    work->edge_sh, work->edge_hidden);
+    p.error_word = work->status;
+    bool images = model->n_layers > 0;
+    for (int t = 0; t < model->n_layers; ++t) {
+        p.mlp_img[t] = model->layer[t].mlp_img;
+        images = images && p.mlp_img[t] != nullptr;
+    }
+    if (images) {
+        // operand images packed: the tcgen05 kernel, 64 edges per CTA
+        FMB_CUDA_CHECK(opt_in_shared_memory((const void*)k_edge_features_tc, kTcBytes));
+        k_edge_features_tc<<<ceil_div(nl->capacity, kTcEdges), kTcThreads, kTcBytes, stream>>>(
+            p, positions, nl->edge_index, nl->unit_shifts, count, work->edge_vec, work->edge_sh, work->edge_hidden);
         FMB_LAUNCH_CHECK();
         return FMB_OK;
     }
-    k_edge_features<<<blocks, kThreads, smem, stream>>>(p, positions, nl->edge_index, nl->unit_shifts,
-                                                        count, work->edge_vec, work->edge_sh,
-                                                        work->edge_hidden);
+    const size_t smem_mma = (size_t)kMmaSmemFloats * sizeof(float);
+    FMB_CUDA_CHECK(opt_in_shared_memory((const void*)k_edge_features_mma, (int)smem_mma));
+    k_edge_features_mma<<<ceil_div(nl->capacity, kEdgesPerBlock), kThreads, smem_mma, stream>>>(
+        p, positions, nl->edge_index, nl->unit_shifts, count, work->edge_vec, work->edge_sh, work->edge_hidden);
     FMB_LAUNCH_CHECK();
     return FMB_OK;
 }

@@ -56,7 +56,7 @@ struct StageScope {
 // record the fork / join as graph dependencies.
 struct SideStream {
     cudaStream_t stream = nullptr;
-    cudaEvent_t fork = nullptr, join = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr, join_tangent = nullptr;
 };
 
 SideStream* side_stream(cudaStream_t main) {
@@ -69,7 +69,8 @@ SideStream* side_stream(cudaStream_t main) {
         if (cudaStreamIsCapturing(main, &status) != cudaSuccess || status != cudaStreamCaptureStatusNone) return nullptr;
         if (cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) != cudaSuccess) { s.stream = nullptr; return nullptr; }
         if (cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) != cudaSuccess ||
-            cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) != cudaSuccess) {
+            cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&s.join_tangent, cudaEventDisableTiming) != cudaSuccess) {
             s.stream = nullptr;
             return nullptr;
         }
@@ -537,8 +538,10 @@ extern "C" FMB_API int fmb_edge_features(const fmb_model_t* model, const fmb_nl_
 
 // Starts the radial-weight producer of the last interaction (values: which = 0, d/dr: which = 1) on the side stream
 // when the pass will use kept weights (one chunk, no domain restriction); the layer code then waits for it instead of
-// launching it.
-int fork_radial(Ctx& c, int which) {
+// launching it. `tangent_too` (forward pass of a whole force call): the d/dr producer follows the value producer on the
+// side stream at once and `tangent_ready` is what the adjoint waits for -- beside the forward tensor product it costs
+// little, beside the adjoint's node kernels it took 120 of their SMs.
+int fork_radial(Ctx& c, int which, bool tangent_too = false, cudaEvent_t* tangent_ready = nullptr) {
     const int layer = c.m->n_layers - 1;
     if (!overlap_enabled() || !keeps_forward_weights(c, layer) || !c.m->layer[layer].rad_img || !tensor_cores_enabled())
         return FMB_OK;
@@ -550,15 +553,23 @@ int fork_radial(Ctx& c, int which) {
     FMB_TRY(radial_weights(c, layer, 0, which, which, edge_limits(c) + (which == 0 ? 1 : 0), side->stream, side_ctas));
     FMB_CUDA_CHECK(cudaEventRecord(side->join, side->stream));
     c.radial_ready = side->join;
+    if (tangent_too && which == 0 && tangent_ready) {
+        FMB_TRY(radial_weights(c, layer, 0, 1, 1, edge_limits(c), side->stream, side_ctas));
+        FMB_CUDA_CHECK(cudaEventRecord(side->join_tangent, side->stream));
+        *tangent_ready = side->join_tangent;
+    }
     return FMB_OK;
 }
 
-extern "C" FMB_API int fmb_forward(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, fmb_stream_t stream) {
+namespace {
+
+int forward_pass(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, cudaStream_t stream,
+                 cudaEvent_t* tangent_ready) {
     Ctx c;
-    FMB_TRY(make_ctx(c, model, nl, work, (cudaStream_t)stream));
+    FMB_TRY(make_ctx(c, model, nl, work, stream));
     k_edge_limits<<<1, 1, 0, c.stream>>>(nl->edge_row_ptr, c.n0, c.n1, edge_limits(c));
     FMB_LAUNCH_CHECK();
-    FMB_TRY(fork_radial(c, 0));
+    FMB_TRY(fork_radial(c, 0, tangent_ready != nullptr, tangent_ready));
     FMB_TRY(forward_layer(c, 0));
     FMB_TRY(forward_layer(c, 1));
     // readout; the gradient of the last layer's scalars is parked in `basis` (free after the forward pass)
@@ -567,17 +578,34 @@ extern "C" FMB_API int fmb_forward(const fmb_model_t* model, const fmb_nl_t* nl,
     return FMB_OK;
 }
 
-extern "C" FMB_API int fmb_backward(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, fmb_stream_t stream) {
+// `tangent_ready`: set by a forward pass of the same call that has already started the d/dr producer (the edge limits
+// it wrote are still valid too)
+int backward_pass(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, cudaStream_t stream,
+                  cudaEvent_t tangent_ready) {
     Ctx c;
-    FMB_TRY(make_ctx(c, model, nl, work, (cudaStream_t)stream));
-    k_edge_limits<<<1, 1, 0, c.stream>>>(nl->edge_row_ptr, c.n0, c.n1, edge_limits(c));
-    FMB_LAUNCH_CHECK();
-    FMB_TRY(fork_radial(c, 1));
+    FMB_TRY(make_ctx(c, model, nl, work, stream));
+    if (tangent_ready) {
+        c.radial_ready = tangent_ready;
+    } else {
+        k_edge_limits<<<1, 1, 0, c.stream>>>(nl->edge_row_ptr, c.n0, c.n1, edge_limits(c));
+        FMB_LAUNCH_CHECK();
+        FMB_TRY(fork_radial(c, 1));
+    }
     FMB_TRY(backward_layer(c, 1, work->basis, work->d_h, 1));
     FMB_TRY(backward_layer(c, 0, work->d_h, nullptr, 0));
     StageScope scope(c.stream, kStReadout);
     FMB_TRY(reduce_outputs(model, work, c.n1, cell_volume(nl), c.stream));
     return FMB_OK;
+}
+
+}  // namespace
+
+extern "C" FMB_API int fmb_forward(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, fmb_stream_t stream) {
+    return forward_pass(model, nl, work, (cudaStream_t)stream, nullptr);
+}
+
+extern "C" FMB_API int fmb_backward(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work, fmb_stream_t stream) {
+    return backward_pass(model, nl, work, (cudaStream_t)stream, nullptr);
 }
 
 extern "C" FMB_API int fmb_forces_phase(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t* work,
@@ -617,8 +645,9 @@ extern "C" FMB_API int fmb_forces(const fmb_model_t* model, const fmb_nl_t* nl, 
         return FMB_OK;
     }
     FMB_TRY(fmb_edge_features(model, nl, work, positions, stream));
-    FMB_TRY(fmb_forward(model, nl, work, stream));
-    FMB_TRY(fmb_backward(model, nl, work, stream));
+    cudaEvent_t tangent_ready = nullptr;
+    FMB_TRY(forward_pass(model, nl, work, (cudaStream_t)stream, &tangent_ready));
+    FMB_TRY(backward_pass(model, nl, work, (cudaStream_t)stream, tangent_ready));
     return FMB_OK;
 }
 

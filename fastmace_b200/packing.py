@@ -99,6 +99,37 @@ def radial_image(w4: torch.Tensor, channels: int = 128) -> torch.Tensor:
     return image.reshape(-1)
 
 
+def mlp_image(w0: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
+    """The three hidden layers of a radial MLP ([8][64], [64][64], [64][64], fp32, already scaled) as the operand images
+    the tcgen05 edge kernel bulk-copies: a layer [K][64] becomes the tile [64 outputs][K] of its transpose, K-major with
+    the 128-byte swizzle in halves of 32 K (2,048 floats each; the first layer fills 8 of the 32 columns of one half),
+    tf32 values first, then the tf32 remainders. Float offsets: first layer 0 / 2,048, second 4,096 / 8,192, third
+    12,288 / 16,384."""
+    assert tuple(w0.shape) == (8, 64) and tuple(w1.shape) == (64, 64) and tuple(w2.shape) == (64, 64)
+    row = torch.arange(64).view(64, 1)
+    kk = torch.arange(32).view(1, 32)
+    index = ((row >> 3) * 256 + (row & 7) * 32 + ((((kk >> 2) & 7) ^ (row & 7)) << 2) + (kk & 3)).reshape(-1)
+    image = torch.zeros(20480, dtype=torch.float32)
+
+    def parts(w):
+        bt = w.to(torch.float32).t().contiguous()                  # [64 outputs][K]
+        hi = tf32_round(bt)
+        return hi, tf32_round(bt - hi)
+
+    hi, lo = parts(w0)
+    for base, source in ((0, hi), (2048, lo)):
+        tile = torch.zeros(64, 32, dtype=torch.float32)
+        tile[:, :8] = source
+        image[base + index] = tile.reshape(-1)
+    for layer, w in enumerate((w1, w2)):
+        hi, lo = parts(w)
+        for part, source in enumerate((hi, lo)):
+            for half in range(2):
+                base = 4096 + layer * 8192 + part * 4096 + half * 2048
+                image[base + index] = source[:, half * 32:half * 32 + 32].reshape(-1)
+    return image
+
+
 def contraction_terms(spec: MaceSpec, weights, layer: int, species_z):
     """(terms int32 [T, 4], coef float64 [n_species, T, C]) of one layer's symmetric contraction, sorted by output."""
     c = spec.channels
@@ -179,6 +210,9 @@ class PackedModel:
             layer.tc[0] = self._twin(f"l{t}.rad.3", [self.tensors[f"l{t}.rad.3"]])
             if t > 0 and c == 128:
                 layer.rad_img = self._put(f"l{t}.rad.img", radial_image(self.tensors[f"l{t}.rad.3"].cpu(), c))
+            if spec.num_bessel == 8 and tuple(spec.radial_hidden) == (64, 64, 64):
+                layer.mlp_img = self._put(f"l{t}.rad.mlp_img",
+                                          mlp_image(*(self.tensors[f"l{t}.rad.{i}"].cpu() for i in range(3))))
             if t == 0:
                 x_species = h0 @ (w["l0.up.0"] / math.sqrt(c))
                 sc = torch.zeros(len(idx), spec.out_dim(0), c, dtype=torch.float64)
@@ -282,4 +316,4 @@ class PackedModel:
         return ctypes.byref(self.struct)
 
 
-__all__ = ["PackedModel", "contraction_terms", "radial_image", "tensor_core_image", "tensor_core_twin", "tf32_round"]
+__all__ = ["PackedModel", "contraction_terms", "mlp_image", "radial_image", "tensor_core_image", "tensor_core_twin", "tf32_round"]

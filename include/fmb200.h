@@ -161,6 +161,12 @@ typedef struct {
      * tc_img[i] belongs to tc[i] (entry 0 unused), first_img[0 / 1] to first[2 / 3]. Null = not packed. */
     const float* tc_img[9];
     const float* first_img[2];
+    /* The three hidden layers of the radial MLP (rad_w[0..2]) as operand images for the tcgen05 edge kernel: layer
+     * [K][64] -> tile [64 outputs][K] of its transpose, K-major with the 128-byte swizzle in halves of 32 K (2,048
+     * floats; the first layer fills 8 of the 32 columns of one half), tf32 values then tf32 remainders; float offsets
+     * 0 / 2,048 (first), 4,096 / 8,192 (second), 12,288 / 16,384 (third), 20,480 floats in all. Null on any layer =
+     * the warp-level tensor-core kernel evaluates the MLPs from rad_w. */
+    const float* mlp_img;
 } fmb_layer_t;
 
 typedef struct {

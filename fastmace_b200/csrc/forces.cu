@@ -430,7 +430,7 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
         t.row_ptr = c.nl->edge_row_ptr; t.senders = c.nl->edge_index; t.mirror = c.w->mirror; t.x = c.w->x;
         t.edge_sh = c.w->edge_sh; t.edge_vec = c.w->edge_vec; t.tp_w = c.w->tp_w;
         t.tangent_offset = c.chunk * L.n_paths * kC; t.d_mid = c.w->d_mid; t.dxe = c.w->edge_dx; t.qe = c.w->edge_q;
-        t.d_x = c.w->d_x;
+        t.d_x = c.w->d_x; t.whole_list = c.n_chunks == 1; t.error_word = c.w->status;
         for (int k = 0; k < c.n_chunks; ++k) {
             const long long e0 = (long long)k * c.chunk;
             if (c.radial_ready) {

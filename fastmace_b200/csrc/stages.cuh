@@ -109,6 +109,8 @@ struct EdgeAdjointArgs {
     float* dxe;                    // [edges][(lin + 1)^2][C]
     float* qe;                     // [edges][4]
     float* d_x;                    // [n_rows][(lin + 1)^2][C]
+    bool whole_list;               // the launch covers the whole edge list (tp_w holds every edge's weights)
+    uint32_t* error_word;
 };
 int mirror_map(const fmb_nl_t* nl, int32_t* mirror, uint32_t* status, cudaStream_t stream);
 // per-edge adjoint of an interaction after the first for one chunk of edges; after the last chunk the gather of the

@@ -40,6 +40,7 @@ FMB_TP_BACKWARD_SEL(1)
 FMB_TP_BACKWARD_SEL(2)
 
 constexpr int kBatch = 8;
+constexpr int kAdjBatch = 16;          // edges between two CTA barriers of the streamed kernels (their 17 sums meet in shared memory)
 #ifndef FMB_ADJ_STAGES
 #define FMB_ADJ_STAGES 3
 #define FMB_ADJ_MINB 4
@@ -183,8 +184,6 @@ k_tp_adjoint_edges(int n_atoms, int n_rows, int n_valid, long long chunk_e0, lon
 // kAdjStages - 1 edges ahead of the consumers with bulk copies that complete on mbarriers: per edge the weights, their
 // d/dr, the sender's feature rows and the 16 harmonics. A stage is handed back by one arrival per warp.
 constexpr unsigned kAdjSpin = 1u << 20;
-
-constexpr int kAdjBatch = 16;          // edges between two CTA barriers (their 17 sums meet in shared memory)
 
 template <int LIN, int STAGES, int MINB>
 __global__ void __launch_bounds__(kC, MINB)
@@ -376,10 +375,11 @@ k_first_adjoint_edges(int n_rows, int n_valid, int n_add, int n_species, const i
                       const float* __restrict__ edge_sh, const float* __restrict__ edge_vec,
                       const float* __restrict__ hidden, const float* __restrict__ hidden_tangent,
                       const float* __restrict__ d_s, float4* __restrict__ qe) {
-    __shared__ float red[kBatch][4][18];
+    __shared__ float red[2][kAdjBatch][4][18];      // two batches: one barrier per batch (see k_tp_adjoint_stream)
     extern __shared__ float own[];                        // [16][n_species][64]
     const int c = threadIdx.x, k = c & 63, half = c >> 6, warp = c >> 5, lane = c & 31;
     const long long row_floats = (long long)kNSH * n_species * kRadial;
+    int buf = 0;
     for (int a = blockIdx.x; a < n_rows; a += gridDim.x) {
         const long long rb = row_ptr[a], re = row_ptr[a + 1];
         if (a >= n_valid) {
@@ -390,8 +390,8 @@ k_first_adjoint_edges(int n_rows, int n_valid, int n_add, int n_species, const i
         __syncthreads();
         for (int q = c; q < (int)row_floats; q += kC) own[q] = __ldg(d_s + a * row_floats + q);
         __syncthreads();
-        for (long long batch = rb; batch < re; batch += kBatch) {
-            const int nb = (int)min((long long)kBatch, re - batch);
+        for (long long batch = rb; batch < re; batch += kAdjBatch) {
+            const int nb = (int)min((long long)kAdjBatch, re - batch);
             for (int b = 0; b < nb; ++b) {
                 const long long e = batch + b;
                 const int zj = species[senders[e]];
@@ -421,8 +421,8 @@ k_first_adjoint_edges(int n_rows, int n_valid, int n_add, int n_species, const i
                 part[0] += __shfl_xor_sync(0xffffffffu, part[0], 2);
                 part[0] += __shfl_xor_sync(0xffffffffu, part[0], 1);
                 part[8] = warp_sum(part[8]);
-                if ((lane & 3) == 0) red[b][warp][lane >> 2] = part[0];
-                if (lane == 0) red[b][warp][16] = part[8];
+                if ((lane & 3) == 0) red[buf][b][warp][lane >> 2] = part[0];
+                if (lane == 0) red[buf][b][warp][16] = part[8];
             }
             __syncthreads();
             if (c < nb) {
@@ -430,10 +430,10 @@ k_first_adjoint_edges(int n_rows, int n_valid, int n_add, int n_species, const i
                 float g[16];
 #pragma unroll
                 for (int m = 0; m < 8; ++m) {
-                    g[m] = red[c][0][m] + red[c][1][m];
-                    g[8 + m] = red[c][2][m] + red[c][3][m];
+                    g[m] = red[buf][c][0][m] + red[buf][c][1][m];
+                    g[8 + m] = red[buf][c][2][m] + red[buf][c][3][m];
                 }
-                const float drt = red[c][0][16] + red[c][1][16] + red[c][2][16] + red[c][3][16];
+                const float drt = red[buf][c][0][16] + red[buf][c][1][16] + red[buf][c][2][16] + red[buf][c][3][16];
                 const float4 uv = __ldg(reinterpret_cast<const float4*>(edge_vec) + e);
                 float q3[3];
                 edge_vector_gradient(g, drt, uv.x, uv.y, uv.z, uv.w, q3);
@@ -444,7 +444,7 @@ k_first_adjoint_edges(int n_rows, int n_valid, int n_add, int n_species, const i
                 }
                 qe[e] = out;
             }
-            __syncthreads();
+            buf ^= 1;
         }
     }
 }

@@ -103,12 +103,13 @@ k_tp_forward(int n_atoms, int n_rows, long long chunk_e0, long long chunk_edges,
     }
 }
 
-// The same forward pass with the radial weights streamed through shared memory (whole edge list in one chunk): the
-// direct-load kernel above spends its time waiting for the 4 P C bytes of weights per edge, which come from HBM
-// (long-scoreboard stalls: 8.6 per issued instruction). Here a CTA owns a contiguous block of receivers, so its weights
-// are one contiguous range of rows of tp_w, and one thread keeps kFwdStages rows ahead of the consumers with bulk
-// copies that complete on mbarriers; a stage is handed back by one arrival per warp.
-constexpr int kFwdStages = 8;
+// The same forward pass with every per-edge operand streamed through shared memory (whole edge list in one chunk):
+// the direct-load kernel above spends its time waiting for the 4 P C bytes of weights per edge, which come from HBM
+// (long-scoreboard stalls: 8.6 per issued instruction), and the sender's rows. Here a CTA owns a contiguous block of
+// receivers, so its edges are one contiguous range, and one thread keeps kFwdStages - 1 edges ahead of the consumers
+// with bulk copies that complete on mbarriers: per edge the weights, the sender's feature rows and the 16 harmonics.
+// A stage is handed back by one arrival per warp.
+constexpr int kFwdStages = 5;
 constexpr unsigned kFwdSpin = 1u << 20;
 
 template <int LIN>
@@ -118,7 +119,8 @@ k_tp_forward_stream(int n_rows, const int32_t* __restrict__ row_ptr, const int32
                     float* __restrict__ mid, uint32_t* __restrict__ error_word) {
     constexpr int P = TpShape<LIN>::kPaths, IN = TpShape<LIN>::kInDim, MID = TpShape<LIN>::kMidDim;
     constexpr int kRow = P * kC;                       // floats of one edge's weights
-    extern __shared__ __align__(128) float ring[];     // [kFwdStages][kRow]
+    constexpr int kStage = kRow + IN * kC + 16;        // weights, sender rows, harmonics
+    extern __shared__ __align__(128) float ring[];     // [kFwdStages][kStage]
     __shared__ uint64_t bars[2 * kFwdStages];
     __shared__ int abort_sh;
     volatile int* abort_flag = &abort_sh;
@@ -137,17 +139,28 @@ k_tp_forward_stream(int n_rows, const int32_t* __restrict__ row_ptr, const int32
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    long long issued = eb;                                         // thread 0: next edge whose weights to request
+    // thread 0: next edge to request, its stage and the parity its `empty` barrier must have passed; the sender index
+    // is read one request ahead so that its latency is not on the path
+    long long issued = eb;
+    int issue_stage = 0;
+    uint32_t issue_parity = 1;
+    int next_sender = (c == 0 && eb < ee) ? senders[eb] : 0;
     auto issue = [&]() {
-        const long long k = issued - eb;
-        const uint32_t s = (uint32_t)(k % kFwdStages);
-        tc::mbar_wait(bar0 + 8 * (kFwdStages + s), (uint32_t)((k / kFwdStages) & 1) ^ 1u, abort_flag, kFwdSpin);
-        tc::mbar_expect_tx(bar0 + 8 * s, kRow * 4);
-        tc::bulk_load(ring0 + s * (kRow * 4), tp_w + issued * kRow, kRow * 4, bar0 + 8 * s);
+        tc::mbar_wait(bar0 + 8 * (kFwdStages + issue_stage), issue_parity, abort_flag, kFwdSpin);
+        const uint32_t full = bar0 + 8 * issue_stage;
+        const uint32_t dst = ring0 + issue_stage * (kStage * 4);
+        tc::mbar_expect_tx(full, kStage * 4);
+        tc::bulk_load(dst, tp_w + issued * kRow, kRow * 4, full);
+        tc::bulk_load(dst + kRow * 4, x + (long long)next_sender * (IN * kC), IN * kC * 4, full);
+        tc::bulk_load(dst + (kRow + IN * kC) * 4, edge_sh + 16 * issued, 64, full);
         ++issued;
+        if (issued < ee) next_sender = senders[issued];
+        if (++issue_stage == kFwdStages) { issue_stage = 0; issue_parity ^= 1u; }
     };
     if (c == 0)
         while (issued < ee && issued < eb + kFwdStages - 1) issue();
+    int stage = 0;
+    uint32_t parity = 0;
     for (int i = r0; i < r1; ++i) {
         const long long rb = row_ptr[i], re = row_ptr[i + 1];
         float acc[MID];
@@ -156,19 +169,22 @@ k_tp_forward_stream(int n_rows, const int32_t* __restrict__ row_ptr, const int32
         for (long long e = rb; e < re; ++e) {
             // the stage the previous edge used has been handed back by now: refill it
             if (c == 0 && issued < ee && issued < e + kFwdStages) issue();
-            const int s_atom = senders[e];
             float xs[IN], Y[16], w[P];
+            tc::mbar_wait(bar0 + 8 * stage, parity, abort_flag, kFwdSpin);
+            const float* st = ring + stage * kStage;
 #pragma unroll
-            for (int k = 0; k < IN; ++k) xs[k] = __ldg(x + ((long long)s_atom * IN + k) * kC + c);
-            load_sh(edge_sh, e, Y);
-            const long long k = e - eb;
-            const uint32_t s = (uint32_t)(k % kFwdStages);
-            tc::mbar_wait(bar0 + 8 * s, (uint32_t)((k / kFwdStages) & 1), abort_flag, kFwdSpin);
-            const float* st = ring + s * kRow + c;
+            for (int p = 0; p < P; ++p) w[p] = st[p * kC + c];
 #pragma unroll
-            for (int p = 0; p < P; ++p) w[p] = st[p * kC];
+            for (int k = 0; k < IN; ++k) xs[k] = st[kRow + k * kC + c];
+            {
+                const float4* yp = reinterpret_cast<const float4*>(st + kRow + IN * kC);
+                const float4 y0 = yp[0], y1 = yp[1], y2 = yp[2], y3 = yp[3];
+                Y[0] = y0.x; Y[1] = y0.y; Y[2] = y0.z; Y[3] = y0.w; Y[4] = y1.x; Y[5] = y1.y; Y[6] = y1.z; Y[7] = y1.w;
+                Y[8] = y2.x; Y[9] = y2.y; Y[10] = y2.z; Y[11] = y2.w; Y[12] = y3.x; Y[13] = y3.y; Y[14] = y3.z; Y[15] = y3.w;
+            }
             __syncwarp();
-            if (lane == 0) tc::mbar_arrive(bar0 + 8 * (kFwdStages + s));
+            if (lane == 0) tc::mbar_arrive(bar0 + 8 * (kFwdStages + stage));
+            if (++stage == kFwdStages) { stage = 0; parity ^= 1u; }
             tp_forward<LIN>(xs, Y, w, acc);
         }
         float* out = mid + ((long long)i * MID) * kC + c;
@@ -489,8 +505,6 @@ int persistent_grid(const void* kernel, int n_atoms) {
 
 }  // namespace
 
-// FMB_TP_STREAM=0 keeps the direct-load forward kernel (A/B tests)
-
 int tp_forward_launch(const TpArgs& t, cudaStream_t stream) {
     if (t.n_rows <= 0) return FMB_OK;
 #define FMB_FWD(LIN_, SP_)                                                                                             \
@@ -502,7 +516,7 @@ int tp_forward_launch(const TpArgs& t, cudaStream_t stream) {
     }
 #define FMB_FWD_STREAM(LIN_)                                                                                           \
     {                                                                                                                  \
-        constexpr int smem = kFwdStages * TpShape<LIN_>::kPaths * kC * 4;                                              \
+        constexpr int smem = kFwdStages * (TpShape<LIN_>::kPaths * kC + TpShape<LIN_>::kInDim * kC + 16) * 4;          \
         static int grid_cap = 0;                                                                                       \
         FMB_CUDA_CHECK(opt_in_shared_memory((const void*)k_tp_forward_stream<LIN_>, smem));                            \
         if (grid_cap == 0) {                                                                                           \

@@ -31,12 +31,14 @@ namespace {
 using namespace tc;
 
 constexpr int kWsThreads = 160;          // 4 loader / epilogue warps + the control warp
-constexpr int kWsStages = 2;
+constexpr int kWsMaxStages = 2;
 constexpr int kWsTK = 32;                // K elements per stage
 constexpr int kWsPiece = 128 * kWsTK * 4;        // 16 KB: one of the value / remainder parts of an operand stage
-constexpr int kWsStageBytes = 6 * kWsPiece;      // A value, A remainder, W value (2 pieces), W remainder (2 pieces)
-constexpr int kWsWHi = 2 * kWsPiece, kWsWLo = 4 * kWsPiece;      // offsets of the weight parts inside a stage
-constexpr int kWsBytes = kWsStages * kWsStageBytes + 256 + 1024;
+// A stage: A value, A remainder, then the W value and W remainder pieces -- one of each for a launch of 128-column
+// tiles (64 KB), two of each where column tiles are paired (96 KB). A launch of at most one wave runs two stages per
+// CTA; a larger one runs a single stage and, being small, two or three CTAs per SM, so that the tiles of what would
+// be the second wave overlap the first instead of waiting for it.
+constexpr int kWsTail = 256 + 1024;
 constexpr unsigned kWsSpin = 1u << 20;
 constexpr int kWsMaxProblems = 8;
 
@@ -66,6 +68,7 @@ struct WsBatch {
     WsProblem p[kWsMaxProblems];
     int count;
     int wide;                    // pair adjacent column tiles (128 x 256 per CTA) where a problem has two or more
+    int stages;                  // operand stages per CTA (1 or 2)
     uint32_t* error_word;
 };
 
@@ -87,11 +90,15 @@ __device__ __forceinline__ void add_to_global(float* dst, const float4& v) {
 // barrier slots: b_full[2], a_full[2], empty[2], acc
 constexpr int kWsBFull = 0, kWsAFull = 2, kWsEmpty = 4, kWsAcc = 6;
 
-__global__ void __launch_bounds__(kWsThreads, 1)
+__global__ void __launch_bounds__(kWsThreads, 3)
 k_gemm_ws(const __grid_constant__ WsBatch batch) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kWsStages * kWsStageBytes);
+    const int stages = batch.stages;
+    const int w_pieces_launch = batch.wide ? 2 : 1;
+    const uint32_t stage_bytes = (uint32_t)(2 + 2 * w_pieces_launch) * kWsPiece;
+    const uint32_t w_hi_off = 2 * kWsPiece, w_lo_off = (uint32_t)(2 + w_pieces_launch) * kWsPiece;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + stages * stage_bytes);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const uint32_t bar0 = smem_u32(bars);
@@ -130,7 +137,7 @@ k_gemm_ws(const __grid_constant__ WsBatch batch) {
     const int chunks = k / kWsTK;
 
     if (tid == 0) {
-        for (int s = 0; s < kWsStages; ++s) {
+        for (int s = 0; s < kWsMaxStages; ++s) {
             mbar_init(bar(kWsBFull + s), 1);
             mbar_init(bar(kWsAFull + s), 4);
             mbar_init(bar(kWsEmpty + s), 1);
@@ -139,7 +146,8 @@ k_gemm_ws(const __grid_constant__ WsBatch batch) {
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 4) tmem_alloc(smem_u32(tmem_slot), 256);
+    const uint32_t tmem_columns = batch.wide ? 256u : 128u;
+    if (warp == 4) tmem_alloc(smem_u32(tmem_slot), tmem_columns);
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
@@ -154,26 +162,26 @@ k_gemm_ws(const __grid_constant__ WsBatch batch) {
             int requested = 0;
             for (int kc = 0; kc < chunks; ++kc) {
                 // keep the weight pieces of the next stages on their way
-                while (requested < chunks && requested < kc + kWsStages) {
-                    const int s = requested % kWsStages;
-                    mbar_wait(bar(kWsEmpty + s), ((requested / kWsStages) & 1) ^ 1, abort_flag, kWsSpin);
+                while (requested < chunks && requested < kc + stages) {
+                    const int s = requested % stages;
+                    mbar_wait(bar(kWsEmpty + s), ((requested / stages) & 1) ^ 1, abort_flag, kWsSpin);
                     mbar_expect_tx(bar(kWsBFull + s), (tn >> 7) * 2 * kWsPiece);
-                    const uint32_t dst = stage0 + s * kWsStageBytes;
+                    const uint32_t dst = stage0 + s * stage_bytes;
                     for (int half = 0; half < (tn >> 7); ++half) {
                         const float* piece = pieces + ((size_t)half * chunks + requested) * piece_floats;
-                        bulk_load(dst + kWsWHi + half * kWsPiece, piece, kWsPiece, bar(kWsBFull + s));
-                        bulk_load(dst + kWsWLo + half * kWsPiece, piece + kWsPiece / 4, kWsPiece, bar(kWsBFull + s));
+                        bulk_load(dst + w_hi_off + half * kWsPiece, piece, kWsPiece, bar(kWsBFull + s));
+                        bulk_load(dst + w_lo_off + half * kWsPiece, piece + kWsPiece / 4, kWsPiece, bar(kWsBFull + s));
                     }
                     ++requested;
                 }
-                const int s = kc % kWsStages;
-                const uint32_t parity = (kc / kWsStages) & 1;
+                const int s = kc % stages;
+                const uint32_t parity = (kc / stages) & 1;
                 mbar_wait(bar(kWsBFull + s), parity, abort_flag, kWsSpin);
                 mbar_wait(bar(kWsAFull + s), parity, abort_flag, kWsSpin);
                 fence_after_sync();
-                const uint32_t base = stage0 + s * kWsStageBytes;
+                const uint32_t base = stage0 + s * stage_bytes;
                 const uint64_t a_hi = make_desc(base), a_lo = make_desc(base + kWsPiece);
-                const uint64_t w_hi = make_desc(base + kWsWHi), w_lo = make_desc(base + kWsWLo);
+                const uint64_t w_hi = make_desc(base + w_hi_off), w_lo = make_desc(base + w_lo_off);
 #pragma unroll
                 for (int k8 = 0; k8 < 4; ++k8)
                     mma_tf32(tmem_base, a_lo + (uint64_t)(2 * k8), w_hi + (uint64_t)(2 * k8), idesc, (kc > 0 || k8 > 0) ? 1 : 0);
@@ -205,9 +213,9 @@ k_gemm_ws(const __grid_constant__ WsBatch batch) {
 #pragma unroll
                 for (int j = 0; j < 2; ++j) cur[i][j] = next[i][j];
             if (kc + 1 < chunks) ws_fetch(src, ok, kc + 1, ld_q, next);
-            const int s = kc % kWsStages;
-            mbar_wait(bar(kWsEmpty + s), ((kc / kWsStages) & 1) ^ 1, abort_flag, kWsSpin);
-            uint8_t* hi_tile = smem + s * kWsStageBytes;
+            const int s = kc % stages;
+            mbar_wait(bar(kWsEmpty + s), ((kc / stages) & 1) ^ 1, abort_flag, kWsSpin);
+            uint8_t* hi_tile = smem + s * stage_bytes;
             uint8_t* lo_tile = hi_tile + kWsPiece;
 #pragma unroll
             for (int i = 0; i < 4; ++i)
@@ -283,7 +291,7 @@ k_gemm_ws(const __grid_constant__ WsBatch batch) {
     if (warp == 4) {
         __syncwarp();
         if (lane == 0 && *abort_flag && batch.error_word) atomicOr(batch.error_word, FMB_STATUS_TENSOR_TIMEOUT);
-        tmem_free(tmem_base, 256);
+        tmem_free(tmem_base, tmem_columns);
     }
 }
 
@@ -303,6 +311,13 @@ int gemm_ws_batch(const GemmArgs* list, int count, cudaStream_t stream) {
     int narrow_tiles = 0;
     for (int q = 0; q < count; ++q) narrow_tiles += ceil_div(std::max(list[q].m, 0), 128) * (list[q].n / 128);
     batch.wide = narrow_tiles > sm_count ? 1 : 0;
+    // pairing is for launches whose 128-column tiles would not fit one wave even at three CTAs per SM
+    if (batch.wide) {
+        bool any_pair = false;
+        for (int q = 0; q < count; ++q) any_pair = any_pair || list[q].n >= 256;
+        if (!any_pair) batch.wide = 0;
+    }
+    batch.stages = narrow_tiles > sm_count ? 1 : kWsMaxStages;
     int tiles = 0;
     for (int q = 0; q < count; ++q) {
         const GemmArgs& g = list[q];
@@ -321,8 +336,9 @@ int gemm_ws_batch(const GemmArgs* list, int count, cudaStream_t stream) {
         tiles += ceil_div(std::max(g.m, 0), 128) * (n128 - (batch.wide ? n128 / 2 : 0));
     }
     if (tiles == 0) return FMB_OK;
-    FMB_CUDA_CHECK(opt_in_shared_memory((const void*)k_gemm_ws, kWsBytes));
-    k_gemm_ws<<<tiles, kWsThreads, kWsBytes, stream>>>(batch);
+    const int smem_bytes = batch.stages * (batch.wide ? 6 : 4) * kWsPiece + kWsTail;
+    FMB_CUDA_CHECK(opt_in_shared_memory((const void*)k_gemm_ws, kWsMaxStages * 6 * kWsPiece + kWsTail));
+    k_gemm_ws<<<tiles, kWsThreads, smem_bytes, stream>>>(batch);
     FMB_LAUNCH_CHECK();
     return FMB_OK;
 }

@@ -8,7 +8,7 @@
 //     K-major 128-byte-swizzled operand layout, 32 KB per (128 columns, 32 K) piece, and one thread brings the pieces
 //     in with bulk copies that complete on an mbarrier;
 //   * four loader warps hold the activation rows of the next K chunk in registers while they split and store the
-//     current one (two shared-memory stages), so the loads of chunk k + 1 are in flight during chunk k;
+//     current one, so the loads of chunk k + 1 are in flight during chunk k;
 //   * the same thread that issues the bulk copies issues the MMAs (M = 128 rows, N = 128, K = 8 each; 12 per chunk)
 //     and commits them to the stage's `empty` barrier; after the last chunk it commits to the accumulator barrier and
 //     the loader warps turn into the epilogue (strided rows, accumulate, species mask): the accumulator rows are
@@ -72,15 +72,13 @@ struct WsBatch {
     uint32_t* error_word;
 };
 
-// the loader thread's share (4 rows x 2 float4) of K chunk kc
-__device__ __forceinline__ void ws_fetch(const float* const (&src)[4], const bool (&ok)[4], int kc, int ld_q,
-                                         float4 (&out)[4][2]) {
+// the loader thread's share of K chunk kc: one float4 of each of 8 rows; the 8 lanes that share a row read the whole
+// 128-byte line of the chunk, so a warp instruction touches 4 full lines
+__device__ __forceinline__ void ws_fetch(const float* const (&src)[8], const bool (&ok)[8], int kc, int ld_q,
+                                         float4 (&out)[8]) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
-            out[i][j] = ok[i] ? __ldg(reinterpret_cast<const float4*>(src[i] + kc * kWsTK) + ld_q + 4 * j)
-                              : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = 0; i < 8; ++i)
+        out[i] = ok[i] ? __ldg(reinterpret_cast<const float4*>(src[i] + kc * kWsTK) + ld_q) : make_float4(0.f, 0.f, 0.f, 0.f);
 }
 
 __device__ __forceinline__ void add_to_global(float* dst, const float4& v) {
@@ -194,41 +192,37 @@ k_gemm_ws(const __grid_constant__ WsBatch batch) {
             mma_commit(bar(kWsAcc));
         }
     } else {
-        // ------------------------------------------------------------------ loaders: 32 rows x 8 float4 per sweep
-        const int ld_row = warp * 8 + (lane & 7), ld_q = lane >> 3;
-        const float* src[4];
-        bool ok[4];
+        // ------------------------------------------------------------------ loaders: a warp takes 32 rows
+        const int ld_row = warp * 32 + (lane >> 3), ld_q = lane & 7;
+        const float* src[8];
+        bool ok[8];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int row = row0 + ld_row + 32 * i;
+        for (int i = 0; i < 8; ++i) {
+            const int row = row0 + ld_row + 4 * i;
             ok[i] = row < m;
             src[i] = a + (ok[i] ? amap(row) : 0);
         }
-        float4 next[4][2];
+        float4 next[8];
         ws_fetch(src, ok, 0, ld_q, next);
         for (int kc = 0; kc < chunks; ++kc) {
-            float4 cur[4][2];
+            float4 cur[8];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-#pragma unroll
-                for (int j = 0; j < 2; ++j) cur[i][j] = next[i][j];
+            for (int i = 0; i < 8; ++i) cur[i] = next[i];
             if (kc + 1 < chunks) ws_fetch(src, ok, kc + 1, ld_q, next);
             const int s = kc % stages;
             mbar_wait(bar(kWsEmpty + s), ((kc / stages) & 1) ^ 1, abort_flag, kWsSpin);
             uint8_t* hi_tile = smem + s * stage_bytes;
             uint8_t* lo_tile = hi_tile + kWsPiece;
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-#pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    const float4 v = cur[i][j];
-                    const float4 hi = make_float4(tf32_rna(v.x), tf32_rna(v.y), tf32_rna(v.z), tf32_rna(v.w));
-                    const float4 lo = make_float4(tf32_rna(v.x - hi.x), tf32_rna(v.y - hi.y), tf32_rna(v.z - hi.z),
-                                                  tf32_rna(v.w - hi.w));
-                    const uint32_t off = tile_offset<128>(ld_row + 32 * i, (ld_q + 4 * j) * 4);
-                    *reinterpret_cast<float4*>(hi_tile + off) = hi;
-                    *reinterpret_cast<float4*>(lo_tile + off) = lo;
-                }
+            for (int i = 0; i < 8; ++i) {
+                const float4 v = cur[i];
+                const float4 hi = make_float4(tf32_rna(v.x), tf32_rna(v.y), tf32_rna(v.z), tf32_rna(v.w));
+                const float4 lo = make_float4(tf32_rna(v.x - hi.x), tf32_rna(v.y - hi.y), tf32_rna(v.z - hi.z),
+                                              tf32_rna(v.w - hi.w));
+                const uint32_t off = tile_offset<128>(ld_row + 4 * i, ld_q * 4);
+                *reinterpret_cast<float4*>(hi_tile + off) = hi;
+                *reinterpret_cast<float4*>(lo_tile + off) = lo;
+            }
             fence_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(kWsAFull + s));

@@ -251,12 +251,15 @@ k_gemm_ws(const __grid_constant__ WsBatch batch) {
                 fence_after_sync();
             }
 #pragma unroll
-            for (int col = 0; col < 128; col += 16) {
-                float v[16];
-                tmem_load<16>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c0 + col), v);
+            for (int col = 0; col < 128; col += 32) {
+                float v[16], u[16];
+                const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c0 + col);
+                tmem_load_16x2(taddr, taddr + 16, v, u);
 #pragma unroll
-                for (int q = 0; q < 4; ++q)
+                for (int q = 0; q < 4; ++q) {
                     turn[lane * 32 + (((col >> 2) + q) ^ lane)] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                    turn[lane * 32 + (((col >> 2) + 4 + q) ^ lane)] = make_float4(u[4 * q], u[4 * q + 1], u[4 * q + 2], u[4 * q + 3]);
+                }
             }
             __syncwarp();
             int q = q0, rem = rem0;

@@ -366,77 +366,76 @@ k_gather_dx(int n_rows, int n_source, const int32_t* __restrict__ row_ptr, const
     }
 }
 
-// First interaction (reassociated form), per-edge: the receiver's gradient block [16][Z][64] in shared memory,
+// First interaction (reassociated form), per edge: the receiver's gradient block [16][Z][64] in shared memory,
 // dE/dY[lm] = sum_k dS[lm, z_j, k] hidden[k], dE/dr = sum_k hidden'[k] sum_lm dS[lm, z_j, k] Y[lm]; the edge-vector
-// gradient is added to qe (rows below n_add, which the later interaction wrote) or stored.
-__global__ void __launch_bounds__(kC)
-k_first_adjoint_edges(int n_rows, int n_valid, int n_add, int n_species, const int32_t* __restrict__ row_ptr,
-                      const int32_t* __restrict__ senders, const int32_t* __restrict__ species,
-                      const float* __restrict__ edge_sh, const float* __restrict__ edge_vec,
-                      const float* __restrict__ hidden, const float* __restrict__ hidden_tangent,
-                      const float* __restrict__ d_s, float4* __restrict__ qe) {
-    __shared__ float red[2][kAdjBatch][4][18];      // two batches: one barrier per batch (see k_tp_adjoint_stream)
-    extern __shared__ float own[];                        // [16][n_species][64]
-    const int c = threadIdx.x, k = c & 63, half = c >> 6, warp = c >> 5, lane = c & 31;
+// gradient is added to qe (rows below n_add, which the later interaction wrote) or stored. A thread takes an edge and
+// four harmonics: the sums over the 64 radial features run inside the thread -- the features of 16 edges are staged in
+// shared memory -- and only the four threads of an edge meet at the end, by shuffles inside a group of four lanes. (A
+// thread per (feature, eight harmonics) spent 137 instructions per warp and edge on 16 FMAs per thread: channel
+// reductions by shuffle and two barriers per eight edges; 72 -> 45 us.)
+constexpr int kFaPass = 16;                       // edges per pass
+constexpr int kFaThreads = 4 * kFaPass;
+constexpr int kFaLd = kRadial + 1;                // row stride of the staged features (conflict-free across edges)
+
+__global__ void __launch_bounds__(kFaThreads)
+k_first_adjoint_rows(int n_rows, int n_valid, int n_add, int n_species, const int32_t* __restrict__ row_ptr,
+                     const int32_t* __restrict__ senders, const int32_t* __restrict__ species,
+                     const float* __restrict__ edge_sh, const float* __restrict__ edge_vec,
+                     const float* __restrict__ hidden, const float* __restrict__ hidden_tangent,
+                     const float* __restrict__ d_s, float4* __restrict__ qe) {
+    __shared__ float hs[kFaPass][kFaLd], hps[kFaPass][kFaLd];
+    extern __shared__ float own[];                        // [16][n_species][kFaLd]: the four harmonics groups and the
+                                                          // species of a warp's edges fall into different banks
+    const int c = threadIdx.x, slot = c >> 2, grp = c & 3, lane = c & 31;
     const long long row_floats = (long long)kNSH * n_species * kRadial;
-    int buf = 0;
+    const int lm_stride = n_species * kFaLd;
     for (int a = blockIdx.x; a < n_rows; a += gridDim.x) {
         const long long rb = row_ptr[a], re = row_ptr[a + 1];
         if (a >= n_valid) {
             if (a >= n_add)
-                for (long long e = rb + c; e < re; e += kC) qe[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (long long e = rb + c; e < re; e += kFaThreads) qe[e] = make_float4(0.f, 0.f, 0.f, 0.f);
             continue;
         }
-        __syncthreads();
-        for (int q = c; q < (int)row_floats; q += kC) own[q] = __ldg(d_s + a * row_floats + q);
-        __syncthreads();
-        for (long long batch = rb; batch < re; batch += kAdjBatch) {
-            const int nb = (int)min((long long)kAdjBatch, re - batch);
-            for (int b = 0; b < nb; ++b) {
-                const long long e = batch + b;
-                const int zj = species[senders[e]];
-                const float h = __ldg(hidden + e * kRadial + k), hp = __ldg(hidden_tangent + e * kRadial + k);
-                const float4* yp = reinterpret_cast<const float4*>(edge_sh + 16 * e + 8 * half);
-                const float4 y0 = __ldg(yp), y1 = __ldg(yp + 1);
-                const float Y[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
-                float part[9];
-                float dh = 0.0f;
-#pragma unroll
-                for (int m = 0; m < 8; ++m) {
-                    const float cc = own[((8 * half + m) * n_species + zj) * kRadial + k];
-                    part[m] = cc * h;
-                    dh = fmaf(cc, Y[m], dh);
-                }
-                part[8] = dh * hp;
-#pragma unroll
-                for (int halfw = 4, bit = 16; halfw >= 1; halfw >>= 1, bit >>= 1) {
-                    const bool upper = (lane & bit) != 0;
-#pragma unroll
-                    for (int m = 0; m < halfw; ++m) {
-                        const float keep = upper ? part[m + halfw] : part[m];
-                        const float send = upper ? part[m] : part[m + halfw];
-                        part[m] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
-                    }
-                }
-                part[0] += __shfl_xor_sync(0xffffffffu, part[0], 2);
-                part[0] += __shfl_xor_sync(0xffffffffu, part[0], 1);
-                part[8] = warp_sum(part[8]);
-                if ((lane & 3) == 0) red[buf][b][warp][lane >> 2] = part[0];
-                if (lane == 0) red[buf][b][warp][16] = part[8];
+        __syncthreads();                                  // the previous row's block is no longer read
+        for (int q = c; q < (int)row_floats; q += kFaThreads) own[(q >> 6) * kFaLd + (q & 63)] = __ldg(d_s + a * row_floats + q);
+        for (long long batch = rb; batch < re; batch += kFaPass) {
+            const int nb = (int)min((long long)kFaPass, re - batch);
+            __syncthreads();                              // the previous pass is done with the staged features
+            for (int q = c; q < nb * kRadial; q += kFaThreads) {
+                const int el = q >> 6, k = q & 63;
+                hs[el][k] = __ldg(hidden + (batch + el) * kRadial + k);
+                hps[el][k] = __ldg(hidden_tangent + (batch + el) * kRadial + k);
             }
             __syncthreads();
-            if (c < nb) {
-                const long long e = batch + c;
-                float g[16];
-#pragma unroll
-                for (int m = 0; m < 8; ++m) {
-                    g[m] = red[buf][c][0][m] + red[buf][c][1][m];
-                    g[8 + m] = red[buf][c][2][m] + red[buf][c][3][m];
+            const bool live = slot < nb;
+            const long long e = batch + (live ? slot : 0);
+            float g[4] = {0.f, 0.f, 0.f, 0.f}, dr = 0.0f;
+            if (live) {
+                const int zj = species[senders[e]];
+                const float4 y = __ldg(reinterpret_cast<const float4*>(edge_sh + 16 * e) + grp);
+                const float* ds = own + (4 * grp * n_species + zj) * kFaLd;       // harmonics 4 grp .. 4 grp + 3
+#pragma unroll 8
+                for (int k = 0; k < kRadial; ++k) {
+                    const float h = hs[slot][k], hp = hps[slot][k];
+                    const float d0 = ds[k], d1 = ds[lm_stride + k], d2 = ds[2 * lm_stride + k], d3 = ds[3 * lm_stride + k];
+                    g[0] = fmaf(d0, h, g[0]); g[1] = fmaf(d1, h, g[1]); g[2] = fmaf(d2, h, g[2]); g[3] = fmaf(d3, h, g[3]);
+                    const float dh = fmaf(d0, y.x, fmaf(d1, y.y, fmaf(d2, y.z, d3 * y.w)));
+                    dr = fmaf(dh, hp, dr);
                 }
-                const float drt = red[buf][c][0][16] + red[buf][c][1][16] + red[buf][c][2][16] + red[buf][c][3][16];
+            }
+            // the four threads of an edge exchange their harmonics' gradients and add up the radial one
+            float all[16];
+            const int base = lane & ~3;
+#pragma unroll
+            for (int src = 0; src < 4; ++src)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) all[4 * src + i] = __shfl_sync(0xffffffffu, g[i], base + src);
+            dr += __shfl_xor_sync(0xffffffffu, dr, 1);
+            dr += __shfl_xor_sync(0xffffffffu, dr, 2);
+            if (live && grp == 0) {
                 const float4 uv = __ldg(reinterpret_cast<const float4*>(edge_vec) + e);
                 float q3[3];
-                edge_vector_gradient(g, drt, uv.x, uv.y, uv.z, uv.w, q3);
+                edge_vector_gradient(all, dr, uv.x, uv.y, uv.z, uv.w, q3);
                 float4 out = make_float4(q3[0], q3[1], q3[2], 0.0f);
                 if (a < n_add) {
                     const float4 old = qe[e];
@@ -444,7 +443,6 @@ k_first_adjoint_edges(int n_rows, int n_valid, int n_add, int n_species, const i
                 }
                 qe[e] = out;
             }
-            buf ^= 1;
         }
     }
 }
@@ -569,10 +567,10 @@ int gather_sender_gradient(const EdgeAdjointArgs& t, cudaStream_t stream) {
 
 int first_adjoint_edges(const FirstArgs& f, int n_add, float* qe, cudaStream_t stream) {
     if (f.n_rows <= 0) return FMB_OK;
-    const size_t smem = (size_t)f.n_species * kNSH * kRadial * sizeof(float);
+    const size_t smem = (size_t)f.n_species * kNSH * kFaLd * sizeof(float);
     static int grid_cap = 0;
-    if (grid_cap == 0) grid_cap = grid_for((const void*)k_first_adjoint_edges, 1 << 30, kC, smem);
-    k_first_adjoint_edges<<<f.n_rows < grid_cap ? f.n_rows : grid_cap, kC, smem, stream>>>(
+    if (grid_cap == 0) grid_cap = grid_for((const void*)k_first_adjoint_rows, 1 << 30, kFaThreads, smem);
+    k_first_adjoint_rows<<<f.n_rows < grid_cap ? f.n_rows : grid_cap, kFaThreads, smem, stream>>>(
         f.n_rows, f.n_valid, n_add, f.n_species, f.row_ptr, f.senders, f.species, f.edge_sh, f.edge_vec, f.hidden,
         f.hidden_tangent, f.d_s, reinterpret_cast<float4*>(qe));
     FMB_LAUNCH_CHECK();

@@ -342,42 +342,60 @@ k_tp_backward(int n_atoms, int n_rows, int n_valid, int fresh_from, long long ch
 // No [E, P*C] weights, no tensor product per edge.
 constexpr int kFirstZ = FMB_MAX_SPECIES;
 
-// CTA per receiver, thread = (k = tid & 63, half = tid >> 6 -> harmonics 8 * half .. 8 * half + 7); the tile is
-// accumulated in shared memory at [z][lm][k], every thread owning its own cells.
+// CTA per receiver, thread = (k = tid & 63, half = tid >> 6 -> harmonics 8 * half .. 8 * half + 7). The sums live in
+// registers, one set per sender species (an edge adds into the set of its sender's species through a 0 / 1 factor, so
+// that no index depends on data), and the operands of four edges are requested together: the chain sender -> species
+// -> features is three dependent loads, which a loop over single edges pays in full for every edge (11 warps stalled
+// on loads per issued instruction in the version that accumulated in shared memory).
+template <int Z>
 __global__ void __launch_bounds__(kC)
-k_first_accumulate(int n_rows, int n_species, const long long* __restrict__ count_ptr,
-                   const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ senders,
+k_first_accumulate(int n_rows, const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ senders,
                    const int32_t* __restrict__ species, const float* __restrict__ edge_sh,
                    const float* __restrict__ hidden, float* __restrict__ s_out) {
-    extern __shared__ float tile[];                       // [n_species][16][64]
+    constexpr int kAhead = 4;
     const int k = threadIdx.x & 63, half = threadIdx.x >> 6;
     for (int i = blockIdx.x; i < n_rows; i += gridDim.x) {
-        for (int q = threadIdx.x; q < n_species * kNSH * kRadial; q += kC) tile[q] = 0.0f;
-        __syncthreads();
+        float acc[Z][8];
+#pragma unroll
+        for (int z = 0; z < Z; ++z)
+#pragma unroll
+            for (int m = 0; m < 8; ++m) acc[z][m] = 0.0f;
         const long long rb = row_ptr[i], re = row_ptr[i + 1];
-        for (long long e = rb; e < re; ++e) {
-            const int z = species[senders[e]];
-            const float h = __ldg(hidden + e * kRadial + k);
-            const float4* yp = reinterpret_cast<const float4*>(edge_sh + 16 * e + 8 * half);
-            const float4 y0 = __ldg(yp), y1 = __ldg(yp + 1);
-            float* cell = tile + ((z * kNSH + 8 * half) * kRadial) + k;
-            cell[0 * kRadial] = fmaf(y0.x, h, cell[0 * kRadial]);
-            cell[1 * kRadial] = fmaf(y0.y, h, cell[1 * kRadial]);
-            cell[2 * kRadial] = fmaf(y0.z, h, cell[2 * kRadial]);
-            cell[3 * kRadial] = fmaf(y0.w, h, cell[3 * kRadial]);
-            cell[4 * kRadial] = fmaf(y1.x, h, cell[4 * kRadial]);
-            cell[5 * kRadial] = fmaf(y1.y, h, cell[5 * kRadial]);
-            cell[6 * kRadial] = fmaf(y1.z, h, cell[6 * kRadial]);
-            cell[7 * kRadial] = fmaf(y1.w, h, cell[7 * kRadial]);
+        for (long long e0 = rb; e0 < re; e0 += kAhead) {
+            int zs[kAhead];
+            float h[kAhead];
+            float4 y0[kAhead], y1[kAhead];
+#pragma unroll
+            for (int q = 0; q < kAhead; ++q) {
+                const bool live = e0 + q < re;
+                const long long e = live ? e0 + q : rb;
+                zs[q] = species[senders[e]];
+                h[q] = live ? __ldg(hidden + e * kRadial + k) : 0.0f;
+                const float4* yp = reinterpret_cast<const float4*>(edge_sh + 16 * e + 8 * half);
+                y0[q] = __ldg(yp);
+                y1[q] = __ldg(yp + 1);
+            }
+#pragma unroll
+            for (int q = 0; q < kAhead; ++q)
+#pragma unroll
+                for (int z = 0; z < Z; ++z) {
+                    const float hz = zs[q] == z ? h[q] : 0.0f;
+                    acc[z][0] = fmaf(y0[q].x, hz, acc[z][0]);
+                    acc[z][1] = fmaf(y0[q].y, hz, acc[z][1]);
+                    acc[z][2] = fmaf(y0[q].z, hz, acc[z][2]);
+                    acc[z][3] = fmaf(y0[q].w, hz, acc[z][3]);
+                    acc[z][4] = fmaf(y1[q].x, hz, acc[z][4]);
+                    acc[z][5] = fmaf(y1[q].y, hz, acc[z][5]);
+                    acc[z][6] = fmaf(y1[q].z, hz, acc[z][6]);
+                    acc[z][7] = fmaf(y1[q].w, hz, acc[z][7]);
+                }
         }
-        __syncthreads();
         // global layout [i][lm][z][k]: the K = n_species * 64 values of one (atom, harmonic) row are contiguous
-        float* out = s_out + (long long)i * kNSH * n_species * kRadial;
-        for (int q = threadIdx.x; q < n_species * kNSH * kRadial; q += kC) {
-            const int kk = q & 63, z = (q >> 6) % n_species, lm = q / (64 * n_species);
-            out[q] = tile[(z * kNSH + lm) * kRadial + kk];
-        }
-        __syncthreads();
+        float* out = s_out + (long long)i * kNSH * Z * kRadial + k;
+#pragma unroll
+        for (int z = 0; z < Z; ++z)
+#pragma unroll
+            for (int m = 0; m < 8; ++m) out[((8 * half + m) * Z + z) * kRadial] = acc[z][m];
     }
 }
 
@@ -591,10 +609,18 @@ namespace fmb {
 int first_accumulate_launch(const FirstArgs& f, cudaStream_t stream) {
     if (f.n_rows <= 0) return FMB_OK;
     FMB_REQUIRE(f.n_species >= 1 && f.n_species <= kFirstZ, "first layer: too many species");
-    const size_t smem = (size_t)f.n_species * kNSH * kRadial * sizeof(float);
-    const int grid = persistent_grid((const void*)k_first_accumulate, f.n_rows);
-    k_first_accumulate<<<grid, kC, smem, stream>>>(f.n_rows, f.n_species, f.count, f.row_ptr, f.senders, f.species,
-                                                   f.edge_sh, f.hidden, f.s);
+#define FMB_FIRST(Z_)                                                                                              \
+    case Z_: {                                                                                                     \
+        const int grid = persistent_grid((const void*)k_first_accumulate<Z_>, f.n_rows);                           \
+        k_first_accumulate<Z_><<<grid, kC, 0, stream>>>(f.n_rows, f.row_ptr, f.senders, f.species, f.edge_sh,     \
+                                                        f.hidden, f.s);                                            \
+        break;                                                                                                     \
+    }
+    switch (f.n_species) {
+        FMB_FIRST(1) FMB_FIRST(2) FMB_FIRST(3) FMB_FIRST(4) FMB_FIRST(5) FMB_FIRST(6) FMB_FIRST(7) FMB_FIRST(8)
+        default: FMB_REQUIRE(false, "first layer: too many species");
+    }
+#undef FMB_FIRST
     FMB_LAUNCH_CHECK();
     return FMB_OK;
 }

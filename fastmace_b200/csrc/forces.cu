@@ -547,7 +547,7 @@ int fork_radial(Ctx& c, int which, bool tangent_too = false, cudaEvent_t* tangen
         return FMB_OK;
     SideStream* side = side_stream(c.stream);
     if (!side) return FMB_OK;
-    constexpr int side_ctas = 120;      // the SMs it leaves free serve the node kernels beside it (measured best of 64 .. 148)
+    constexpr int side_ctas = 136;      // the SMs it leaves free serve the node kernels beside it (104 .. 148 measure alike)
     FMB_CUDA_CHECK(cudaEventRecord(side->fork, c.stream));
     FMB_CUDA_CHECK(cudaStreamWaitEvent(side->stream, side->fork, 0));
     FMB_TRY(radial_weights(c, layer, 0, which, which, edge_limits(c) + (which == 0 ? 1 : 0), side->stream, side_ctas));

@@ -154,6 +154,11 @@ __global__ void k_edge_limits(const int32_t* __restrict__ row_ptr, int n0, int n
 }
 
 long long* edge_limits(const Ctx& c) { return reinterpret_cast<long long*>(c.w->partial + 4096); }
+// every atom gets every row: both limits are the edge count itself and nothing has to be computed
+bool plain_rows(const Ctx& c) { return c.n0 == c.n && c.n1 == c.n; }
+const long long* edge_limit(const Ctx& c, int which) {
+    return plain_rows(c) ? (const long long*)c.nl->count : edge_limits(c) + which;
+}
 
 // first .. last: 0 = values, 1 = their d/dr (second half of tp_w)
 // `stream` / `max_ctas`: the producer can run on the side stream with fewer CTAs than SMs (it is one persistent CTA per
@@ -325,7 +330,7 @@ int forward_layer(const Ctx& c, int layer, bool with_up = true) {
         if (c.radial_ready && layer > 0) {
             FMB_CUDA_CHECK(cudaStreamWaitEvent(c.stream, c.radial_ready, 0));     // produced beside the first interaction
         } else {
-            FMB_TRY(radial_weights(c, layer, e0, 0, 0, edge_limits(c) + (layer == 0 ? 0 : 1)));
+            FMB_TRY(radial_weights(c, layer, e0, 0, 0, edge_limit(c, layer == 0 ? 0 : 1)));
         }
         TpArgs t{};
         t.lin = L.l_in_max; t.species_x = layer == 0; t.n_atoms = c.n; t.n_rows = rows;
@@ -436,7 +441,7 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
             if (c.radial_ready) {
                 FMB_CUDA_CHECK(cudaStreamWaitEvent(c.stream, c.radial_ready, 0));
             } else {
-                FMB_TRY(radial_weights(c, layer, e0, keeps_forward_weights(c, layer) ? 1 : 0, 1, edge_limits(c)));
+                FMB_TRY(radial_weights(c, layer, e0, keeps_forward_weights(c, layer) ? 1 : 0, 1, edge_limit(c, 0)));
             }
             t.chunk_e0 = e0; t.chunk_edges = c.chunk;
             StageScope scope(c.stream, kStTpBwd1);
@@ -456,7 +461,7 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
             FMB_CUDA_CHECK(cudaStreamWaitEvent(c.stream, c.radial_ready, 0));
         } else {
             FMB_TRY(radial_weights(c, layer, e0, keeps_forward_weights(c, layer) ? 1 : 0, 1,
-                                   layer == 0 ? (const long long*)c.nl->count : edge_limits(c)));
+                                   layer == 0 ? (const long long*)c.nl->count : edge_limit(c, 0)));
         }
         TpArgs t{};
         t.lin = L.l_in_max; t.species_x = layer == 0; t.n_atoms = c.n;
@@ -550,11 +555,11 @@ int fork_radial(Ctx& c, int which, bool tangent_too = false, cudaEvent_t* tangen
     constexpr int side_ctas = 136;      // the SMs it leaves free serve the node kernels beside it (104 .. 148 measure alike)
     FMB_CUDA_CHECK(cudaEventRecord(side->fork, c.stream));
     FMB_CUDA_CHECK(cudaStreamWaitEvent(side->stream, side->fork, 0));
-    FMB_TRY(radial_weights(c, layer, 0, which, which, edge_limits(c) + (which == 0 ? 1 : 0), side->stream, side_ctas));
+    FMB_TRY(radial_weights(c, layer, 0, which, which, edge_limit(c, which == 0 ? 1 : 0), side->stream, side_ctas));
     FMB_CUDA_CHECK(cudaEventRecord(side->join, side->stream));
     c.radial_ready = side->join;
     if (tangent_too && which == 0 && tangent_ready) {
-        FMB_TRY(radial_weights(c, layer, 0, 1, 1, edge_limits(c), side->stream, side_ctas));
+        FMB_TRY(radial_weights(c, layer, 0, 1, 1, edge_limit(c, 0), side->stream, side_ctas));
         FMB_CUDA_CHECK(cudaEventRecord(side->join_tangent, side->stream));
         *tangent_ready = side->join_tangent;
     }
@@ -567,8 +572,10 @@ int forward_pass(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t*
                  cudaEvent_t* tangent_ready) {
     Ctx c;
     FMB_TRY(make_ctx(c, model, nl, work, stream));
-    k_edge_limits<<<1, 1, 0, c.stream>>>(nl->edge_row_ptr, c.n0, c.n1, edge_limits(c));
-    FMB_LAUNCH_CHECK();
+    if (!plain_rows(c)) {
+        k_edge_limits<<<1, 1, 0, c.stream>>>(nl->edge_row_ptr, c.n0, c.n1, edge_limits(c));
+        FMB_LAUNCH_CHECK();
+    }
     FMB_TRY(fork_radial(c, 0, tangent_ready != nullptr, tangent_ready));
     FMB_TRY(forward_layer(c, 0));
     FMB_TRY(forward_layer(c, 1));
@@ -587,8 +594,10 @@ int backward_pass(const fmb_model_t* model, const fmb_nl_t* nl, const fmb_work_t
     if (tangent_ready) {
         c.radial_ready = tangent_ready;
     } else {
-        k_edge_limits<<<1, 1, 0, c.stream>>>(nl->edge_row_ptr, c.n0, c.n1, edge_limits(c));
-        FMB_LAUNCH_CHECK();
+        if (!plain_rows(c)) {
+            k_edge_limits<<<1, 1, 0, c.stream>>>(nl->edge_row_ptr, c.n0, c.n1, edge_limits(c));
+            FMB_LAUNCH_CHECK();
+        }
         FMB_TRY(fork_radial(c, 1));
     }
     FMB_TRY(backward_layer(c, 1, work->basis, work->d_h, 1));

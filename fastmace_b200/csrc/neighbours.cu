@@ -297,10 +297,39 @@ __global__ void k_rebuild_flag(const unsigned long long* __restrict__ max_bits, 
     *flag = __longlong_as_double((long long)*max_bits) > threshold2 ? 1 : 0;
 }
 
+// The same test in one launch for lists of a few thousand atoms (one CTA walks them): the maximum is exact whatever
+// the order, so the flag and the recorded maximum equal those of the three-node form above.
+constexpr int kSmallTestAtoms = 8192;
+
+__global__ void __launch_bounds__(1024)
+k_rebuild_test_small(int n, const double* __restrict__ x, const double* __restrict__ ref, double threshold2,
+                     unsigned long long* __restrict__ max_bits, int32_t* __restrict__ flag) {
+    __shared__ double warp_max[32];
+    double d2 = 0.0;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const double dx = sub(x[3 * i], ref[3 * i]), dy = sub(x[3 * i + 1], ref[3 * i + 1]),
+                     dz = sub(x[3 * i + 2], ref[3 * i + 2]);
+        d2 = fmax(d2, norm2(dx, dy, dz));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) d2 = fmax(d2, __shfl_xor_sync(0xffffffffu, d2, o));
+    if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = d2;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        d2 = warp_max[threadIdx.x];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) d2 = fmax(d2, __shfl_xor_sync(0xffffffffu, d2, o));
+        if (threadIdx.x == 0) {
+            *max_bits = d2 > 0.0 ? (unsigned long long)__double_as_longlong(d2) : 0ull;
+            *flag = d2 > threshold2 ? 1 : 0;
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------- scan
 __global__ void __launch_bounds__(kScanBlock)
 k_scan_tiles(const int32_t* __restrict__ in, int32_t* __restrict__ out, int n, int32_t* __restrict__ tile_sums,
-             const int32_t* flag) {
+             const int32_t* flag, int write_total) {
     if (flag && *flag == 0) return;
     __shared__ int32_t warp_totals[32];
     const int tile = blockIdx.x;
@@ -330,7 +359,10 @@ k_scan_tiles(const int32_t* __restrict__ in, int32_t* __restrict__ out, int n, i
             if (lane >= o) wi += t;
         }
         warp_totals[lane] = wi - w;   // exclusive
-        if (lane == 31) tile_sums[tile] = wi;
+        if (lane == 31) {
+            tile_sums[tile] = wi;
+            if (write_total) out[n] = wi;     // a scan of one tile is complete here
+        }
     }
     __syncthreads();
     int run = warp_totals[warp] + incl - sum;
@@ -394,8 +426,9 @@ NlConst make_const(const fmb_nl_t* nl) {
 
 int exclusive_scan(const int32_t* in, int32_t* out, int n, int32_t* scratch, const int32_t* flag, cudaStream_t stream) {
     const int tiles = ceil_div(n, kScanTile);
-    k_scan_tiles<<<tiles, kScanBlock, 0, stream>>>(in, out, n, scratch, flag);
+    k_scan_tiles<<<tiles, kScanBlock, 0, stream>>>(in, out, n, scratch, flag, tiles == 1 ? 1 : 0);
     FMB_LAUNCH_CHECK();
+    if (tiles == 1) return FMB_OK;
     k_scan_sums<<<1, kScanBlock, 0, stream>>>(scratch, tiles, out, n, flag);
     FMB_LAUNCH_CHECK();
     if (tiles > 1) {
@@ -474,6 +507,13 @@ extern "C" FMB_API int fmb_nl_compact(const fmb_nl_t* nl, const double* position
 extern "C" FMB_API int fmb_nl_needs_rebuild(const fmb_nl_t* nl, const double* positions, double fraction, fmb_stream_t stream_) {
     FMB_REQUIRE(nl && positions, "fmb_nl_needs_rebuild: null argument");
     cudaStream_t stream = (cudaStream_t)stream_;
+    if (nl->n_atoms <= kSmallTestAtoms) {
+        const double t = fraction * nl->skin / 2.0;
+        k_rebuild_test_small<<<1, 1024, 0, stream>>>(nl->n_atoms, positions, nl->reference_positions, t * t,
+                                                     (unsigned long long*)nl->max_disp2_bits, nl->rebuild_flag);
+        FMB_LAUNCH_CHECK();
+        return FMB_OK;
+    }
     FMB_CUDA_CHECK(cudaMemsetAsync(nl->max_disp2_bits, 0, sizeof(uint64_t), stream));
     k_max_displacement<<<ceil_div(nl->n_atoms, 256), 256, 0, stream>>>(
         nl->n_atoms, positions, nl->reference_positions, (unsigned long long*)nl->max_disp2_bits);

@@ -221,8 +221,10 @@ struct E0Table {
 __global__ void __launch_bounds__(256)
 k_reduce_partial(int n_atoms, int n_energy, const float* __restrict__ node_energy, const int32_t* __restrict__ species,
                  E0Table e0, const float* __restrict__ atom_virial,
-                 double* __restrict__ partial) {
+                 double* __restrict__ partial, const float* __restrict__ force_acc, float* __restrict__ forces) {
     __shared__ double sh[8][7];
+    // the forces are minus the accumulated gradient (independent of the sums below; it saves a launch)
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < 3 * n_atoms; i += gridDim.x * blockDim.x) forces[i] = -force_acc[i];
     double acc[7] = {0, 0, 0, 0, 0, 0, 0};
     const int per_block = (n_atoms + gridDim.x - 1) / gridDim.x;
     const int begin = blockIdx.x * per_block, end = min(n_atoms, begin + per_block);
@@ -268,11 +270,6 @@ k_reduce_final(int blocks, const double* __restrict__ partial, double inv_volume
         stress[3 * i + j] = (float)s;
         stress[3 * j + i] = (float)s;
     }
-}
-
-__global__ void k_finish_forces(int n3, const float* __restrict__ force_acc, float* __restrict__ forces) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n3) forces[i] = -force_acc[i];
 }
 
 __global__ void k_commit(int n3, const float* __restrict__ forces, const double* __restrict__ energy,
@@ -353,12 +350,11 @@ int reduce_outputs(const fmb_model_t* m, const fmb_work_t* w, int n_energy, doub
     E0Table e0;
     for (int k = 0; k < FMB_MAX_SPECIES; ++k) e0.v[k] = m->e0[k];
     k_reduce_partial<<<kReduceBlocks, 256, 0, stream>>>(w->n_atoms, n_energy, w->node_energy, w->species, e0,
-                                                        w->compute_stress ? w->atom_virial : nullptr, w->partial);
+                                                        w->compute_stress ? w->atom_virial : nullptr, w->partial,
+                                                        w->force_acc, w->forces);
     FMB_LAUNCH_CHECK();
     k_reduce_final<<<1, 7 * 32, 0, stream>>>(kReduceBlocks, w->partial, 1.0 / volume, w->compute_stress, w->energy, w->stress,
                                          w->status);
-    FMB_LAUNCH_CHECK();
-    k_finish_forces<<<ceil_div(3LL * w->n_atoms, 256), 256, 0, stream>>>(3 * w->n_atoms, w->force_acc, w->forces);
     FMB_LAUNCH_CHECK();
     return FMB_OK;
 }

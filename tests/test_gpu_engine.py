@@ -133,6 +133,32 @@ def test_overflow_in_graph_mode_is_restored_grown_and_redone():
     assert torch.equal(graph_state.energy, checked_state.energy)
 
 
+def test_headline_run_survives_its_own_edge_growth():
+    """5,000 steps of the headline configuration (1,944-atom NaCl, medium model, 300 K): the random-init model pulls
+    the crystal together, so the edge count grows by a quarter over the run (62 k -> 78 k). The captured engine must
+    come through -- inside the headroom of its buffers or, where that runs out, through check points, host-driven
+    growth and redo -- with the state of the stage-by-stage engine, bit for bit."""
+    from fastmace_b200.engine import B200Engine
+    out = {}
+    for mode in ("graph", "checked"):
+        spec, weights, s, ff, state, it = _setup("medium", repeat=(9, 9, 3), temperature=300.0, seed=1)
+        first_edges = None
+        engine = B200Engine(ff, it, state, mode=mode)
+        engine.run(1)
+        first_edges = int(ff.neighbours.count.item())
+        engine.run(4999)
+        engine.flush()
+        out[mode] = (state.positions.clone(), state.velocities.clone(), state.energy.clone(), state.forces.clone(),
+                     engine.info(), first_edges, int(ff.neighbours.count.item()))
+    g, c = out["graph"], out["checked"]
+    print(f"edges {g[5]} -> {g[6]}, overflows redone {g[4]['overflows_redone']}, captures {g[4]['captures']}, "
+          f"rebuilds {g[4]['neighbour_rebuilds']}")
+    assert g[6] > 1.2 * g[5]
+    assert bool(torch.isfinite(g[2]).all())
+    for k in range(4):
+        assert torch.equal(g[k], c[k]), k
+
+
 def test_status_words_are_cleared_once_reported():
     from fastmace_b200 import _lib
     spec, weights, s, ff, state, it = _setup()

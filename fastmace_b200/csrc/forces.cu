@@ -12,6 +12,7 @@
 #include <cstdlib>
 
 #include <cmath>
+#include <algorithm>
 #include <vector>
 
 namespace fmb {
@@ -57,6 +58,10 @@ struct StageScope {
 struct SideStream {
     cudaStream_t stream = nullptr;
     cudaEvent_t fork = nullptr, join = nullptr, join_tangent = nullptr;
+    // A phased force call (fmb_forces_phase) starts the producers in phase 0 and waits for them in phase 1. Several
+    // ranks played on one device share this stream: their workspaces are listed, and as the stream runs in order, the
+    // latest `join_tangent` stands for every producer started before it.
+    std::vector<const fmb_work_t*> phased;
 };
 
 SideStream* side_stream(cudaStream_t main) {
@@ -126,10 +131,12 @@ struct Ctx {
 // When the whole edge list is one chunk, the last interaction's radial weights written by the forward pass are still
 // in tp_w when its adjoint runs (the reassociated first layer never touches tp_w), so the adjoint only adds their d/dr.
 // The forward pass then takes the unfused route (GEMM + tensor-product kernel) so that the weights exist; with more
-// than one chunk the fused kernel runs instead and the adjoint recomputes both per chunk.
+// than one chunk the fused kernel runs instead and the adjoint recomputes both per chunk. The rows of the forward pass
+// (n1) and of the adjoint (n0) must be the same prefix of the list: true without decomposition and for a rank of a
+// halo-exchange run, not for the ghost-shell scheme (n1 < n0).
 bool keeps_forward_weights(const Ctx& c, int layer) {
     return c.n_chunks == 1 && layer > 0 && layer == c.m->n_layers - 1 && c.m->layer[0].first[0] != nullptr &&
-           c.n0 == c.n && c.n1 == c.n;
+           c.n0 == c.n1;
 }
 
 // Per-edge hand-over adjoint (adjoint_edges.cu) instead of the mirror evaluation: the buffers exist and the first
@@ -626,6 +633,12 @@ extern "C" FMB_API int fmb_forces_phase(const fmb_model_t* model, const fmb_nl_t
         FMB_REQUIRE(positions, "fmb_forces_phase: phase 0 needs the positions");
         FMB_TRY(fmb_edge_features(model, nl, work, positions, stream));
         FMB_TRY(make_ctx(c, model, nl, work, (cudaStream_t)stream));
+        // the radial weights of the second interaction and their d/dr, beside the first interaction (the edge limits
+        // are in place: the edge kernel's call computed them)
+        cudaEvent_t tangent = nullptr;
+        FMB_TRY(fork_radial(c, 0, true, &tangent));
+        if (c.radial_ready && tangent) side_stream(c.stream)->phased.push_back(work);
+        c.radial_ready = nullptr;
         FMB_TRY(forward_layer(c, 0));
         LinearBatch lb;
         queue_linear_up(lb, c, 1);
@@ -633,11 +646,24 @@ extern "C" FMB_API int fmb_forces_phase(const fmb_model_t* model, const fmb_nl_t
     }
     FMB_TRY(make_ctx(c, model, nl, work, (cudaStream_t)stream));
     if (phase == 1) {
+        SideStream* side = side_stream(c.stream);
+        bool started = false;
+        bool alone = false;
+        if (side) {
+            auto it = std::find(side->phased.begin(), side->phased.end(), work);
+            if (it != side->phased.end()) {
+                started = true;
+                alone = side->phased.size() == 1;
+                side->phased.erase(it);
+            }
+        }
+        if (started) c.radial_ready = alone ? side->join : side->join_tangent;
         FMB_TRY(forward_layer(c, 1, false));
         {
             StageScope scope(c.stream, kStReadout);
             FMB_TRY(readout(model, c.n0, c.n1, h_of(c, 0), h_of(c, 1), work->node_energy, work->d_h, work->basis, c.stream));
         }
+        c.radial_ready = started ? side->join_tangent : nullptr;
         return backward_layer(c, 1, work->basis, work->d_h, 1, false);
     }
     FMB_TRY(backward_linear_up(c, 1, work->d_h));

@@ -40,7 +40,7 @@ class B200ForceField:
     There is no CPU path: construction fails without a CUDA device or without the built library."""
 
     def __init__(self, spec: MaceSpec, weights, numbers, cell, *, compute_stress: bool = False, device="cuda",
-                 neighbours: NeighbourConfig | None = None, chunk_edges: int = DEFAULT_CHUNK_EDGES,
+                 neighbours: NeighbourConfig | None = None, chunk_edges: int | None = None,
                  positions=None, packed: PackedModel | None = None, n_owned: int = -1, n_inner: int = -1,
                  halo_exchange: bool = False, atom_capacity: int | None = None, edge_adjoint: bool | None = None):
         if not torch.cuda.is_available():
@@ -74,7 +74,10 @@ class B200ForceField:
         self._upload_atoms()
         self.neighbours = CellListNeighbours(self.cell, spec.r_cut, self._device, torch.float32, neighbours,
                                              atom_capacity=self.atom_capacity)
-        self.chunk_edges = int(chunk_edges)
+        # ``chunk_edges``: None = the whole edge list as one chunk (per-edge radial weights kept between the forward pass
+        # and the adjoint, streamed kernels) whenever its buffers fit in the free device memory, else chunks of
+        # DEFAULT_CHUNK_EDGES with the weights recomputed per chunk; a number sets the chunk size by hand
+        self.chunk_edges = None if chunk_edges is None else int(chunk_edges)
         # ``edge_adjoint``: None = the per-edge hand-over adjoint whenever its buffers fit in the free device memory,
         # else the mirror evaluation; False = the mirror evaluation regardless (the path of lists too large for the
         # buffers, selectable so that tests reach it on small cells); True = refuse to fall back
@@ -187,10 +190,20 @@ class B200ForceField:
             self.work, self.buf = None, None
             torch.cuda.empty_cache()
         c = spec.channels
-        chunk = min(self.chunk_edges, cap)
         max_paths = max(len(spec.paths(t)) for t in range(spec.num_interactions))
-        max_mid = max(self.packed.struct.layer[t].mid_dim for t in range(spec.num_interactions))
         hid = (spec.hidden_lmax + 1) ** 2
+        if self.chunk_edges is not None:
+            chunk = min(self.chunk_edges, cap)
+        elif cap <= DEFAULT_CHUNK_EDGES:
+            chunk = cap
+        else:
+            # everything this function allocates per edge with the whole list as one chunk: weights and their d/dr,
+            # vector, harmonics, hidden features, hand-over buffers
+            free, _ = torch.cuda.mem_get_info(dev)
+            free += torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)
+            per_edge = 2 * max_paths * c * 4 + 16 + 64 + spec.num_interactions * 2 * 64 * 4 + hid * c * 4 + 20
+            chunk = cap if cap * per_edge <= 0.85 * free else DEFAULT_CHUNK_EDGES
+        max_mid = max(self.packed.struct.layer[t].mid_dim for t in range(spec.num_interactions))
         # the reassociated first layer keeps its per-species outer-product sums [16][n_species][64] in `mid` / `d_mid`
         mid_floats = max(max_mid * c, 16 * len(self.packed.species_z) * 64)
         f32 = dict(dtype=torch.float32, device=dev)

@@ -440,7 +440,7 @@ class DomainSimulation:
         self.config = neighbours or NeighbourConfig()
         self.integrator_config = integrator_config or IntegratorConfig()
         self.temperature_K, self.seed = float(temperature_K), int(seed)
-        self.chunk_edges = chunk_edges or DEFAULT_CHUNK_EDGES
+        self.chunk_edges = chunk_edges          # None: B200ForceField decides from the free memory
         self.atom_headroom = float(atom_headroom)
         self.cell = np.asarray(structure.cell, dtype=np.float64).reshape(3, 3)
         self.natoms = int(structure.natoms)

@@ -12,6 +12,8 @@
 
 #include "fmb_common.cuh"
 
+#include <cooperative_groups.h>
+
 namespace fmb {
 
 namespace {
@@ -39,19 +41,19 @@ struct NlConst {
     double cutoff2;
 };
 
-__global__ void k_zero_bins(int32_t* bin_count, int32_t* bin_fill, int total_bins, const int32_t* flag) {
-    if (flag && *flag == 0) return;
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
+__device__ __forceinline__ void zero_bins_item(int i, int32_t* bin_count, int32_t* bin_fill, int total_bins) {
     if (i <= total_bins) bin_count[i] = 0;
     if (i < total_bins) bin_fill[i] = 0;
 }
 
-__global__ void k_wrap_bin(NlConst c, int n, const double* __restrict__ x, double* __restrict__ wrapped,
-                           double* __restrict__ offsets, int32_t* __restrict__ atom_bin, int32_t* __restrict__ bin_count,
-                           const int32_t* flag) {
+__global__ void k_zero_bins(int32_t* bin_count, int32_t* bin_fill, int total_bins, const int32_t* flag) {
     if (flag && *flag == 0) return;
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
+    zero_bins_item(blockIdx.x * blockDim.x + threadIdx.x, bin_count, bin_fill, total_bins);
+}
+
+__device__ __forceinline__ void wrap_bin_item(const NlConst& c, int i, const double* __restrict__ x,
+                                              double* __restrict__ wrapped, double* __restrict__ offsets,
+                                              int32_t* __restrict__ atom_bin, int32_t* __restrict__ bin_count) {
     double p0 = x[3 * i], p1 = x[3 * i + 1], p2 = x[3 * i + 2];
     double frac[3], off[3], back[3];
     times_3x3(p0, p1, p2, c.inverse, frac);
@@ -72,31 +74,39 @@ __global__ void k_wrap_bin(NlConst c, int n, const double* __restrict__ x, doubl
     atomicAdd(&bin_count[bin], 1);
 }
 
+__global__ void k_wrap_bin(NlConst c, int n, const double* __restrict__ x, double* __restrict__ wrapped,
+                           double* __restrict__ offsets, int32_t* __restrict__ atom_bin, int32_t* __restrict__ bin_count,
+                           const int32_t* flag) {
+    if (flag && *flag == 0) return;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) wrap_bin_item(c, i, x, wrapped, offsets, atom_bin, bin_count);
+}
+
+__device__ __forceinline__ void bin_fill_item(int i, const int32_t* __restrict__ atom_bin,
+                                              const int32_t* __restrict__ bin_start, int32_t* __restrict__ bin_fill,
+                                              int32_t* __restrict__ bin_atoms) {
+    const int bin = atom_bin[i];
+    const int slot = atomicAdd(&bin_fill[bin], 1);
+    bin_atoms[bin_start[bin] + slot] = i;
+}
+
 __global__ void k_bin_fill(int n, const int32_t* __restrict__ atom_bin, const int32_t* __restrict__ bin_start,
                            int32_t* __restrict__ bin_fill, int32_t* __restrict__ bin_atoms, const int32_t* flag) {
     if (flag && *flag == 0) return;
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    int bin = atom_bin[i];
-    int slot = atomicAdd(&bin_fill[bin], 1);
-    bin_atoms[bin_start[bin] + slot] = i;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) bin_fill_item(i, atom_bin, bin_start, bin_fill, bin_atoms);
 }
 
 constexpr int kWarpsPerBlock = 4;
 
 // One warp per receiver. MODE 0: count the candidates; MODE 1: collect, sort by (sender, image) and write them.
 template <int MODE>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
-k_rows(NlConst c, int n, int capacity, const double* __restrict__ wrapped, const double* __restrict__ offsets,
-       const int32_t* __restrict__ atom_bin, const int32_t* __restrict__ bin_start, const int32_t* __restrict__ bin_atoms,
-       int32_t* __restrict__ row_count, const int32_t* __restrict__ row_ptr, int32_t* __restrict__ cand_index,
-       float* __restrict__ cand_shift, uint32_t* __restrict__ status, const int32_t* flag) {
-    if (flag && *flag == 0) return;
-    extern __shared__ unsigned long long s_keys[];   // MODE 1: [kWarpsPerBlock][FMB_MAX_ROW]
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int r = blockIdx.x * kWarpsPerBlock + warp;
-    if (r >= n) return;
-    unsigned long long* keys = MODE == 1 ? s_keys + (size_t)warp * FMB_MAX_ROW : nullptr;
+__device__ __forceinline__ void rows_receiver(const NlConst& c, int r, int lane, unsigned long long* keys, int capacity,
+                                              const double* __restrict__ wrapped, const double* __restrict__ offsets,
+                                              const int32_t* __restrict__ atom_bin, const int32_t* __restrict__ bin_start,
+                                              const int32_t* __restrict__ bin_atoms, int32_t* __restrict__ row_count,
+                                              const int32_t* __restrict__ row_ptr, int32_t* __restrict__ cand_index,
+                                              float* __restrict__ cand_shift, uint32_t* __restrict__ status) {
     const double rx = wrapped[3 * r], ry = wrapped[3 * r + 1], rz = wrapped[3 * r + 2];
     const int bin = atom_bin[r];
     const int b2 = bin % c.nbins[2], b1 = (bin / c.nbins[2]) % c.nbins[1], b0 = bin / (c.nbins[2] * c.nbins[1]);
@@ -195,17 +205,48 @@ k_rows(NlConst c, int n, int capacity, const double* __restrict__ wrapped, const
     }
 }
 
-__global__ void k_finish_build(NlConst c, int n, int capacity, const int32_t* __restrict__ row_ptr,
-                               const double* __restrict__ x, float pad0, float pad1, float pad2,
-                               int32_t* __restrict__ cand_index, float* __restrict__ cand_shift,
-                               int32_t* __restrict__ edge_index, float* __restrict__ unit_shifts,
-                               float* __restrict__ shifts, int64_t* __restrict__ num_candidates,
-                               double* __restrict__ reference, double* __restrict__ build_cell,
-                               uint32_t* __restrict__ status, const int32_t* flag) {
+template <int MODE>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+k_rows(NlConst c, int n, int capacity, const double* __restrict__ wrapped, const double* __restrict__ offsets,
+       const int32_t* __restrict__ atom_bin, const int32_t* __restrict__ bin_start, const int32_t* __restrict__ bin_atoms,
+       int32_t* __restrict__ row_count, const int32_t* __restrict__ row_ptr, int32_t* __restrict__ cand_index,
+       float* __restrict__ cand_shift, uint32_t* __restrict__ status, const int32_t* flag) {
     if (flag && *flag == 0) return;
+    extern __shared__ unsigned long long s_keys[];   // MODE 1: [kWarpsPerBlock][FMB_MAX_ROW]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x * kWarpsPerBlock + warp;
+    if (r >= n) return;
+    unsigned long long* keys = MODE == 1 ? s_keys + (size_t)warp * FMB_MAX_ROW : nullptr;
+    rows_receiver<MODE>(c, r, lane, keys, capacity, wrapped, offsets, atom_bin, bin_start, bin_atoms, row_count, row_ptr,
+                        cand_index, cand_shift, status);
+}
+
+struct FinishArgs {
+    float pad0, pad1, pad2;
+    int32_t* cand_index;
+    float* cand_shift;
+    int32_t* edge_index;
+    float* unit_shifts;
+    float* shifts;
+    int64_t* num_candidates;
+    double* reference;
+    double* build_cell;
+    uint32_t* status;
+};
+
+__device__ __forceinline__ void finish_items(const NlConst& c, int n, int capacity, const int32_t* __restrict__ row_ptr,
+                                             const double* __restrict__ x, const FinishArgs& f, int tid, int stride) {
+    const float pad0 = f.pad0, pad1 = f.pad1, pad2 = f.pad2;
+    int32_t* const cand_index = f.cand_index;
+    float* const cand_shift = f.cand_shift;
+    int32_t* const edge_index = f.edge_index;
+    float* const unit_shifts = f.unit_shifts;
+    float* const shifts = f.shifts;
+    int64_t* const num_candidates = f.num_candidates;
+    double* const reference = f.reference;
+    double* const build_cell = f.build_cell;
+    uint32_t* const status = f.status;
     const int total = row_ptr[n];
-    const int stride = gridDim.x * blockDim.x;
-    const int tid = blockIdx.x * blockDim.x + threadIdx.x;
     if (tid == 0) {
         *num_candidates = total;
         if (total > capacity) atomicOr(status, FMB_STATUS_CAND_OVERFLOW);
@@ -223,6 +264,12 @@ __global__ void k_finish_build(NlConst c, int n, int capacity, const int32_t* __
         shifts[3 * k] = (float)ps[0]; shifts[3 * k + 1] = (float)ps[1]; shifts[3 * k + 2] = (float)ps[2];
     }
     for (int k = tid; k < 3 * n; k += stride) reference[k] = x[k];
+}
+
+__global__ void k_finish_build(NlConst c, int n, int capacity, const int32_t* __restrict__ row_ptr,
+                               const double* __restrict__ x, FinishArgs f, const int32_t* flag) {
+    if (flag && *flag == 0) return;
+    finish_items(c, n, capacity, row_ptr, x, f, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x);
 }
 
 // compact: MODE 0 counts the candidates of each receiver inside the cutoff; MODE 1 writes the stable partition.
@@ -406,6 +453,101 @@ __global__ void k_scan_add(int32_t* __restrict__ out, int n, const int32_t* __re
     if (i < n) out[i] += tile_sums[i / kScanTile];
 }
 
+// ------------------------------------------------------------------------------ gated build of a small list
+// The eight launches of a build as one cooperative kernel, for lists whose two scans fit one CTA (atoms and bins up to
+// kSmallBuild). Inside a captured step the build is gated by the device flag; a step that does not rebuild then pays
+// for one launch that reads the flag and returns instead of eight. The phases are the kernels' own bodies, separated by
+// grid barriers; the result is the same list (the order inside a bin depends on the atomics as before, the rows are
+// sorted afterwards).
+constexpr int kSmallBuild = 4096;
+constexpr int kCoopThreads = 256;
+
+struct SmallBuildArgs {
+    NlConst c;
+    int n, capacity, total_bins;
+    const double* x;
+    double* wrapped;
+    double* offsets;
+    int32_t* atom_bin;
+    int32_t* bin_count;
+    int32_t* bin_start;
+    int32_t* bin_fill;
+    int32_t* bin_atoms;
+    int32_t* cand_row_count;
+    int32_t* cand_row_ptr;
+    FinishArgs finish;
+    const int32_t* flag;
+};
+
+// exclusive scan of n <= kSmallBuild values by one CTA of kCoopThreads threads, total at out[n]
+__device__ void scan_by_one_cta(const int32_t* __restrict__ in, int32_t* __restrict__ out, int n) {
+    constexpr int kItems = kSmallBuild / kCoopThreads;
+    __shared__ int32_t warp_totals[kCoopThreads / 32];
+    const int base = threadIdx.x * kItems;
+    int v[kItems];
+    int sum = 0;
+#pragma unroll
+    for (int k = 0; k < kItems; ++k) {
+        v[k] = base + k < n ? in[base + k] : 0;
+        sum += v[k];
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+    }
+    if (lane == 31) warp_totals[warp] = incl;
+    __syncthreads();
+    int before = 0, total = 0;
+#pragma unroll
+    for (int w = 0; w < kCoopThreads / 32; ++w) {
+        if (w < warp) before += warp_totals[w];
+        total += warp_totals[w];
+    }
+    int run = before + incl - sum;
+#pragma unroll
+    for (int k = 0; k < kItems; ++k) {
+        if (base + k < n) out[base + k] = run;
+        run += v[k];
+    }
+    if (threadIdx.x == 0) out[n] = total;
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(kCoopThreads)
+k_build_small(const __grid_constant__ SmallBuildArgs a) {
+    if (a.flag && *a.flag == 0) return;                 // the same answer in every CTA: nobody reaches a grid barrier
+    extern __shared__ unsigned long long s_keys[];      // [warps of the CTA][FMB_MAX_ROW]
+    cooperative_groups::grid_group grid = cooperative_groups::this_grid();
+    const int tid = blockIdx.x * kCoopThreads + threadIdx.x, stride = gridDim.x * kCoopThreads;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int first_row = blockIdx.x * (kCoopThreads / 32) + warp, row_stride = gridDim.x * (kCoopThreads / 32);
+    for (int i = tid; i <= a.total_bins; i += stride) zero_bins_item(i, a.bin_count, a.bin_fill, a.total_bins);
+    grid.sync();
+    for (int i = tid; i < a.n; i += stride) wrap_bin_item(a.c, i, a.x, a.wrapped, a.offsets, a.atom_bin, a.bin_count);
+    grid.sync();
+    if (blockIdx.x == 0) scan_by_one_cta(a.bin_count, a.bin_start, a.total_bins);
+    grid.sync();
+    for (int i = tid; i < a.n; i += stride) bin_fill_item(i, a.atom_bin, a.bin_start, a.bin_fill, a.bin_atoms);
+    grid.sync();
+    for (int r = first_row; r < a.n; r += row_stride)
+        rows_receiver<0>(a.c, r, lane, nullptr, a.capacity, a.wrapped, a.offsets, a.atom_bin, a.bin_start, a.bin_atoms,
+                         a.cand_row_count, nullptr, nullptr, nullptr, a.finish.status);
+    grid.sync();
+    if (blockIdx.x == 0) scan_by_one_cta(a.cand_row_count, a.cand_row_ptr, a.n);
+    grid.sync();
+    for (int r = first_row; r < a.n; r += row_stride) {
+        rows_receiver<1>(a.c, r, lane, s_keys + (size_t)warp * FMB_MAX_ROW, a.capacity, a.wrapped, a.offsets, a.atom_bin,
+                         a.bin_start, a.bin_atoms, nullptr, a.cand_row_ptr, a.finish.cand_index, a.finish.cand_shift,
+                         a.finish.status);
+        __syncwarp();
+    }
+    grid.sync();
+    finish_items(a.c, a.n, a.capacity, a.cand_row_ptr, a.x, a.finish, tid, stride);
+}
+
 NlConst make_const(const fmb_nl_t* nl) {
     NlConst c;
     for (int k = 0; k < 9; ++k) {
@@ -442,6 +584,52 @@ int exclusive_scan(const int32_t* in, int32_t* out, int n, int32_t* scratch, con
 
 using namespace fmb;
 
+namespace fmb {
+namespace {
+
+FinishArgs finish_args(const fmb_nl_t* nl) {
+    FinishArgs f;
+    f.pad0 = nl->pad_unit_shift[0]; f.pad1 = nl->pad_unit_shift[1]; f.pad2 = nl->pad_unit_shift[2];
+    f.cand_index = nl->candidate_index; f.cand_shift = nl->candidate_unit_shifts;
+    f.edge_index = nl->edge_index; f.unit_shifts = nl->unit_shifts; f.shifts = nl->shifts;
+    f.num_candidates = nl->num_candidates; f.reference = nl->reference_positions; f.build_cell = nl->build_cell;
+    f.status = nl->status;
+    return f;
+}
+
+// the gated build of a small list as one cooperative launch; FMB_ERR_UNSUPPORTED when the device cannot hold the grid
+int build_small(const fmb_nl_t* nl, const double* positions, const int32_t* flag, cudaStream_t stream) {
+    const size_t smem = (size_t)(kCoopThreads / 32) * FMB_MAX_ROW * sizeof(unsigned long long);
+    FMB_CUDA_CHECK(opt_in_shared_memory((const void*)k_build_small, (int)smem));
+    static int resident = 0;
+    if (resident == 0) {
+        int per_sm = 0, sms = 0, dev = 0, coop = 0;
+        FMB_CUDA_CHECK(cudaGetDevice(&dev));
+        FMB_CUDA_CHECK(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
+        FMB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_build_small, kCoopThreads, smem) != cudaSuccess) per_sm = 0;
+        resident = coop && per_sm > 0 ? per_sm * sms : -1;
+    }
+    if (resident < 0) return FMB_ERR_UNSUPPORTED;
+    SmallBuildArgs a;
+    a.c = make_const(nl);
+    a.n = nl->n_atoms; a.capacity = nl->capacity; a.total_bins = nl->nbins[0] * nl->nbins[1] * nl->nbins[2];
+    a.x = positions; a.wrapped = nl->wrapped; a.offsets = nl->offsets; a.atom_bin = nl->atom_bin;
+    a.bin_count = nl->bin_count; a.bin_start = nl->bin_start; a.bin_fill = nl->bin_fill; a.bin_atoms = nl->bin_atoms;
+    a.cand_row_count = nl->cand_row_count; a.cand_row_ptr = nl->cand_row_ptr;
+    a.finish = finish_args(nl);
+    a.flag = flag;
+    // one warp per receiver in one pass where the device holds that many CTAs; never more than are resident together
+    const int wanted = ceil_div(a.n, kCoopThreads / 32);
+    const int grid = wanted < resident ? wanted : resident;
+    void* args[] = {(void*)&a};
+    FMB_CUDA_CHECK(cudaLaunchCooperativeKernel((const void*)k_build_small, dim3(grid), dim3(kCoopThreads), args, smem, stream));
+    return FMB_OK;
+}
+
+}  // namespace
+}  // namespace fmb
+
 extern "C" FMB_API int fmb_nl_build(const fmb_nl_t* nl, const double* positions, int only_if_flag, fmb_stream_t stream_) {
     FMB_REQUIRE(nl && positions, "fmb_nl_build: null argument");
     FMB_REQUIRE(nl->n_atoms > 0 && nl->capacity > 0, "fmb_nl_build: empty list");
@@ -452,6 +640,10 @@ extern "C" FMB_API int fmb_nl_build(const fmb_nl_t* nl, const double* positions,
     const int n = nl->n_atoms;
     const int total_bins = nl->nbins[0] * nl->nbins[1] * nl->nbins[2];
     const int32_t* flag = only_if_flag ? nl->rebuild_flag : nullptr;
+    if (only_if_flag && n <= kSmallBuild && total_bins < kSmallBuild) {
+        const int rc = build_small(nl, positions, flag, stream);
+        if (rc != FMB_ERR_UNSUPPORTED) return rc;
+    }
     k_zero_bins<<<ceil_div(total_bins + 1, 256), 256, 0, stream>>>(nl->bin_count, nl->bin_fill, total_bins, flag);
     FMB_LAUNCH_CHECK();
     k_wrap_bin<<<ceil_div(n, 256), 256, 0, stream>>>(c, n, positions, nl->wrapped, nl->offsets, nl->atom_bin,
@@ -474,11 +666,7 @@ extern "C" FMB_API int fmb_nl_build(const fmb_nl_t* nl, const double* positions,
                                                                   nl->cand_row_ptr, nl->candidate_index,
                                                                   nl->candidate_unit_shifts, nl->status, flag);
     FMB_LAUNCH_CHECK();
-    k_finish_build<<<148 * 2, 256, 0, stream>>>(c, n, nl->capacity, nl->cand_row_ptr, positions, nl->pad_unit_shift[0],
-                                                nl->pad_unit_shift[1], nl->pad_unit_shift[2], nl->candidate_index,
-                                                nl->candidate_unit_shifts, nl->edge_index, nl->unit_shifts, nl->shifts,
-                                                nl->num_candidates, nl->reference_positions, nl->build_cell, nl->status,
-                                                flag);
+    k_finish_build<<<148 * 2, 256, 0, stream>>>(c, n, nl->capacity, nl->cand_row_ptr, positions, finish_args(nl), flag);
     FMB_LAUNCH_CHECK();
     return FMB_OK;
 }

@@ -72,6 +72,24 @@ def _emit(lin: int) -> str:
                               for mi, me, c in terms)
             out.append(f"    acc[{slots[(p, mo)]}] = fmaf(w[{p}], {expr}, acc[{slots[(p, mo)]}]);")
     out += ["}", ""]
+    # forward, two channels per thread on the packed FP32 pipe (fma.rn.f32x2): the per-channel quantities are pairs,
+    # a harmonic times its coupling coefficient is one scalar product shared by the pair
+    out += [f"template <> __device__ __forceinline__ void tp_forward_pair<{lin}>(const float2 (&x)[{in_dim}], "
+            f"const float (&Y)[16], const float2 (&w)[{len(paths)}], float2 (&acc)[{mid}]) {{"]
+    for p, path in enumerate(paths):
+        out.append(f"    // path {p}: {path['l_in']} x {path['l_edge']} -> {path['l_out']}")
+        by_out = {}
+        for mi, me, mo, c in path["terms"]:
+            by_out.setdefault(mo, []).append((mi, me, c))
+        for mo, terms in sorted(by_out.items()):
+            lines = []
+            for k, (mi, me, c) in enumerate(terms):
+                pair = f"pair_of({_lit(c)} * Y[{path['edge_off'] + me}])"
+                xin = f"x[{path['in_off'] + mi}]"
+                lines.append(f"float2 e = __fmul2_rn({xin}, {pair});" if k == 0 else f"e = __ffma2_rn({xin}, {pair}, e);")
+            slot = slots[(p, mo)]
+            out.append(f"    {{ {' '.join(lines)} acc[{slot}] = __ffma2_rn(w[{p}], e, acc[{slot}]); }}")
+    out += ["}", ""]
     # backward
     out += [f"template <bool FLIP, bool NEED_DX> __device__ __forceinline__ void tp_backward_{lin}("
             f"const float (&x)[{in_dim}], const float (&Y)[16], const float (&w)[{len(paths)}], "
@@ -123,6 +141,10 @@ def render() -> str:
             "template <int LIN> __device__ __forceinline__ void tp_forward(const float (&x)[(LIN + 1) * (LIN + 1)], "
             "const float (&Y)[16], const float (&w)[LIN == 0 ? 4 : LIN == 1 ? 10 : 17], "
             "float (&acc)[LIN == 0 ? 16 : LIN == 1 ? 40 : 71]);",
+            "template <int LIN> __device__ __forceinline__ void tp_forward_pair(const float2 (&x)[(LIN + 1) * (LIN + 1)], "
+            "const float (&Y)[16], const float2 (&w)[LIN == 0 ? 4 : LIN == 1 ? 10 : 17], "
+            "float2 (&acc)[LIN == 0 ? 16 : LIN == 1 ? 40 : 71]);",
+            "__device__ __forceinline__ float2 pair_of(float v) { return make_float2(v, v); }",
             ""]
     body = [_emit(lin) for lin in (0, 1, 2)]
     tail = ["}  // namespace fmb", ""]

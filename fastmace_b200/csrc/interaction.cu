@@ -195,6 +195,93 @@ k_tp_forward_stream(int n_rows, const int32_t* __restrict__ row_ptr, const int32
     if (c == 0 && abort_sh && error_word) atomicOr(error_word, FMB_STATUS_TENSOR_TIMEOUT);
 }
 
+// The streamed forward pass with two channels per thread on the packed FP32 pipe (fma.rn.f32x2, sm_100): 64 threads
+// per CTA, the per-channel operands and the message row as pairs, a harmonic times its coupling coefficient as one
+// scalar product shared by the pair. The kernel above is bound by FP32 issue (260 instructions per warp and edge for 32
+// channels); the pair form issues about as many for 64.
+constexpr int kPairThreads = kC / 2;
+
+template <int LIN>
+__global__ void __launch_bounds__(kPairThreads)
+k_tp_forward_pairs(int n_rows, const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ senders,
+                   const float* __restrict__ x, const float* __restrict__ edge_sh, const float* __restrict__ tp_w,
+                   float* __restrict__ mid, uint32_t* __restrict__ error_word) {
+    constexpr int P = TpShape<LIN>::kPaths, IN = TpShape<LIN>::kInDim, MID = TpShape<LIN>::kMidDim;
+    constexpr int kRow = P * kC;                       // floats of one edge's weights
+    constexpr int kStage = kRow + IN * kC + 16;        // weights, sender rows, harmonics
+    extern __shared__ __align__(128) float ring[];     // [kFwdStages][kStage]
+    __shared__ uint64_t bars[2 * kFwdStages];
+    __shared__ int abort_sh;
+    volatile int* abort_flag = &abort_sh;
+    const int c = threadIdx.x, lane = c & 31;          // channels 2 c and 2 c + 1
+    const int per_cta = (n_rows + gridDim.x - 1) / gridDim.x;
+    const int r0 = blockIdx.x * per_cta, r1 = min(n_rows, r0 + per_cta);
+    if (r0 >= r1) return;
+    const long long eb = row_ptr[r0], ee = row_ptr[r1];
+    const uint32_t bar0 = tc::smem_u32(bars), ring0 = tc::smem_u32(ring);
+    if (c == 0) {
+        for (int s = 0; s < kFwdStages; ++s) {
+            tc::mbar_init(bar0 + 8 * s, 1);                                  // full
+            tc::mbar_init(bar0 + 8 * (kFwdStages + s), kPairThreads / 32);   // empty: one arrival per warp
+        }
+        abort_sh = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    long long issued = eb;
+    int issue_stage = 0;
+    uint32_t issue_parity = 1;
+    int next_sender = (c == 0 && eb < ee) ? senders[eb] : 0;
+    auto issue = [&]() {
+        tc::mbar_wait(bar0 + 8 * (kFwdStages + issue_stage), issue_parity, abort_flag, kFwdSpin);
+        const uint32_t full = bar0 + 8 * issue_stage;
+        const uint32_t dst = ring0 + issue_stage * (kStage * 4);
+        tc::mbar_expect_tx(full, kStage * 4);
+        tc::bulk_load(dst, tp_w + issued * kRow, kRow * 4, full);
+        tc::bulk_load(dst + kRow * 4, x + (long long)next_sender * (IN * kC), IN * kC * 4, full);
+        tc::bulk_load(dst + (kRow + IN * kC) * 4, edge_sh + 16 * issued, 64, full);
+        ++issued;
+        if (issued < ee) next_sender = senders[issued];
+        if (++issue_stage == kFwdStages) { issue_stage = 0; issue_parity ^= 1u; }
+    };
+    if (c == 0)
+        while (issued < ee && issued < eb + kFwdStages - 1) issue();
+    int stage = 0;
+    uint32_t parity = 0;
+    for (int i = r0; i < r1; ++i) {
+        const long long rb = row_ptr[i], re = row_ptr[i + 1];
+        float2 acc[MID];
+#pragma unroll
+        for (int k = 0; k < MID; ++k) acc[k] = make_float2(0.0f, 0.0f);
+        for (long long e = rb; e < re; ++e) {
+            if (c == 0 && issued < ee && issued < e + kFwdStages) issue();
+            float2 xs[IN], w[P];
+            float Y[16];
+            tc::mbar_wait(bar0 + 8 * stage, parity, abort_flag, kFwdSpin);
+            const float* st = ring + stage * kStage;
+#pragma unroll
+            for (int p = 0; p < P; ++p) w[p] = reinterpret_cast<const float2*>(st + p * kC)[c];
+#pragma unroll
+            for (int k = 0; k < IN; ++k) xs[k] = reinterpret_cast<const float2*>(st + kRow + k * kC)[c];
+            {
+                const float4* yp = reinterpret_cast<const float4*>(st + kRow + IN * kC);
+                const float4 y0 = yp[0], y1 = yp[1], y2 = yp[2], y3 = yp[3];
+                Y[0] = y0.x; Y[1] = y0.y; Y[2] = y0.z; Y[3] = y0.w; Y[4] = y1.x; Y[5] = y1.y; Y[6] = y1.z; Y[7] = y1.w;
+                Y[8] = y2.x; Y[9] = y2.y; Y[10] = y2.z; Y[11] = y2.w; Y[12] = y3.x; Y[13] = y3.y; Y[14] = y3.z; Y[15] = y3.w;
+            }
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(bar0 + 8 * (kFwdStages + stage));
+            if (++stage == kFwdStages) { stage = 0; parity ^= 1u; }
+            tp_forward_pair<LIN>(xs, Y, w, acc);
+        }
+        float2* out = reinterpret_cast<float2*>(mid + ((long long)i * MID) * kC) + c;
+#pragma unroll
+        for (int k = 0; k < MID; ++k) out[(long long)k * (kC / 2)] = acc[k];
+    }
+    __syncthreads();
+    if (c == 0 && abort_sh && error_word) atomicOr(error_word, FMB_STATUS_TENSOR_TIMEOUT);
+}
+
 // ---------------------------------------------------------------------------------------------- backward
 constexpr int kEdgeBatch = 8;
 constexpr int kRed = 17;     // 16 harmonic gradients + the radial one
@@ -554,8 +641,23 @@ int tp_forward_launch(const TpArgs& t, cudaStream_t stream) {
         FMB_FWD(0, true)
     } else if (t.lin == 0) {
         FMB_FWD(0, false)
-    } else if (t.whole_list && (t.lin == 1 || t.lin == 2)) {
-        if (t.lin == 1) FMB_FWD_STREAM(1) else FMB_FWD_STREAM(2)
+    } else if (t.whole_list && t.lin == 1) {
+        constexpr int smem = kFwdStages * (TpShape<1>::kPaths * kC + TpShape<1>::kInDim * kC + 16) * 4;
+        static int grid_cap = 0;
+        FMB_CUDA_CHECK(opt_in_shared_memory((const void*)k_tp_forward_pairs<1>, smem));
+        if (grid_cap == 0) {
+            int per_sm = 0, sms = 148, dev = 0;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_tp_forward_pairs<1>, kPairThreads, smem) != cudaSuccess ||
+                per_sm < 1)
+                per_sm = 1;
+            if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            grid_cap = per_sm * sms;
+        }
+        const int grid = t.n_rows < grid_cap ? t.n_rows : grid_cap;
+        k_tp_forward_pairs<1><<<grid, kPairThreads, smem, stream>>>(t.n_rows, t.row_ptr, t.senders, t.x, t.edge_sh, t.tp_w,
+                                                                    t.mid, t.error_word);
+    } else if (t.whole_list && t.lin == 2) {
+        FMB_FWD_STREAM(2)
     } else if (t.lin == 1) {
         FMB_FWD(1, false)
     } else if (t.lin == 2) {

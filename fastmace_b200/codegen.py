@@ -119,6 +119,44 @@ def _emit(lin: int) -> str:
         out.append("        }")
         out.append("    }")
     out += ["}", ""]
+    # backward, two channels per thread (packed FP32): x, w, wp, g, dx and the partial sums dY, dr are pairs, the
+    # harmonics scalars; a coupling coefficient enters as a constant pair
+    out += [f"template <bool FLIP, bool NEED_DX> __device__ __forceinline__ void tp_backward_pair_{lin}("
+            f"const float2 (&x)[{in_dim}], const float (&Y)[16], const float2 (&w)[{len(paths)}], "
+            f"const float2 (&wp)[{len(paths)}], const float2 (&g)[{mid}], float2 (&dY)[16], float2& dr, "
+            f"float2 (&dx)[{in_dim}]) {{"]
+    for p, path in enumerate(paths):
+        sign = -1.0 if path["l_edge"] % 2 else 1.0
+        out.append(f"    {{  // path {p}: {path['l_in']} x {path['l_edge']} -> {path['l_out']}")
+        out.append(f"        constexpr float sg = FLIP ? {_lit(sign)} : 1.0f;")
+        by_edge = {}
+        by_in = {}
+        for mi, me, mo, c in path["terms"]:
+            by_edge.setdefault(me, []).append((mi, mo, c))
+            by_in.setdefault(mi, []).append((me, mo, c))
+        out.append("        float2 dw = make_float2(0.0f, 0.0f);")
+        for me, terms in sorted(by_edge.items()):
+            lines = []
+            for k, (mi, mo, c) in enumerate(terms):
+                prod = f"__fmul2_rn(x[{path['in_off'] + mi}], g[{slots[(p, mo)]}])"
+                coef = f"pair_of(sg * {_lit(c)})"
+                lines.append(f"float2 s = __fmul2_rn({prod}, {coef});" if k == 0 else f"s = __ffma2_rn({prod}, {coef}, s);")
+            ye = path["edge_off"] + me
+            out.append(f"        {{ {' '.join(lines)} dw = __ffma2_rn(s, pair_of(Y[{ye}]), dw); "
+                       f"dY[{ye}] = __ffma2_rn(w[{p}], s, dY[{ye}]); }}")
+        out.append(f"        dr = __ffma2_rn(wp[{p}], dw, dr);")
+        out.append("        if (NEED_DX) {")
+        for mi, terms in sorted(by_in.items()):
+            lines = []
+            for k, (me, mo, c) in enumerate(terms):
+                prod = f"__fmul2_rn(g[{slots[(p, mo)]}], pair_of(Y[{path['edge_off'] + me}]))"
+                coef = f"pair_of(sg * {_lit(c)})"
+                lines.append(f"float2 u = __fmul2_rn({prod}, {coef});" if k == 0 else f"u = __ffma2_rn({prod}, {coef}, u);")
+            xi = path["in_off"] + mi
+            out.append(f"            {{ {' '.join(lines)} dx[{xi}] = __ffma2_rn(w[{p}], u, dx[{xi}]); }}")
+        out.append("        }")
+        out.append("    }")
+    out += ["}", ""]
     # per-l blocks of the message layout for the host (base component, segments)
     out.append(f"template <> struct TpBlocks<{lin}> {{")
     out.append("    static constexpr int kBase[4] = {" + ", ".join(str(blocks[l][0]) for l in range(4)) + "};")

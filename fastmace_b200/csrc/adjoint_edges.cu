@@ -330,6 +330,170 @@ k_tp_adjoint_stream(int n_rows, const int32_t* __restrict__ row_ptr, const int32
     if (c == 0 && abort_sh && error_word) atomicOr(error_word, FMB_STATUS_TENSOR_TIMEOUT);
 }
 
+// The streamed adjoint with two channels per thread on the packed FP32 pipe (fma.rn.f32x2, sm_100): 64 threads per CTA,
+// the per-channel operands, the row's message gradient and the partial sums as pairs. The scalar form above issues 533
+// instructions per warp and edge for 32 channels and is bound by that; the pair form issues about as many for 64, and
+// its channel reductions run over half as many threads.
+template <int LIN> struct TpBackwardPairSel;
+#define FMB_TP_BACKWARD_PAIR_SEL(LIN_)                                                                                 \
+    template <> struct TpBackwardPairSel<LIN_> {                                                                       \
+        template <typename... A> static __device__ __forceinline__ void run(A&&... a) {                               \
+            tp_backward_pair_##LIN_<false, true>(a...);                                                                \
+        }                                                                                                              \
+    };
+FMB_TP_BACKWARD_PAIR_SEL(1)
+
+constexpr int kPairThreads = kC / 2;
+
+template <int LIN, int STAGES, int MINB>
+__global__ void __launch_bounds__(kPairThreads, MINB)
+k_tp_adjoint_pairs(int n_rows, const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ senders,
+                   const float* __restrict__ x, const float* __restrict__ edge_sh, const float* __restrict__ edge_vec,
+                   const float* __restrict__ tp_w, long long tangent_offset, const float* __restrict__ d_mid,
+                   float* __restrict__ dxe, float4* __restrict__ qe, uint32_t* __restrict__ error_word) {
+    constexpr int P = TpShape<LIN>::kPaths, IN = TpShape<LIN>::kInDim, MID = TpShape<LIN>::kMidDim;
+    constexpr int kW = P * kC;                              // floats of one edge's weights
+    constexpr int kStage = 2 * kW + IN * kC + 16;           // weights, d/dr, sender rows, harmonics
+    constexpr int kWarps = kPairThreads / 32;
+    extern __shared__ __align__(128) float ring[];          // [STAGES][kStage]
+    __shared__ uint64_t bars[2 * STAGES];
+    __shared__ int abort_sh, first_row_sh;
+    __shared__ float red[2][kAdjBatch][kWarps][18];
+    volatile int* abort_flag = &abort_sh;
+    const int c = threadIdx.x, warp = c >> 5, lane = c & 31;     // channels 2 c and 2 c + 1
+    const long long total = row_ptr[n_rows];
+    const long long per_cta = (total + gridDim.x - 1) / gridDim.x;
+    const long long eb = (long long)blockIdx.x * per_cta, ee = min(total, eb + per_cta);
+    if (eb >= ee) return;
+    const uint32_t bar0 = tc::smem_u32(bars), ring0 = tc::smem_u32(ring);
+    if (c == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            tc::mbar_init(bar0 + 8 * s, 1);                        // full
+            tc::mbar_init(bar0 + 8 * (STAGES + s), kWarps);        // empty: one arrival per warp
+        }
+        abort_sh = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    long long issued = eb;
+    int issue_stage = 0;
+    uint32_t issue_parity = 1;
+    int next_sender = c == 0 ? senders[eb] : 0;
+    auto issue = [&]() {
+        tc::mbar_wait(bar0 + 8 * (STAGES + issue_stage), issue_parity, abort_flag, kAdjSpin);
+        const uint32_t full = bar0 + 8 * issue_stage;
+        const uint32_t dst = ring0 + issue_stage * (kStage * 4);
+        tc::mbar_expect_tx(full, kStage * 4);
+        tc::bulk_load(dst, tp_w + issued * kW, kW * 4, full);
+        tc::bulk_load(dst + kW * 4, tp_w + tangent_offset + issued * kW, kW * 4, full);
+        tc::bulk_load(dst + 2 * kW * 4, x + (long long)next_sender * (IN * kC), IN * kC * 4, full);
+        tc::bulk_load(dst + (2 * kW + IN * kC) * 4, edge_sh + 16 * issued, 64, full);
+        ++issued;
+        if (issued < ee) next_sender = senders[issued];
+        if (++issue_stage == STAGES) { issue_stage = 0; issue_parity ^= 1u; }
+    };
+    if (c == 0) {
+        while (issued < ee && issued < eb + STAGES - 1) issue();
+        int lo = 0, hi = n_rows - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (row_ptr[mid] <= eb) lo = mid; else hi = mid - 1;
+        }
+        first_row_sh = lo;
+    }
+    __syncthreads();
+    int a = first_row_sh;
+    long long row_end = row_ptr[a + 1];
+    float2 g_a[MID];
+#pragma unroll
+    for (int k = 0; k < MID; ++k) g_a[k] = __ldg(reinterpret_cast<const float2*>(d_mid + ((long long)a * MID + k) * kC) + c);
+    int stage = 0, buf = 0;
+    uint32_t parity = 0;
+    for (long long batch = eb; batch < ee; batch += kAdjBatch) {
+        const int nb = (int)min((long long)kAdjBatch, ee - batch);
+        for (int k = 0; k < nb; ++k) {
+            const long long e = batch + k;
+            if (e >= row_end) {
+                do { ++a; row_end = row_ptr[a + 1]; } while (e >= row_end);
+#pragma unroll
+                for (int q = 0; q < MID; ++q)
+                    g_a[q] = __ldg(reinterpret_cast<const float2*>(d_mid + ((long long)a * MID + q) * kC) + c);
+            }
+            if (c == 0 && issued < ee && issued < e + STAGES) issue();
+            float Y[16];
+            float2 w[P], wp[P], x_j[IN], dY2[16], dxj[IN];
+            tc::mbar_wait(bar0 + 8 * stage, parity, abort_flag, kAdjSpin);
+            {
+                const float* st = ring + stage * kStage;
+#pragma unroll
+                for (int p = 0; p < P; ++p) {
+                    w[p] = reinterpret_cast<const float2*>(st + p * kC)[c];
+                    wp[p] = reinterpret_cast<const float2*>(st + kW + p * kC)[c];
+                }
+#pragma unroll
+                for (int q = 0; q < IN; ++q) {
+                    x_j[q] = reinterpret_cast<const float2*>(st + 2 * kW + q * kC)[c];
+                    dxj[q] = make_float2(0.0f, 0.0f);
+                }
+                const float4* yp = reinterpret_cast<const float4*>(st + 2 * kW + IN * kC);
+                const float4 y0 = yp[0], y1 = yp[1], y2 = yp[2], y3 = yp[3];
+                Y[0] = y0.x; Y[1] = y0.y; Y[2] = y0.z; Y[3] = y0.w; Y[4] = y1.x; Y[5] = y1.y; Y[6] = y1.z; Y[7] = y1.w;
+                Y[8] = y2.x; Y[9] = y2.y; Y[10] = y2.z; Y[11] = y2.w; Y[12] = y3.x; Y[13] = y3.y; Y[14] = y3.z; Y[15] = y3.w;
+            }
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(bar0 + 8 * (STAGES + stage));
+            if (++stage == STAGES) { stage = 0; parity ^= 1u; }
+#pragma unroll
+            for (int q = 0; q < 16; ++q) dY2[q] = make_float2(0.0f, 0.0f);
+            float2 dr2 = make_float2(0.0f, 0.0f);
+            TpBackwardPairSel<LIN>::run(x_j, Y, w, wp, g_a, dY2, dr2, dxj);
+#pragma unroll
+            for (int q = 0; q < IN; ++q) reinterpret_cast<float2*>(dxe + (e * IN + q) * kC)[c] = dxj[q];
+            float dY[16];
+#pragma unroll
+            for (int q = 0; q < 16; ++q) dY[q] = dY2[q].x + dY2[q].y;
+            float dr = dr2.x + dr2.y;
+            {
+#pragma unroll
+                for (int half = 8, bit = 16; half >= 1; half >>= 1, bit >>= 1) {
+                    const bool upper = (lane & bit) != 0;
+#pragma unroll
+                    for (int i = 0; i < half; ++i) {
+                        const float keep = upper ? dY[i + half] : dY[i];
+                        const float send = upper ? dY[i] : dY[i + half];
+                        dY[i] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
+                    }
+                }
+                dY[0] += __shfl_xor_sync(0xffffffffu, dY[0], 1);
+            }
+            dr = warp_sum(dr);
+            if ((lane & 1) == 0) red[buf][k][warp][lane >> 1] = dY[0];
+            if (lane == 0) red[buf][k][warp][16] = dr;
+        }
+        __syncthreads();
+        if (c < nb) {
+            const long long e = batch + c;
+            float g[16];
+#pragma unroll
+            for (int q = 0; q < 16; ++q) {
+                g[q] = red[buf][c][0][q];
+#pragma unroll
+                for (int ww = 1; ww < kWarps; ++ww) g[q] += red[buf][c][ww][q];
+            }
+            float drt = red[buf][c][0][16];
+#pragma unroll
+            for (int ww = 1; ww < kWarps; ++ww) drt += red[buf][c][ww][16];
+            const float4 uv = __ldg(reinterpret_cast<const float4*>(edge_vec) + e);
+            float q3[3];
+            edge_vector_gradient(g, drt, uv.x, uv.y, uv.z, uv.w, q3);
+            qe[e] = make_float4(q3[0], q3[1], q3[2], 0.0f);
+        }
+        buf ^= 1;
+    }
+    __syncthreads();
+    if (c == 0 && abort_sh && error_word) atomicOr(error_word, FMB_STATUS_TENSOR_TIMEOUT);
+}
+
 // dE/dx_a = sum over the row of a of the hand-over of the mirror edges (rows at or beyond n_source hand over nothing)
 template <int IN>
 __global__ void __launch_bounds__(kC)
@@ -516,16 +680,16 @@ int tp_adjoint_edges(const EdgeAdjointArgs& t, cudaStream_t stream) {
     } else if (t.lin == 1 && t.whole_list && t.n_valid >= t.n_rows && t.chunk_e0 == 0) {
         constexpr int kStages = FMB_ADJ_STAGES, kMinB = FMB_ADJ_MINB;
         constexpr int smem = kStages * (2 * TpShape<1>::kPaths * kC + TpShape<1>::kInDim * kC + 16) * 4;
-        auto kernel = k_tp_adjoint_stream<1, kStages, kMinB>;
+        auto kernel = k_tp_adjoint_pairs<1, kStages, kMinB>;
         FMB_CUDA_CHECK(opt_in_shared_memory((const void*)kernel, smem));
         static int grid_cap = 0;
         if (grid_cap == 0) {
             int per_sm = 0, sms = 148, dev = 0;
-            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kC, smem) != cudaSuccess || per_sm < 1) per_sm = 1;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kPairThreads, smem) != cudaSuccess || per_sm < 1) per_sm = 1;
             if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
             grid_cap = per_sm * sms;
         }
-        kernel<<<grid_cap, kC, smem, stream>>>(
+        kernel<<<grid_cap, kPairThreads, smem, stream>>>(
             t.n_rows, t.row_ptr, t.senders, t.x, t.edge_sh, t.edge_vec, t.tp_w, t.tangent_offset, t.d_mid, t.dxe,
             reinterpret_cast<float4*>(t.qe), t.error_word);
     } else if (t.lin == 1) {

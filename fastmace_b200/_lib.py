@@ -83,6 +83,7 @@ class WorkStruct(ctypes.Structure):
         ("partial", c_void_p), ("energy", c_void_p), ("forces", c_void_p), ("stress", c_void_p), ("status", c_void_p),
         ("n_energy_atoms", c_int32), ("n_inner_atoms", c_int32),
         ("mirror", c_void_p), ("edge_q", c_void_p), ("edge_dx", c_void_p),
+        ("edge_slot", c_void_p), ("canon_list", c_void_p), ("canon_count", c_void_p),
         ("symcon_groups", c_void_p), ("n_symcon_groups", c_int32), ("halo_exchange", c_int32),
     ]
 

@@ -46,11 +46,17 @@ constexpr int kAdjBatch = 16;          // edges between two CTA barriers of the 
 #define FMB_ADJ_MINB 4
 #endif
 
-// mirror[e] = index of the edge (sender = receiver(e), receiver = sender(e), image = -image(e)), or -1
+// mirror[e] = index of the edge (sender = receiver(e), receiver = sender(e), image = -image(e)), or -1. With `slot`:
+// the edges below *listed_below that stand for their pair (no opposite edge, or the lower index of the two) are listed
+// in `list` and get the position as their slot (the order of the list depends on the atomics; the slots are only
+// names of rows).
 __global__ void k_mirror(const long long* __restrict__ count_ptr, int capacity, const int32_t* __restrict__ edge_index,
                          const float* __restrict__ unit_shifts, const int32_t* __restrict__ row_ptr,
-                         int32_t* __restrict__ mirror, uint32_t* __restrict__ status) {
+                         int32_t* __restrict__ mirror, uint32_t* __restrict__ status,
+                         const long long* __restrict__ listed_below, int32_t* __restrict__ slot,
+                         int32_t* __restrict__ list, unsigned long long* __restrict__ list_count) {
     const long long count = *count_ptr;
+    const long long listed = slot ? *listed_below : 0;
     for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < count; e += (long long)gridDim.x * blockDim.x) {
         const int s = edge_index[e], r = edge_index[capacity + e];
         const float u0 = -unit_shifts[3 * e], u1 = -unit_shifts[3 * e + 1], u2 = -unit_shifts[3 * e + 2];
@@ -70,6 +76,11 @@ __global__ void k_mirror(const long long* __restrict__ count_ptr, int capacity, 
         }
         mirror[e] = found;
         if (found < 0) atomicOr(status, FMB_STATUS_NO_MIRROR);
+        if (slot && e < listed && (found < 0 || e < found)) {
+            const int k = (int)atomicAdd(list_count, 1ull);
+            slot[e] = k;
+            list[k] = (int)e;
+        }
     }
 }
 
@@ -177,163 +188,18 @@ k_tp_adjoint_edges(int n_atoms, int n_rows, int n_valid, long long chunk_e0, lon
     }
 }
 
-// The same adjoint with every per-edge operand streamed through shared memory (whole edge list in one launch, every
-// row carries a gradient). The kernel above asks for an edge's 2 P C weights, its sender's rows and its harmonics when
-// it gets to the edge and then waits for them (2.6 warps stalled on loads per issued instruction, issue slots 54 %
-// busy). Here a CTA owns a contiguous block of receivers, so its edges are a contiguous range, and one thread keeps
-// kAdjStages - 1 edges ahead of the consumers with bulk copies that complete on mbarriers: per edge the weights, their
-// d/dr, the sender's feature rows and the 16 harmonics. A stage is handed back by one arrival per warp.
+// The adjoint with every per-edge operand streamed through shared memory (whole edge list in one launch, every row
+// carries a gradient) and two channels per thread on the packed FP32 pipe (fma.rn.f32x2, sm_100). The direct-load
+// kernel above asks for an edge's 2 P C weights, its sender's rows and its harmonics when it gets to the edge and
+// waits for them; its CTAs take whole rows (a tail of 14 % of the SM time on 1,944 atoms) and meet twice per eight
+// edges. Here every CTA takes the same number of edges (an edge is independent of the others of its row), one thread
+// keeps STAGES - 1 edges ahead of the consumers with bulk copies that complete on mbarriers -- per edge the weights,
+// their d/dr, the sender's feature rows and the 16 harmonics -- a stage is handed back by one arrival per warp, and
+// the CTA meets once per 16 edges. 64 threads per CTA: the per-channel operands, the row's message gradient and the
+// partial sums are pairs. The scalar form issued 533 instructions per warp and edge for 32 channels and was bound by
+// that; the pair form issues about as many for 64.
 constexpr unsigned kAdjSpin = 1u << 20;
 
-template <int LIN, int STAGES, int MINB>
-__global__ void __launch_bounds__(kC, MINB)
-k_tp_adjoint_stream(int n_rows, const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ senders,
-                    const float* __restrict__ x, const float* __restrict__ edge_sh, const float* __restrict__ edge_vec,
-                    const float* __restrict__ tp_w, long long tangent_offset, const float* __restrict__ d_mid,
-                    float* __restrict__ dxe, float4* __restrict__ qe, uint32_t* __restrict__ error_word) {
-    constexpr int P = TpShape<LIN>::kPaths, IN = TpShape<LIN>::kInDim, MID = TpShape<LIN>::kMidDim;
-    constexpr int kW = P * kC;                              // floats of one edge's weights
-    constexpr int kStage = 2 * kW + IN * kC + 16;           // weights, d/dr, sender rows, harmonics
-    extern __shared__ __align__(128) float ring[];          // [STAGES][kStage]
-    __shared__ uint64_t bars[2 * STAGES];
-    __shared__ int abort_sh, first_row_sh;
-    __shared__ float red[2][kAdjBatch][4][18];
-    volatile int* abort_flag = &abort_sh;
-    const int c = threadIdx.x, warp = c >> 5, lane = c & 31;
-    // every CTA takes the same number of edges (an edge is independent of the others of its row here): the range
-    // [eb, ee) of the receiver-sorted list, starting inside row `a`
-    const long long total = row_ptr[n_rows];
-    const long long per_cta = (total + gridDim.x - 1) / gridDim.x;
-    const long long eb = (long long)blockIdx.x * per_cta, ee = min(total, eb + per_cta);
-    if (eb >= ee) return;
-    const uint32_t bar0 = tc::smem_u32(bars), ring0 = tc::smem_u32(ring);
-    if (c == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            tc::mbar_init(bar0 + 8 * s, 1);                    // full
-            tc::mbar_init(bar0 + 8 * (STAGES + s), 4);         // empty: one arrival per warp
-        }
-        abort_sh = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-    // thread 0: the next edge to request, its stage and the parity its `empty` barrier must have passed; the sender
-    // index is read one request ahead so that its latency is not on the path
-    long long issued = eb;
-    int issue_stage = 0;
-    uint32_t issue_parity = 1;
-    int next_sender = c == 0 ? senders[eb] : 0;
-    auto issue = [&]() {
-        tc::mbar_wait(bar0 + 8 * (STAGES + issue_stage), issue_parity, abort_flag, kAdjSpin);
-        const uint32_t full = bar0 + 8 * issue_stage;
-        const uint32_t dst = ring0 + issue_stage * (kStage * 4);
-        tc::mbar_expect_tx(full, kStage * 4);
-        tc::bulk_load(dst, tp_w + issued * kW, kW * 4, full);
-        tc::bulk_load(dst + kW * 4, tp_w + tangent_offset + issued * kW, kW * 4, full);
-        tc::bulk_load(dst + 2 * kW * 4, x + (long long)next_sender * (IN * kC), IN * kC * 4, full);
-        tc::bulk_load(dst + (2 * kW + IN * kC) * 4, edge_sh + 16 * issued, 64, full);
-        ++issued;
-        if (issued < ee) next_sender = senders[issued];
-        if (++issue_stage == STAGES) { issue_stage = 0; issue_parity ^= 1u; }
-    };
-    if (c == 0) {
-        while (issued < ee && issued < eb + STAGES - 1) issue();
-        // the row of the first edge: the last row that starts at or before eb (the copies above are on their way)
-        int lo = 0, hi = n_rows - 1;
-        while (lo < hi) {
-            const int mid = (lo + hi + 1) >> 1;
-            if (row_ptr[mid] <= eb) lo = mid; else hi = mid - 1;
-        }
-        first_row_sh = lo;
-    }
-    __syncthreads();
-    int a = first_row_sh;
-    long long row_end = row_ptr[a + 1];
-    float g_a[MID];
-#pragma unroll
-    for (int k = 0; k < MID; ++k) g_a[k] = __ldg(d_mid + ((long long)a * MID + k) * kC + c);
-    int stage = 0, buf = 0;
-    uint32_t parity = 0;
-    for (long long batch = eb; batch < ee; batch += kAdjBatch) {
-        const int nb = (int)min((long long)kAdjBatch, ee - batch);
-        for (int k = 0; k < nb; ++k) {
-            const long long e = batch + k;
-            if (e >= row_end) {
-                do { ++a; row_end = row_ptr[a + 1]; } while (e >= row_end);
-#pragma unroll
-                for (int q = 0; q < MID; ++q) g_a[q] = __ldg(d_mid + ((long long)a * MID + q) * kC + c);
-            }
-            // the stage the previous edge used has been handed back by now (or will be at once): refill it
-            if (c == 0 && issued < ee && issued < e + STAGES) issue();
-            float Y[16], w[P], wp[P], x_j[IN], dY[16], dxj[IN];
-            tc::mbar_wait(bar0 + 8 * stage, parity, abort_flag, kAdjSpin);
-            {
-                const float* st = ring + stage * kStage;
-#pragma unroll
-                for (int p = 0; p < P; ++p) {
-                    w[p] = st[p * kC + c];
-                    wp[p] = st[kW + p * kC + c];
-                }
-#pragma unroll
-                for (int q = 0; q < IN; ++q) {
-                    x_j[q] = st[2 * kW + q * kC + c];
-                    dxj[q] = 0.0f;
-                }
-                const float4* yp = reinterpret_cast<const float4*>(st + 2 * kW + IN * kC);
-                const float4 y0 = yp[0], y1 = yp[1], y2 = yp[2], y3 = yp[3];
-                Y[0] = y0.x; Y[1] = y0.y; Y[2] = y0.z; Y[3] = y0.w; Y[4] = y1.x; Y[5] = y1.y; Y[6] = y1.z; Y[7] = y1.w;
-                Y[8] = y2.x; Y[9] = y2.y; Y[10] = y2.z; Y[11] = y2.w; Y[12] = y3.x; Y[13] = y3.y; Y[14] = y3.z; Y[15] = y3.w;
-            }
-            __syncwarp();
-            if (lane == 0) tc::mbar_arrive(bar0 + 8 * (STAGES + stage));
-            if (++stage == STAGES) { stage = 0; parity ^= 1u; }
-#pragma unroll
-            for (int q = 0; q < 16; ++q) dY[q] = 0.0f;
-            float dr = 0.0f;
-            TpBackwardSel<LIN, false, true>::run(x_j, Y, w, wp, g_a, dY, dr, dxj);
-#pragma unroll
-            for (int q = 0; q < IN; ++q) dxe[(e * IN + q) * kC + c] = dxj[q];
-            // 16 + 1 sums over the channels: transpose-reduce inside the warp, the four warps meet in shared memory
-            {
-#pragma unroll
-                for (int half = 8, bit = 16; half >= 1; half >>= 1, bit >>= 1) {
-                    const bool upper = (lane & bit) != 0;
-#pragma unroll
-                    for (int i = 0; i < half; ++i) {
-                        const float keep = upper ? dY[i + half] : dY[i];
-                        const float send = upper ? dY[i] : dY[i + half];
-                        dY[i] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
-                    }
-                }
-                dY[0] += __shfl_xor_sync(0xffffffffu, dY[0], 1);
-            }
-            dr = warp_sum(dr);
-            if ((lane & 1) == 0) red[buf][k][warp][lane >> 1] = dY[0];
-            if (lane == 0) red[buf][k][warp][16] = dr;
-        }
-        // one barrier per batch: the sums alternate between two buffers, and the threads that finish a batch (in warp
-        // 0) reach the next barrier only after they have read it, which is before anyone writes that buffer again
-        __syncthreads();
-        if (c < nb) {
-            const long long e = batch + c;
-            float g[16];
-#pragma unroll
-            for (int q = 0; q < 16; ++q) g[q] = red[buf][c][0][q] + red[buf][c][1][q] + red[buf][c][2][q] + red[buf][c][3][q];
-            const float drt = red[buf][c][0][16] + red[buf][c][1][16] + red[buf][c][2][16] + red[buf][c][3][16];
-            const float4 uv = __ldg(reinterpret_cast<const float4*>(edge_vec) + e);
-            float q3[3];
-            edge_vector_gradient(g, drt, uv.x, uv.y, uv.z, uv.w, q3);
-            qe[e] = make_float4(q3[0], q3[1], q3[2], 0.0f);
-        }
-        buf ^= 1;
-    }
-    __syncthreads();
-    if (c == 0 && abort_sh && error_word) atomicOr(error_word, FMB_STATUS_TENSOR_TIMEOUT);
-}
-
-// The streamed adjoint with two channels per thread on the packed FP32 pipe (fma.rn.f32x2, sm_100): 64 threads per CTA,
-// the per-channel operands, the row's message gradient and the partial sums as pairs. The scalar form above issues 533
-// instructions per warp and edge for 32 channels and is bound by that; the pair form issues about as many for 64, and
-// its channel reductions run over half as many threads.
 template <int LIN> struct TpBackwardPairSel;
 #define FMB_TP_BACKWARD_PAIR_SEL(LIN_)                                                                                 \
     template <> struct TpBackwardPairSel<LIN_> {                                                                       \
@@ -350,7 +216,8 @@ __global__ void __launch_bounds__(kPairThreads, MINB)
 k_tp_adjoint_pairs(int n_rows, const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ senders,
                    const float* __restrict__ x, const float* __restrict__ edge_sh, const float* __restrict__ edge_vec,
                    const float* __restrict__ tp_w, long long tangent_offset, const float* __restrict__ d_mid,
-                   float* __restrict__ dxe, float4* __restrict__ qe, uint32_t* __restrict__ error_word) {
+                   float* __restrict__ dxe, float4* __restrict__ qe, uint32_t* __restrict__ error_word,
+                   const int32_t* __restrict__ mirror, const int32_t* __restrict__ slot) {
     constexpr int P = TpShape<LIN>::kPaths, IN = TpShape<LIN>::kInDim, MID = TpShape<LIN>::kMidDim;
     constexpr int kW = P * kC;                              // floats of one edge's weights
     constexpr int kStage = 2 * kW + IN * kC + 16;           // weights, d/dr, sender rows, harmonics
@@ -379,17 +246,28 @@ k_tp_adjoint_pairs(int n_rows, const int32_t* __restrict__ row_ptr, const int32_
     int issue_stage = 0;
     uint32_t issue_parity = 1;
     int next_sender = c == 0 ? senders[eb] : 0;
+    // the row of tp_w that holds an edge's weights: its own, or with one row per pair of opposite edges the slot of
+    // the lower edge of the pair
+    auto row_of = [&](long long e) -> long long {
+        if (!slot) return e;
+        const int m = mirror[e];
+        return slot[(m < 0 || e < m) ? e : (long long)m];
+    };
+    long long next_row = c == 0 ? row_of(eb) : 0;
     auto issue = [&]() {
         tc::mbar_wait(bar0 + 8 * (STAGES + issue_stage), issue_parity, abort_flag, kAdjSpin);
         const uint32_t full = bar0 + 8 * issue_stage;
         const uint32_t dst = ring0 + issue_stage * (kStage * 4);
         tc::mbar_expect_tx(full, kStage * 4);
-        tc::bulk_load(dst, tp_w + issued * kW, kW * 4, full);
-        tc::bulk_load(dst + kW * 4, tp_w + tangent_offset + issued * kW, kW * 4, full);
+        tc::bulk_load(dst, tp_w + next_row * kW, kW * 4, full);
+        tc::bulk_load(dst + kW * 4, tp_w + tangent_offset + next_row * kW, kW * 4, full);
         tc::bulk_load(dst + 2 * kW * 4, x + (long long)next_sender * (IN * kC), IN * kC * 4, full);
         tc::bulk_load(dst + (2 * kW + IN * kC) * 4, edge_sh + 16 * issued, 64, full);
         ++issued;
-        if (issued < ee) next_sender = senders[issued];
+        if (issued < ee) {
+            next_sender = senders[issued];
+            next_row = row_of(issued);
+        }
         if (++issue_stage == STAGES) { issue_stage = 0; issue_parity ^= 1u; }
     };
     if (c == 0) {
@@ -661,10 +539,13 @@ int grid_for(const void* kernel, int rows, int threads, size_t smem) {
 
 }  // namespace
 
-int mirror_map(const fmb_nl_t* nl, int32_t* mirror, uint32_t* status, cudaStream_t stream) {
+int mirror_map(const fmb_nl_t* nl, int32_t* mirror, uint32_t* status, const long long* listed_below, int32_t* slot,
+               int32_t* list, long long* list_count, cudaStream_t stream) {
     const int blocks = ceil_div(nl->capacity, 256);
+    if (slot) FMB_CUDA_CHECK(cudaMemsetAsync(list_count, 0, sizeof(long long), stream));
     k_mirror<<<blocks < 1184 ? blocks : 1184, 256, 0, stream>>>((const long long*)nl->count, nl->capacity, nl->edge_index,
-                                                               nl->unit_shifts, nl->edge_row_ptr, mirror, status);
+                                                               nl->unit_shifts, nl->edge_row_ptr, mirror, status,
+                                                               listed_below, slot, list, (unsigned long long*)list_count);
     FMB_LAUNCH_CHECK();
     return FMB_OK;
 }
@@ -691,7 +572,7 @@ int tp_adjoint_edges(const EdgeAdjointArgs& t, cudaStream_t stream) {
         }
         kernel<<<grid_cap, kPairThreads, smem, stream>>>(
             t.n_rows, t.row_ptr, t.senders, t.x, t.edge_sh, t.edge_vec, t.tp_w, t.tangent_offset, t.d_mid, t.dxe,
-            reinterpret_cast<float4*>(t.qe), t.error_word);
+            reinterpret_cast<float4*>(t.qe), t.error_word, t.mirror, t.slot);
     } else if (t.lin == 1) {
         // four CTAs per SM (127 registers): measured best on the 1,944-atom cell among 2 .. 6
         static const int grid_cap = grid_for((const void*)k_tp_adjoint_edges<1, 4>, 1 << 30, kC, 0);

@@ -167,6 +167,15 @@ const long long* edge_limit(const Ctx& c, int which) {
     return plain_rows(c) ? (const long long*)c.nl->count : edge_limits(c) + which;
 }
 
+// One row of radial weights per pair of opposite edges (they have the same length): the whole list is one chunk whose
+// weights are kept, the per-edge adjoint's mirror map exists, and the kernels that read the rows by slot are the ones
+// that run (node l_max 1, tensor-core producer).
+bool pair_rows(const Ctx& c) {
+    const int last = c.m->n_layers - 1;
+    return last > 0 && keeps_forward_weights(c, last) && edge_local_adjoint(c) && c.w->edge_slot && c.w->canon_list &&
+           c.w->canon_count && c.m->layer[last].l_in_max == 1 && c.m->layer[last].rad_img != nullptr;
+}
+
 // first .. last: 0 = values, 1 = their d/dr (second half of tp_w)
 // `stream` / `max_ctas`: the producer can run on the side stream with fewer CTAs than SMs (it is one persistent CTA per
 // SM with all of its shared and tensor memory, so the SMs it leaves free are what the kernels beside it run on)
@@ -178,11 +187,13 @@ int radial_weights(const Ctx& c, int layer, long long e0, int first, int last, c
     StageScope scope(stream, kStRadial);
     if (L.rad_img && tensor_cores_enabled()) {
         // the fused kernels' tensor-core pipeline as a plain producer (one launch per matrix)
+        const bool pairs = layer == c.m->n_layers - 1 && pair_rows(c);
+        if (pairs) limit = c.w->canon_count;              // the listed edges, one row each
         bool done = true;
         for (int tangent = first; tangent <= last && done; ++tangent) {
             const int rc = radial_weights_tc(hidden_of(c, layer, tangent) + e0 * kRadial, L.rad_img,
                                              c.w->tp_w + (long long)tangent * c.chunk * L.n_paths * kC, (int)rows, L.n_paths,
-                                             limit, e0, c.w->status, max_ctas, stream);
+                                             limit, e0, pairs ? c.w->canon_list : nullptr, c.w->status, max_ctas, stream);
             if (rc == FMB_ERR_UNSUPPORTED) done = false;
             else if (rc) return rc;
         }
@@ -344,6 +355,7 @@ int forward_layer(const Ctx& c, int layer, bool with_up = true) {
         t.chunk_e0 = e0; t.chunk_edges = c.chunk; t.whole_list = c.n_chunks == 1; t.error_word = c.w->status;
         t.count = (const long long*)c.nl->count; t.row_ptr = c.nl->edge_row_ptr; t.senders = c.nl->edge_index;
         t.species = c.w->species; t.x = x; t.edge_sh = c.w->edge_sh; t.tp_w = c.w->tp_w; t.mid = c.w->mid;
+        if (layer == c.m->n_layers - 1 && pair_rows(c)) { t.mirror = c.w->mirror; t.slot = c.w->edge_slot; }
         StageScope scope(c.stream, layer == 0 ? kStTpFwd0 : kStTpFwd1);
         FMB_TRY(tp_forward_launch(t, c.stream));
     }
@@ -443,6 +455,7 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
         t.edge_sh = c.w->edge_sh; t.edge_vec = c.w->edge_vec; t.tp_w = c.w->tp_w;
         t.tangent_offset = c.chunk * L.n_paths * kC; t.d_mid = c.w->d_mid; t.dxe = c.w->edge_dx; t.qe = c.w->edge_q;
         t.d_x = c.w->d_x; t.whole_list = c.n_chunks == 1; t.error_word = c.w->status;
+        if (layer == c.m->n_layers - 1 && pair_rows(c)) t.slot = c.w->edge_slot;
         for (int k = 0; k < c.n_chunks; ++k) {
             const long long e0 = (long long)k * c.chunk;
             if (c.radial_ready) {
@@ -543,8 +556,13 @@ extern "C" FMB_API int fmb_edge_features(const fmb_model_t* model, const fmb_nl_
     const int rc = edge_features(model, nl, work, positions, limit, (cudaStream_t)stream);
     if (rc) return rc;
     // opposite-edge map for the per-edge adjoint (the compaction reorders edges every step)
-    if (work->mirror && work->edge_q && work->edge_dx)
-        return mirror_map(nl, work->mirror, work->status, (cudaStream_t)stream);
+    if (work->mirror && work->edge_q && work->edge_dx) {
+        Ctx c;
+        FMB_TRY(make_ctx(c, model, nl, work, (cudaStream_t)stream));
+        const bool pairs = pair_rows(c);
+        return mirror_map(nl, work->mirror, work->status, limit ? limit : (const long long*)nl->count,
+                          pairs ? work->edge_slot : nullptr, work->canon_list, work->canon_count, (cudaStream_t)stream);
+    }
     return FMB_OK;
 }
 

@@ -205,7 +205,8 @@ template <int LIN>
 __global__ void __launch_bounds__(kPairThreads)
 k_tp_forward_pairs(int n_rows, const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ senders,
                    const float* __restrict__ x, const float* __restrict__ edge_sh, const float* __restrict__ tp_w,
-                   float* __restrict__ mid, uint32_t* __restrict__ error_word) {
+                   float* __restrict__ mid, uint32_t* __restrict__ error_word, const int32_t* __restrict__ mirror,
+                   const int32_t* __restrict__ slot) {
     constexpr int P = TpShape<LIN>::kPaths, IN = TpShape<LIN>::kInDim, MID = TpShape<LIN>::kMidDim;
     constexpr int kRow = P * kC;                       // floats of one edge's weights
     constexpr int kStage = kRow + IN * kC + 16;        // weights, sender rows, harmonics
@@ -232,16 +233,27 @@ k_tp_forward_pairs(int n_rows, const int32_t* __restrict__ row_ptr, const int32_
     int issue_stage = 0;
     uint32_t issue_parity = 1;
     int next_sender = (c == 0 && eb < ee) ? senders[eb] : 0;
+    // the row of tp_w that holds an edge's weights: its own, or with one row per pair of opposite edges the slot of
+    // the lower edge of the pair
+    auto row_of = [&](long long e) -> long long {
+        if (!slot) return e;
+        const int m = mirror[e];
+        return slot[(m < 0 || e < m) ? e : (long long)m];
+    };
+    long long next_row = (c == 0 && eb < ee) ? row_of(eb) : 0;
     auto issue = [&]() {
         tc::mbar_wait(bar0 + 8 * (kFwdStages + issue_stage), issue_parity, abort_flag, kFwdSpin);
         const uint32_t full = bar0 + 8 * issue_stage;
         const uint32_t dst = ring0 + issue_stage * (kStage * 4);
         tc::mbar_expect_tx(full, kStage * 4);
-        tc::bulk_load(dst, tp_w + issued * kRow, kRow * 4, full);
+        tc::bulk_load(dst, tp_w + next_row * kRow, kRow * 4, full);
         tc::bulk_load(dst + kRow * 4, x + (long long)next_sender * (IN * kC), IN * kC * 4, full);
         tc::bulk_load(dst + (kRow + IN * kC) * 4, edge_sh + 16 * issued, 64, full);
         ++issued;
-        if (issued < ee) next_sender = senders[issued];
+        if (issued < ee) {
+            next_sender = senders[issued];
+            next_row = row_of(issued);
+        }
         if (++issue_stage == kFwdStages) { issue_stage = 0; issue_parity ^= 1u; }
     };
     if (c == 0)
@@ -655,7 +667,7 @@ int tp_forward_launch(const TpArgs& t, cudaStream_t stream) {
         }
         const int grid = t.n_rows < grid_cap ? t.n_rows : grid_cap;
         k_tp_forward_pairs<1><<<grid, kPairThreads, smem, stream>>>(t.n_rows, t.row_ptr, t.senders, t.x, t.edge_sh, t.tp_w,
-                                                                    t.mid, t.error_word);
+                                                                    t.mid, t.error_word, t.mirror, t.slot);
     } else if (t.whole_list && t.lin == 2) {
         FMB_FWD_STREAM(2)
     } else if (t.lin == 1) {

@@ -33,6 +33,8 @@ struct TpArgs {
     float* atom_virial;
     int first_layer_of_pass;
     uint32_t* error_word;  // device status word for bounded-wait failures of the staged kernels
+    const int32_t* mirror; // with `slot`: the weights of edge e are row slot[min(e, mirror[e])] of tp_w (one row per pair)
+    const int32_t* slot;
 };
 int tp_forward_launch(const TpArgs& t, cudaStream_t stream);
 int tp_backward_launch(const TpArgs& t, cudaStream_t stream);
@@ -65,8 +67,10 @@ int tp_fused_forward(const FusedArgs& f, cudaStream_t stream);
 
 // Per-edge radial weights (or their d/dr) [rows][n_paths * 128] = hidden [rows][64] x last radial layer, through the
 // fused kernels' tensor-core pipeline (tp_fused.cu); FMB_ERR_UNSUPPORTED without the weight image.
+// `row_index` (or null): output row r is computed from hidden row row_index[r]
 int radial_weights_tc(const float* hidden, const float* image, float* out, int rows, int n_paths, const long long* limit,
-                      long long limit_offset, uint32_t* error_word, int max_ctas, cudaStream_t stream);
+                      long long limit_offset, const int32_t* row_index, uint32_t* error_word, int max_ctas,
+                      cudaStream_t stream);
 
 // first layer in reassociated form (outer products per receiver and sender species)
 struct FirstArgs {
@@ -111,8 +115,11 @@ struct EdgeAdjointArgs {
     float* d_x;                    // [n_rows][(lin + 1)^2][C]
     bool whole_list;               // the launch covers the whole edge list (tp_w holds every edge's weights)
     uint32_t* error_word;
+    const int32_t* slot;           // or null: the weights of edge e are row slot[min(e, mirror[e])] of tp_w
 };
-int mirror_map(const fmb_nl_t* nl, int32_t* mirror, uint32_t* status, cudaStream_t stream);
+// `slot`, `list`, `list_count` (or null): the edges below *listed_below that stand for their pair
+int mirror_map(const fmb_nl_t* nl, int32_t* mirror, uint32_t* status, const long long* listed_below, int32_t* slot,
+               int32_t* list, long long* list_count, cudaStream_t stream);
 // per-edge adjoint of an interaction after the first for one chunk of edges; after the last chunk the gather of the
 // sender-side gradients into d_x
 int tp_adjoint_edges(const EdgeAdjointArgs& t, cudaStream_t stream);

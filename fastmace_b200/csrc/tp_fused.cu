@@ -392,6 +392,7 @@ struct WeightArgs {
     int rows;                     // host bound on the rows of this launch
     int n_paths;
     uint32_t* error_word;
+    const int32_t* row_index;     // or null: output row r comes from hidden row row_index[r]
 };
 
 constexpr int kWeightStages = 4;
@@ -464,7 +465,8 @@ k_radial_weights(const __grid_constant__ WeightArgs a) {
             for (int sweep = 0; sweep < TN / 64; ++sweep) {
                 const int row = ld_row + 64 * sweep;
                 const bool ok = e0 + row < rows;
-                const float* src = a.hidden + (e0 + row) * kRadial;
+                const long long source = a.row_index ? (ok ? (long long)a.row_index[e0 + row] : 0) : e0 + row;
+                const float* src = a.hidden + source * kRadial;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const float4 v = ok ? __ldg(reinterpret_cast<const float4*>(src) + ld_q + 4 * j) : zero4;
@@ -530,7 +532,8 @@ int launch_fused(const FusedArgs& f, cudaStream_t stream) {
 }  // namespace
 
 int radial_weights_tc(const float* hidden, const float* image, float* out, int rows, int n_paths, const long long* limit,
-                      long long limit_offset, uint32_t* error_word, int max_ctas, cudaStream_t stream) {
+                      long long limit_offset, const int32_t* row_index, uint32_t* error_word, int max_ctas,
+                      cudaStream_t stream) {
     if (!image || n_paths < 1) return FMB_ERR_UNSUPPORTED;
     if (rows <= 0) return FMB_OK;
     static int sms = 0;
@@ -541,7 +544,7 @@ int radial_weights_tc(const float* hidden, const float* image, float* out, int r
         FMB_CUDA_CHECK(cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev));
         sms = count;
     }
-    WeightArgs a{hidden, image, out, limit, limit_offset, rows, n_paths, error_word};
+    WeightArgs a{hidden, image, out, limit, limit_offset, rows, n_paths, error_word, row_index};
     const int tiles = (rows + kWeightTile - 1) / kWeightTile;
     const int ctas = max_ctas > 0 && max_ctas < sms ? max_ctas : sms;
     k_radial_weights<<<tiles < ctas ? tiles : ctas, kFusedThreads, kWeightBytes, stream>>>(a);

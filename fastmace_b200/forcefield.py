@@ -241,9 +241,12 @@ class B200ForceField:
                 buf["mirror"] = torch.zeros(cap, dtype=torch.int32, device=dev)
                 buf["edge_q"] = torch.zeros(cap, 4, **f32)
                 buf["edge_dx"] = torch.zeros(cap, hid, c, **f32)
+                buf["edge_slot"] = torch.zeros(cap, dtype=torch.int32, device=dev)
+                buf["canon_list"] = torch.zeros(cap, dtype=torch.int32, device=dev)
+                buf["canon_count"] = torch.zeros(1, dtype=torch.int64, device=dev)
             except torch.OutOfMemoryError:
                 # the free memory was there but not in one piece: run the mirror-evaluation adjoint instead
-                for name in ("mirror", "edge_q", "edge_dx"):
+                for name in ("mirror", "edge_q", "edge_dx", "edge_slot", "canon_list", "canon_count"):
                     buf.pop(name, None)
                 torch.cuda.empty_cache()
                 self.edge_local = False

@@ -230,6 +230,14 @@ typedef struct {
     int32_t* mirror;
     float* edge_q;
     float* edge_dx;
+    /* Optional, with the three above: an edge and its opposite edge have the same length, hence the same radial
+     * weights, so the last interaction's weights are produced once per pair. canon_list [edge_capacity] int32 lists the
+     * edges that stand for their pair (the lower index of the two), canon_count [1] int64 their number, edge_slot
+     * [edge_capacity] int32 holds, for a listed edge, its row in tp_w. Written by fmb_edge_features every call. Null =
+     * one row of tp_w per edge. */
+    int32_t* edge_slot;
+    int32_t* canon_list;
+    long long* canon_count;
     /* Optional: atoms grouped four at a time by species for the symmetric contraction ([n_symcon_groups][4] atom
      * indices, -1 = empty slot; every atom exactly once; all atoms of a group have the same species). Null = one atom per
      * CTA. */

@@ -458,6 +458,7 @@ def run_domain(args, world, rank, local_rank, device):
                             local_over_owned=max(l / max(1, o) for l, o in zip(local_all, owned_all)),
                             halo_rows_sent=sent_all, local_edges_rank0=n_edges, initial_energy_eV=initial_energy,
                             repartitions=info["repartitions"], repartition_seconds=info["repartition_seconds"],
+                            repartition_seconds_each=info["repartition_log"],
                             exchanges="per step: positions (24 B), x rows and their gradient (%d B each), forces (12 B) per "
                                       "halo atom over NCCL all_to_all; all-reduces of 10 + 10 float64 and one flag" % row,
                             nvlink_bytes_per_step_rank0=sent_all[0] * (24 + 2 * row + 12),

@@ -458,6 +458,7 @@ class DomainSimulation:
         self.step_count = 0
         self.repartitions = 0
         self.repartition_seconds = 0.0
+        self.repartition_log: list[float] = []      # seconds of each re-partition (the first one sets the buffers up)
         self.energy = torch.zeros(1, **f64)
         self.stress = torch.zeros(3, 3, **f64)
         positions = torch.tensor(np.asarray(structure.positions), **f64)
@@ -494,6 +495,7 @@ class DomainSimulation:
             r.set_partition(part, positions, velocities, random_kick)
         torch.cuda.synchronize(self.device)
         self.repartition_seconds += time.perf_counter() - t0
+        self.repartition_log.append(round(time.perf_counter() - t0, 4))
         self.repartitions += 1
 
     # ------------------------------------------------------------------ exchanges
@@ -590,6 +592,7 @@ class DomainSimulation:
         return {"engine": "fmb200-halo", "ranks": self.plan.n_ranks, "bricks": self.plan.grid, "rank": r.rank,
                 "owned_atoms": r.part.n_owned, "local_atoms": r.part.n_local, "halo_rows_sent": len(r.part.send_index),
                 "repartitions": self.repartitions, "repartition_seconds": round(self.repartition_seconds, 4),
+                "repartition_log": list(self.repartition_log),
                 "steps": self.step_count,
                 "local_edges": int(r.ff.edge_count.item()) if r.active else 0,
                 "streaming_interactions": self.spec.num_interactions, "sort_receivers": True,

@@ -23,6 +23,7 @@ STATUS_BIN_OVERFLOW = 4
 STATUS_NONFINITE = 8
 STATUS_TENSOR_TIMEOUT = 16
 STATUS_NO_MIRROR = 32
+STATUS_PAIR_OVERFLOW = 64
 
 EXPORTS = ("fmb_version", "fmb_last_error", "fmb_sizeof", "fmb_launch_count", "fmb_nl_build", "fmb_nl_compact", "fmb_nl_compact_static",
            "fmb_nl_needs_rebuild",
@@ -85,6 +86,7 @@ class WorkStruct(ctypes.Structure):
         ("mirror", c_void_p), ("edge_q", c_void_p), ("edge_dx", c_void_p),
         ("edge_slot", c_void_p), ("canon_list", c_void_p), ("canon_count", c_void_p),
         ("symcon_groups", c_void_p), ("n_symcon_groups", c_int32), ("halo_exchange", c_int32),
+        ("pair_capacity", c_int32), ("pad_", c_int32),
     ]
 
 

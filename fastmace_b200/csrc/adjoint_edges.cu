@@ -54,7 +54,7 @@ __global__ void k_mirror(const long long* __restrict__ count_ptr, int capacity, 
                          const float* __restrict__ unit_shifts, const int32_t* __restrict__ row_ptr,
                          int32_t* __restrict__ mirror, uint32_t* __restrict__ status,
                          const long long* __restrict__ listed_below, int32_t* __restrict__ slot,
-                         int32_t* __restrict__ list, unsigned long long* __restrict__ list_count) {
+                         int32_t* __restrict__ list, unsigned long long* __restrict__ list_count, int list_capacity) {
     const long long count = *count_ptr;
     const long long listed = slot ? *listed_below : 0;
     for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < count; e += (long long)gridDim.x * blockDim.x) {
@@ -77,9 +77,14 @@ __global__ void k_mirror(const long long* __restrict__ count_ptr, int capacity, 
         mirror[e] = found;
         if (found < 0) atomicOr(status, FMB_STATUS_NO_MIRROR);
         if (slot && e < listed && (found < 0 || e < found)) {
-            const int k = (int)atomicAdd(list_count, 1ull);
-            slot[e] = k;
-            list[k] = (int)e;
+            const unsigned long long k = atomicAdd(list_count, 1ull);
+            if (k < (unsigned long long)list_capacity) {
+                slot[e] = (int)k;
+                list[k] = (int)e;
+            } else {
+                slot[e] = 0;                                   // a row that exists; the status word says it is wrong
+                atomicOr(status, FMB_STATUS_PAIR_OVERFLOW);
+            }
         }
     }
 }
@@ -540,12 +545,13 @@ int grid_for(const void* kernel, int rows, int threads, size_t smem) {
 }  // namespace
 
 int mirror_map(const fmb_nl_t* nl, int32_t* mirror, uint32_t* status, const long long* listed_below, int32_t* slot,
-               int32_t* list, long long* list_count, cudaStream_t stream) {
+               int32_t* list, long long* list_count, int list_capacity, cudaStream_t stream) {
     const int blocks = ceil_div(nl->capacity, 256);
     if (slot) FMB_CUDA_CHECK(cudaMemsetAsync(list_count, 0, sizeof(long long), stream));
     k_mirror<<<blocks < 1184 ? blocks : 1184, 256, 0, stream>>>((const long long*)nl->count, nl->capacity, nl->edge_index,
                                                                nl->unit_shifts, nl->edge_row_ptr, mirror, status,
-                                                               listed_below, slot, list, (unsigned long long*)list_count);
+                                                               listed_below, slot, list, (unsigned long long*)list_count,
+                                                               list_capacity);
     FMB_LAUNCH_CHECK();
     return FMB_OK;
 }

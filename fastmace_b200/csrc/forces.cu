@@ -176,13 +176,21 @@ bool pair_rows(const Ctx& c) {
            c.w->canon_count && c.m->layer[last].l_in_max == 1 && c.m->layer[last].rad_img != nullptr;
 }
 
+// rows of each half of tp_w (values, then d/dr)
+long long weight_rows(const Ctx& c) { return c.w->pair_capacity > 0 ? (long long)c.w->pair_capacity : c.chunk; }
+
 // first .. last: 0 = values, 1 = their d/dr (second half of tp_w)
 // `stream` / `max_ctas`: the producer can run on the side stream with fewer CTAs than SMs (it is one persistent CTA per
 // SM with all of its shared and tensor memory, so the SMs it leaves free are what the kernels beside it run on)
 int radial_weights(const Ctx& c, int layer, long long e0, int first, int last, const long long* limit,
                    cudaStream_t stream = nullptr, int max_ctas = 0) {
     const fmb_layer_t& L = c.m->layer[layer];
-    const long long rows = std::min<long long>(c.chunk, c.count_cap - e0);
+    long long rows = std::min<long long>(c.chunk, c.count_cap - e0);
+    if (c.w->pair_capacity > 0) {
+        FMB_REQUIRE(layer == c.m->n_layers - 1 && pair_rows(c),
+                    "forces: tp_w is sized for one row per pair of opposite edges, which this call cannot use");
+        rows = std::min<long long>(rows, c.w->pair_capacity);
+    }
     if (!stream) stream = c.stream;
     StageScope scope(stream, kStRadial);
     if (L.rad_img && tensor_cores_enabled()) {
@@ -192,7 +200,7 @@ int radial_weights(const Ctx& c, int layer, long long e0, int first, int last, c
         bool done = true;
         for (int tangent = first; tangent <= last && done; ++tangent) {
             const int rc = radial_weights_tc(hidden_of(c, layer, tangent) + e0 * kRadial, L.rad_img,
-                                             c.w->tp_w + (long long)tangent * c.chunk * L.n_paths * kC, (int)rows, L.n_paths,
+                                             c.w->tp_w + (long long)tangent * weight_rows(c) * L.n_paths * kC, (int)rows, L.n_paths,
                                              limit, e0, pairs ? c.w->canon_list : nullptr, c.w->status, max_ctas, stream);
             if (rc == FMB_ERR_UNSUPPORTED) done = false;
             else if (rc) return rc;
@@ -211,7 +219,7 @@ int radial_weights(const Ctx& c, int layer, long long e0, int first, int last, c
             g.bt_lo = L.tc[0] + (long long)kRadial * L.n_paths * kC;
         }
         g.error_word = c.w->status;
-        g.c = c.w->tp_w + (long long)tangent * c.chunk * L.n_paths * kC;
+        g.c = c.w->tp_w + (long long)tangent * weight_rows(c) * L.n_paths * kC;
         g.c_bs = (long long)L.n_paths * kC;
         g.m = (int)rows;
         g.n = L.n_paths * kC;
@@ -453,7 +461,7 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
         t.n_gather = c.exchange ? c.n : c.n0;      // halo atoms collect their shares too: they go back to their owners
         t.row_ptr = c.nl->edge_row_ptr; t.senders = c.nl->edge_index; t.mirror = c.w->mirror; t.x = c.w->x;
         t.edge_sh = c.w->edge_sh; t.edge_vec = c.w->edge_vec; t.tp_w = c.w->tp_w;
-        t.tangent_offset = c.chunk * L.n_paths * kC; t.d_mid = c.w->d_mid; t.dxe = c.w->edge_dx; t.qe = c.w->edge_q;
+        t.tangent_offset = weight_rows(c) * L.n_paths * kC; t.d_mid = c.w->d_mid; t.dxe = c.w->edge_dx; t.qe = c.w->edge_q;
         t.d_x = c.w->d_x; t.whole_list = c.n_chunks == 1; t.error_word = c.w->status;
         if (layer == c.m->n_layers - 1 && pair_rows(c)) t.slot = c.w->edge_slot;
         for (int k = 0; k < c.n_chunks; ++k) {
@@ -487,7 +495,7 @@ int backward_layer(const Ctx& c, int layer, const float* d_h_out, float* d_h_in,
         t.lin = L.l_in_max; t.species_x = layer == 0; t.n_atoms = c.n;
         // every atom that sends into a row with a gradient gets a force; first-layer senders are all atoms
         t.n_rows = layer == 0 ? c.n : c.n0; t.n_valid = rows; t.fresh_from = layer == 0 ? c.n0 : 0;
-        t.chunk_e0 = e0; t.chunk_edges = c.chunk; t.tangent_offset = c.chunk * L.n_paths * kC;
+        t.chunk_e0 = e0; t.chunk_edges = c.chunk; t.tangent_offset = weight_rows(c) * L.n_paths * kC;
         t.count = (const long long*)c.nl->count; t.row_ptr = c.nl->edge_row_ptr; t.senders = c.nl->edge_index;
         t.species = c.w->species; t.x = layer == 0 ? L.x_species : c.w->x;
         t.edge_sh = c.w->edge_sh; t.edge_vec = c.w->edge_vec; t.tp_w = c.w->tp_w;
@@ -561,7 +569,8 @@ extern "C" FMB_API int fmb_edge_features(const fmb_model_t* model, const fmb_nl_
         FMB_TRY(make_ctx(c, model, nl, work, (cudaStream_t)stream));
         const bool pairs = pair_rows(c);
         return mirror_map(nl, work->mirror, work->status, limit ? limit : (const long long*)nl->count,
-                          pairs ? work->edge_slot : nullptr, work->canon_list, work->canon_count, (cudaStream_t)stream);
+                          pairs ? work->edge_slot : nullptr, work->canon_list, work->canon_count,
+                          work->pair_capacity > 0 ? work->pair_capacity : nl->capacity, (cudaStream_t)stream);
     }
     return FMB_OK;
 }

@@ -119,7 +119,7 @@ struct EdgeAdjointArgs {
 };
 // `slot`, `list`, `list_count` (or null): the edges below *listed_below that stand for their pair
 int mirror_map(const fmb_nl_t* nl, int32_t* mirror, uint32_t* status, const long long* listed_below, int32_t* slot,
-               int32_t* list, long long* list_count, cudaStream_t stream);
+               int32_t* list, long long* list_count, int list_capacity, cudaStream_t stream);
 // per-edge adjoint of an interaction after the first for one chunk of edges; after the last chunk the gather of the
 // sender-side gradients into d_x
 int tp_adjoint_edges(const EdgeAdjointArgs& t, cudaStream_t stream);

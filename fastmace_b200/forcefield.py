@@ -192,17 +192,31 @@ class B200ForceField:
         c = spec.channels
         max_paths = max(len(spec.paths(t)) for t in range(spec.num_interactions))
         hid = (spec.hidden_lmax + 1) ** 2
+        pair_capacity = 0
         if self.chunk_edges is not None:
             chunk = min(self.chunk_edges, cap)
         elif cap <= DEFAULT_CHUNK_EDGES:
             chunk = cap
+        elif getattr(self, "_chunked_only", False):
+            chunk = DEFAULT_CHUNK_EDGES
         else:
-            # everything this function allocates per edge with the whole list as one chunk: weights and their d/dr,
-            # vector, harmonics, hidden features, hand-over buffers
+            # what this function allocates per edge with the whole list as one chunk: vector, harmonics, hidden
+            # features, hand-over buffers with the pair map -- and the weights with their d/dr, one row per edge or,
+            # where the kernels that read one row per pair of opposite edges apply, a little over half a row
             free, _ = torch.cuda.mem_get_info(dev)
             free += torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)
-            per_edge = 2 * max_paths * c * 4 + 16 + 64 + spec.num_interactions * 2 * 64 * 4 + hid * c * 4 + 20
-            chunk = cap if cap * per_edge <= 0.85 * free else DEFAULT_CHUNK_EDGES
+            others = 16 + 64 + spec.num_interactions * 2 * 64 * 4 + hid * c * 4 + 28
+            row = 2 * max_paths * c * 4
+            layers = self.packed.struct.layer
+            pair_rows = (self.edge_adjoint is not False and spec.num_interactions == 2 and spec.l_in_max(1) == 1
+                         and bool(layers[1].rad_img) and bool(layers[0].first[0]))
+            pairs = cap // 2 + cap // 16
+            if pair_rows and cap * others + pairs * row <= 0.85 * free:
+                chunk, pair_capacity = cap, pairs
+            elif cap * (others + row) <= 0.85 * free:
+                chunk = cap
+            else:
+                chunk = DEFAULT_CHUNK_EDGES
         max_mid = max(self.packed.struct.layer[t].mid_dim for t in range(spec.num_interactions))
         # the reassociated first layer keeps its per-species outer-product sums [16][n_species][64] in `mid` / `d_mid`
         mid_floats = max(max_mid * c, 16 * len(self.packed.species_z) * 64)
@@ -211,7 +225,7 @@ class B200ForceField:
             "edge_vec": torch.zeros(cap, 4, **f32),
             "edge_sh": torch.zeros(cap, 16, **f32),
             "edge_hidden": torch.zeros(spec.num_interactions, 2, cap, 64, **f32),
-            "tp_w": torch.zeros(2 * chunk, max_paths * c, **f32),
+            "tp_w": torch.zeros(2 * (pair_capacity or chunk), max_paths * c, **f32),
             "x": torch.zeros(n, hid, c, **f32),
             "mid": torch.zeros(n, mid_floats, **f32),
             "msg": torch.zeros(spec.num_interactions, n, 16, c, **f32),
@@ -250,9 +264,17 @@ class B200ForceField:
                     buf.pop(name, None)
                 torch.cuda.empty_cache()
                 self.edge_local = False
+                if pair_capacity:
+                    # the weight buffer was sized for the pair map that now does not exist: size everything again,
+                    # in chunks
+                    del buf
+                    torch.cuda.empty_cache()
+                    self._chunked_only = True
+                    return self._allocate_work()
         self.buf = buf
         w = _lib.WorkStruct()
         w.edge_capacity, w.chunk_edges, w.compute_stress = cap, chunk, int(self._compute_stress)
+        w.pair_capacity = pair_capacity
         for name, tensor in buf.items():
             setattr(w, name, tensor.data_ptr())
         w.energy, w.forces, w.stress = self.energy.data_ptr(), self._forces_all.data_ptr(), self.stress.data_ptr()
@@ -336,6 +358,8 @@ class B200ForceField:
             raise _lib.Fmb200Error("an edge has no opposite edge: the neighbour list is not full")
         if status & _lib.STATUS_TENSOR_TIMEOUT:
             raise _lib.Fmb200Error("a tensor-core kernel gave up waiting (FMB_STATUS_TENSOR_TIMEOUT)")
+        if status & _lib.STATUS_PAIR_OVERFLOW:
+            raise _lib.Fmb200Error("more pairs of opposite edges than the radial-weight buffer has rows")
 
     def per_atom_energies(self):
         return self.buf["node_energy"][:self.natoms].double().cpu().numpy()

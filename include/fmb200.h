@@ -36,6 +36,7 @@ extern "C" {
 #define FMB_STATUS_NONFINITE 8u       /* a non-finite energy was produced */
 #define FMB_STATUS_TENSOR_TIMEOUT 16u /* a tensor-core kernel gave up waiting for its own MMA completion barrier */
 #define FMB_STATUS_NO_MIRROR 32u      /* an edge has no opposite edge: the neighbour list is not a full list */
+#define FMB_STATUS_PAIR_OVERFLOW 64u  /* more pairs of opposite edges than tp_w has rows (pair_capacity) */
 
 #define FMB_MAX_ROW 1024              /* candidates per receiver the in-kernel sort can hold */
 #define FMB_MAX_LAYERS 2
@@ -250,6 +251,11 @@ typedef struct {
      * phase 1 (returned to their owners, whose rows receive them before phase 2), and forces come out as partial sums
      * for every local atom (the halo atoms' shares go back to their owners). */
     int32_t halo_exchange;
+    /* With the pair-row fields above: the rows each half of tp_w holds when it is sized for one row per pair of
+     * opposite edges (a little over edge_capacity / 2) instead of chunk_edges rows; 0 = chunk_edges rows. A list with
+     * more pairs than that raises FMB_STATUS_PAIR_OVERFLOW and the rows beyond are not produced. */
+    int32_t pair_capacity;
+    int32_t pad_;
 } fmb_work_t;
 
 /* MACEForceField.__call__ (fastmace/model/forces.py:1127-1136,1220-1240): energy (float64), forces and stress of the

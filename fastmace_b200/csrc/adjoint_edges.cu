@@ -41,10 +41,6 @@ FMB_TP_BACKWARD_SEL(2)
 
 constexpr int kBatch = 8;
 constexpr int kAdjBatch = 16;          // edges between two CTA barriers of the streamed kernels (their 17 sums meet in shared memory)
-#ifndef FMB_ADJ_STAGES
-#define FMB_ADJ_STAGES 3
-#define FMB_ADJ_MINB 4
-#endif
 
 // mirror[e] = index of the edge (sender = receiver(e), receiver = sender(e), image = -image(e)), or -1. With `slot`:
 // the edges below *listed_below that stand for their pair (no opposite edge, or the lower index of the two) are listed
@@ -565,7 +561,7 @@ int tp_adjoint_edges(const EdgeAdjointArgs& t, cudaStream_t stream) {
             t.tp_w, t.tangent_offset, t.d_mid, t.dxe,
             reinterpret_cast<float4*>(t.qe));
     } else if (t.lin == 1 && t.whole_list && t.n_valid >= t.n_rows && t.chunk_e0 == 0) {
-        constexpr int kStages = FMB_ADJ_STAGES, kMinB = FMB_ADJ_MINB;
+        constexpr int kStages = 3, kMinB = 4;      // measured best of 2 .. 6 stages at 2 .. 4 CTAs per SM
         constexpr int smem = kStages * (2 * TpShape<1>::kPaths * kC + TpShape<1>::kInDim * kC + 16) * 4;
         auto kernel = k_tp_adjoint_pairs<1, kStages, kMinB>;
         FMB_CUDA_CHECK(opt_in_shared_memory((const void*)kernel, smem));

@@ -337,12 +337,6 @@ __device__ __forceinline__ void store_split(uint8_t* hi_tile, uint8_t* lo_tile, 
     *reinterpret_cast<float4*>(lo_tile + off) = lo;
 }
 
-#ifdef FMB_EDGE_PROFILE
-#define FMB_ESTAMP() do { if (n_stamp < 40) stamp[n_stamp++] = clock64() - t_begin; } while (0)
-#else
-#define FMB_ESTAMP() do {} while (0)
-#endif
-
 __global__ void __launch_bounds__(kTcThreads, 2)
 k_edge_features_tc(const __grid_constant__ EdgeParams p, const double* __restrict__ x,
                    const int32_t* __restrict__ edge_index, const float* __restrict__ unit_shifts,
@@ -369,10 +363,6 @@ k_edge_features_tc(const __grid_constant__ EdgeParams p, const double* __restric
     const int row_v = quarter * 32 + (lane & 15), row_t = row_v + 16;
     const long long e = e0 + quarter * 16 + (lane & 15);
     const bool live = e < count;
-#ifdef FMB_EDGE_PROFILE
-    long long stamp[40]; int n_stamp = 0;
-    const long long t_begin = clock64();
-#endif
 
     auto request_weights = [&](int layer, int hidden) {
         const float* img = p.mlp_img[layer];
@@ -416,16 +406,13 @@ k_edge_features_tc(const __grid_constant__ EdgeParams p, const double* __restric
                 store_split(a_hi, a_lo, row_v, 4 * half, make_float4(ef[0], ef[1], ef[2], ef[3]));
                 store_split(a_hi, a_lo, row_t, 4 * half, make_float4(def[0], def[1], def[2], def[3]));
             }
-            FMB_ESTAMP();      // 0: operands written
             fence_async_smem();
             fence_before_sync();
             __syncthreads();
             fence_after_sync();
-            FMB_ESTAMP();      // 1: CTA synchronised
             if (layer == 0 && hidden == 0) tmem_base = *tmem_slot;
             if (tid == 0) {
                 mbar_wait(bar_w, w_parity, abort_flag, kTcSpin);
-                FMB_ESTAMP();  // 2: weights there
                 const uint32_t idesc = make_idesc<64>();
                 const uint64_t da_hi = make_desc(smem_u32(a_hi)), da_lo = make_desc(smem_u32(a_lo));
                 const uint64_t dw_hi = make_desc(smem_u32(w_buf)), dw_lo = make_desc(smem_u32(w_buf) + kTcWTile);
@@ -443,13 +430,11 @@ k_edge_features_tc(const __grid_constant__ EdgeParams p, const double* __restric
                     for (int k8 = 0; k8 < 8; ++k8) mma_tf32(tmem_base, da_hi + k_step<128>(k8), dw_hi + k_step<64>(k8), idesc, 1);
                 }
                 mma_commit(bar_mma);
-                FMB_ESTAMP();  // 3: issued
             }
             w_parity ^= 1u;
             mbar_wait(bar_mma, mma_parity, abort_flag, kTcSpin);
             mma_parity ^= 1u;
             fence_after_sync();
-            FMB_ESTAMP();      // 4: MMAs complete
             if (tid == 0) {
                 // the weight buffer is free: the next layer's image travels while this layer's SiLU runs
                 if (hidden < 2) request_weights(layer, hidden + 1);
@@ -464,7 +449,6 @@ k_edge_features_tc(const __grid_constant__ EdgeParams p, const double* __restric
 #pragma unroll
                 for (int i = 0; i < 16; ++i) { own[i] = v0[i]; own[16 + i] = v1[i]; }
             }
-            FMB_ESTAMP();      // 5: accumulator row loaded
             // the lower lane finishes the first 16 of these columns, the upper lane the other 16
             float act[16], tng[16];
 #pragma unroll
@@ -519,14 +503,6 @@ k_edge_features_tc(const __grid_constant__ EdgeParams p, const double* __restric
             }
         }
     }
-#ifdef FMB_EDGE_PROFILE
-    FMB_ESTAMP();
-    if (blockIdx.x == 0 && tid == 0) {
-        printf("edge_tc stamps:");
-        for (int i = 0; i < n_stamp; ++i) printf(" %lld", stamp[i]);
-        printf("\n");
-    }
-#endif
     fence_before_sync();
     __syncthreads();
     if (warp == 0) {

@@ -3,7 +3,7 @@ parts in the shared-memory operand layout, at the offsets the kernels compute.""
 import numpy as np
 import torch
 
-from fastmace_b200.packing import radial_image, tensor_core_image, tensor_core_twin, tf32_round
+from fastmace_b200.packing import mlp_image, radial_image, tensor_core_image, tensor_core_twin, tf32_round
 
 
 def _tile_offset(row, k):
@@ -57,6 +57,39 @@ def test_radial_image_pieces():
         p, c, k = int(rng.integers(3)), int(rng.integers(128)), int(rng.integers(64))
         assert float(image[p, k // 32, 1, _tile_offset(c, k % 32)]) == float(hi[p * 128 + c, k])
         assert float(image[p, k // 32, 0, _tile_offset(c, k % 32)]) == float(lo[p * 128 + c, k])
+
+
+def test_mlp_image_layers_at_the_offsets_the_edge_kernel_copies():
+    """The three hidden radial layers as [64 outputs][K] operand tiles (halves of 32 K, 2,048 floats each; the row
+    pattern of a 64-row tile is that of the first 64 rows of a 128-row one): first layer at float 0 (values) and 2,048
+    (remainders) with K = 8 of the 32 columns filled, the 64 x 64 layers at 4,096 / 8,192 and 12,288 / 16,384."""
+    torch.manual_seed(2)
+    w0, w1, w2 = torch.randn(8, 64), torch.randn(64, 64), torch.randn(64, 64)
+    image = mlp_image(w0, w1, w2)
+    assert image.numel() == 20480
+    rng = np.random.default_rng(2)
+    bt = w0.t().contiguous()
+    hi = tf32_round(bt)
+    lo = tf32_round(bt - hi)
+    for n in range(64):
+        for k in range(32):
+            want_hi = float(hi[n, k]) if k < 8 else 0.0
+            want_lo = float(lo[n, k]) if k < 8 else 0.0
+            assert float(image[_tile_offset(n, k)]) == want_hi
+            assert float(image[2048 + _tile_offset(n, k)]) == want_lo
+    for layer, w in enumerate((w1, w2)):
+        bt = w.t().contiguous()
+        hi = tf32_round(bt)
+        lo = tf32_round(bt - hi)
+        base = 4096 + layer * 8192
+        for _ in range(300):
+            n, k = int(rng.integers(64)), int(rng.integers(64))
+            at = (k // 32) * 2048 + _tile_offset(n, k % 32)
+            assert float(image[base + at]) == float(hi[n, k])
+            assert float(image[base + 4096 + at]) == float(lo[n, k])
+    # every float of the image is one of the parts (nothing written twice, nothing left over in the 64 x 64 layers)
+    assert int((image[4096:] != 0).sum()) == int((tf32_round(w1) != 0).sum() + (tf32_round(w1 - tf32_round(w1)) != 0).sum()
+                                                  + (tf32_round(w2) != 0).sum() + (tf32_round(w2 - tf32_round(w2)) != 0).sum())
 
 
 def test_species_groups_cover_every_atom_once():

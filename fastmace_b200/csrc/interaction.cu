@@ -125,8 +125,8 @@ k_tp_forward_stream(int n_rows, const int32_t* __restrict__ row_ptr, const int32
     __shared__ int abort_sh;
     volatile int* abort_flag = &abort_sh;
     const int c = threadIdx.x, lane = c & 31;
-    const int per_cta = (n_rows + gridDim.x - 1) / gridDim.x;
-    const int r0 = blockIdx.x * per_cta, r1 = min(n_rows, r0 + per_cta);
+    // contiguous blocks of receivers that differ by at most one row, so that every CTA of the grid has work
+    const int r0 = (int)((long long)blockIdx.x * n_rows / gridDim.x), r1 = (int)((long long)(blockIdx.x + 1) * n_rows / gridDim.x);
     if (r0 >= r1) return;
     const long long eb = row_ptr[r0], ee = row_ptr[r1];
     const uint32_t bar0 = tc::smem_u32(bars), ring0 = tc::smem_u32(ring);
@@ -215,8 +215,8 @@ k_tp_forward_pairs(int n_rows, const int32_t* __restrict__ row_ptr, const int32_
     __shared__ int abort_sh;
     volatile int* abort_flag = &abort_sh;
     const int c = threadIdx.x, lane = c & 31;          // channels 2 c and 2 c + 1
-    const int per_cta = (n_rows + gridDim.x - 1) / gridDim.x;
-    const int r0 = blockIdx.x * per_cta, r1 = min(n_rows, r0 + per_cta);
+    // contiguous blocks of receivers that differ by at most one row, so that every CTA of the grid has work
+    const int r0 = (int)((long long)blockIdx.x * n_rows / gridDim.x), r1 = (int)((long long)(blockIdx.x + 1) * n_rows / gridDim.x);
     if (r0 >= r1) return;
     const long long eb = row_ptr[r0], ee = row_ptr[r1];
     const uint32_t bar0 = tc::smem_u32(bars), ring0 = tc::smem_u32(ring);

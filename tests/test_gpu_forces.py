@@ -160,6 +160,38 @@ def test_medium_216_atoms():
     assert df <= 5e-4 * fscale + 1e-7
 
 
+def test_pair_rows_hold_the_radial_weights_of_both_edges_of_a_pair():
+    """With the whole list as one chunk an edge and its opposite edge share one row of radial weights (they have the
+    same length). After a force call: every pair is listed once, the slots are the rows 0 .. pairs - 1, and the row an
+    edge reads -- slot[min(e, mirror e)] -- holds hidden(e) x (last radial layer) for values and for d/dr."""
+    from fastmace_b200.forcefield import B200ForceField
+    spec, weights, s = _case("medium216")
+    ff = B200ForceField(spec, weights, s.numbers, s.cell, compute_stress=True)
+    ff.evaluate(s, stress=True)
+    torch.cuda.synchronize()
+    assert int(ff.work.pair_capacity) == 0 and "edge_slot" in ff.buf
+    count = int(ff.neighbours.count.item())
+    mirror = ff.buf["mirror"][:count].long()
+    edges = torch.arange(count, device=ff.device)
+    assert bool((mirror >= 0).all()) and bool((mirror[mirror] == edges).all()) and bool((mirror != edges).all())
+    pairs = int(ff.buf["canon_count"].item())
+    assert pairs * 2 == count
+    listed = edges < mirror
+    slots = ff.buf["edge_slot"][:count].long()
+    assert torch.equal(torch.sort(slots[listed]).values, torch.arange(pairs, device=ff.device))
+    assert torch.equal(ff.buf["canon_list"][:pairs].long()[slots[listed]], edges[listed])
+    row = slots[torch.minimum(edges, mirror)]
+    last = spec.num_interactions - 1
+    rad = ff.packed.tensors[f"l{last}.rad.3"].double()                        # [64][paths * C], scaled
+    rows_per_half = ff.buf["tp_w"].shape[0] // 2
+    for tangent in (0, 1):
+        hidden = ff.buf["edge_hidden"][last, tangent, :count].double()
+        want = hidden @ rad
+        got = ff.buf["tp_w"][tangent * rows_per_half + row].double()
+        scale = float(want.abs().max())
+        assert float((got - want).abs().max()) <= 2e-6 * scale, tangent
+
+
 def test_gemm_kernels_against_torch():
     """SIMT fp32 GEMM and the tcgen05 3xTF32 GEMM against a float64 product."""
     from fastmace_b200 import _lib
